@@ -1,0 +1,362 @@
+// Quantize-at-load weight packers and their inverses, plus the fp16 (SD/SDXL) row quantizer that serves both
+// weights at load and activations at run time.
+//
+//   gpu_sd_quant_rows      fp16 rows -> [R64|R256] -> int8 + fp32 row scale          reference csrc/sd.cu:578-606
+//   gpu_convrot_requant    f32/bf16 weight -> R256 -> int8 + row scale (seed 0: nearest-even; else PCG-hash
+//                          stochastic rounding)                                       csrc/kernels.cu:1362-1389,1409-1420
+//   gpu_convrot_dequant    int8 ConvRot weight -> original basis (f32/bf16)           csrc/kernels.cu:1345-1354,1393-1405
+//   gpu_embed_dequant      int8 ConvRot embedding rows -> f32 rows of bf16 values     csrc/kernels.cu:622-638
+//   gpu_dequant_i8         int8 * row scale -> f32                                    csrc/kernels.cu:330-343
+//   gpu_w6_decode          6-bit two-plane codes + e4m3 group scales -> int8          csrc/h3.cu:11-46
+//
+// One CTA per row; the row lives in shared memory as fp32 (padded against bank conflicts). The rotation runs as
+// two register phases: each thread takes 16 consecutive elements (index bits 0-3: radix-4 stages 0 and 1), then 16
+// elements 16 apart (index bits 4-7: stages 2 and 3; groups of 64 have only stage 2), so a row is read and written
+// in shared memory twice whatever its length. Every butterfly adds in the reference's left-to-right order.
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+
+namespace {
+
+// element i of the row sits at word i + 4*(i/16): 16-element runs stay 16-byte aligned and consecutive runs start
+// 20 banks apart
+__device__ __forceinline__ int pad(int i) { return i + ((i >> 4) << 2); }
+__host__ __device__ constexpr int padded_words(int K) { return K + ((K + 15) / 16) * 4 + 4; }
+
+__device__ __forceinline__ void h4(float& x0, float& x1, float& x2, float& x3) {
+    const float s = __fadd_rn(x0, x1), d = __fsub_rn(x0, x1);
+    const float r0 = __fmul_rn(0.5f, __fsub_rn(__fadd_rn(s, x2), x3));
+    const float r1 = __fmul_rn(0.5f, __fadd_rn(__fsub_rn(s, x2), x3));
+    const float r2 = __fmul_rn(0.5f, __fadd_rn(__fadd_rn(d, x2), x3));
+    const float r3 = __fmul_rn(0.5f, __fadd_rn(__fadd_rn(-d, x2), x3));
+    x0 = r0, x1 = r1, x2 = r2, x3 = r3;
+}
+
+// In-place rotation of the padded shared-memory row: groups of 256 (four stages) or 64 (three).
+__device__ void rotate_row_smem(float* row, int K, int group) {
+    // phase 1: stages 0 and 1 on 16 consecutive elements
+    for (int c = threadIdx.x; c < K / 16; c += blockDim.x) {
+        float v[16];
+        float* base = row + pad(c * 16);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float4 f = reinterpret_cast<const float4*>(base)[i];
+            v[4 * i] = f.x, v[4 * i + 1] = f.y, v[4 * i + 2] = f.z, v[4 * i + 3] = f.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; i += 4) h4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h4(v[i], v[i + 4], v[i + 8], v[i + 12]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) reinterpret_cast<float4*>(base)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    }
+    __syncthreads();
+    if (group == 256) {
+        // phase 2: stages 2 and 3 on elements e + 16 r of a 256-group
+        for (int c = threadIdx.x; c < K / 16; c += blockDim.x) {
+            const int g = c >> 4, e = c & 15;
+            float v[16];
+#pragma unroll
+            for (int r = 0; r < 16; ++r) v[r] = row[pad((g << 8) + e + 16 * r)];
+#pragma unroll
+            for (int i = 0; i < 16; i += 4) h4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) h4(v[i], v[i + 4], v[i + 8], v[i + 12]);
+#pragma unroll
+            for (int r = 0; r < 16; ++r) row[pad((g << 8) + e + 16 * r)] = v[r];
+        }
+    } else {
+        // phase 2: stage 2 on elements e + 16 r, r < 4, of a 64-group
+        for (int c = threadIdx.x; c < K / 4; c += blockDim.x) {
+            const int g = c >> 4, e = c & 15;
+            float* b = row;
+            const int i0 = (g << 6) + e;
+            float x0 = b[pad(i0)], x1 = b[pad(i0 + 16)], x2 = b[pad(i0 + 32)], x3 = b[pad(i0 + 48)];
+            h4(x0, x1, x2, x3);
+            b[pad(i0)] = x0, b[pad(i0 + 16)] = x1, b[pad(i0 + 32)] = x2, b[pad(i0 + 48)] = x3;
+        }
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    float t = lane < nw ? red[lane] : 0.f;
+    return warp_max(t);
+}
+
+// ---- fp16 row quantizer ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) sd_quant_rows_kernel(const half* __restrict__ x, int64_t x_stride,
+                                                            int8_t* __restrict__ q, float* __restrict__ scales, int K,
+                                                            int rotate, int vec) {
+    extern __shared__ float row[];
+    __shared__ float red[32];
+    const int64_t m = blockIdx.x;
+    const half* r = x + m * x_stride;
+    if (vec) {
+        for (int c = threadIdx.x; c < K / 8; c += blockDim.x) {
+            const uint4 u = __ldg(reinterpret_cast<const uint4*>(r) + c);
+            const __half2* h = reinterpret_cast<const __half2*>(&u);
+            float* d = row + pad(c * 8);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(h[i]);
+                d[2 * i] = f.x, d[2 * i + 1] = f.y;
+            }
+        }
+    } else {
+        for (int k = threadIdx.x; k < K; k += blockDim.x) row[pad(k)] = __half2float(r[k]);
+    }
+    __syncthreads();
+    if (rotate) rotate_row_smem(row, K, rotate);
+    float mx = 0.f;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) mx = fmaxf(mx, fabsf(rnd<half>(row[pad(k)])));
+    mx = block_max(mx, red);
+    const float scale = __fdiv_rn(fmaxf(mx, 1e-30f), 127.f);
+    if (threadIdx.x == 0) scales[m] = scale;
+    const float sh = rnd<half>(scale);
+    const float st = sh > 0.f ? sh : scale;  // a scale below half's range divides in float
+    int8_t* qr = q + m * (int64_t)K;
+    if (vec) {
+        for (int c = threadIdx.x; c < K / 8; c += blockDim.x) {
+            const float* s = row + pad(c * 8);
+            uint32_t w[2] = {0u, 0u};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int qi = clamp_rint_i8(rnd<half>(__fdiv_rn(rnd<half>(s[j]), st)), -128.f);
+                w[j >> 2] |= (uint32_t)(qi & 0xff) << (8 * (j & 3));
+            }
+            reinterpret_cast<uint2*>(qr)[c] = make_uint2(w[0], w[1]);
+        }
+    } else {
+        for (int k = threadIdx.x; k < K; k += blockDim.x)
+            qr[k] = (int8_t)clamp_rint_i8(rnd<half>(__fdiv_rn(rnd<half>(row[pad(k)]), st)), -128.f);
+    }
+}
+
+// ---- ConvRot weight requant / dequant -------------------------------------------------------------------
+__device__ __forceinline__ uint32_t pcg_hash(uint32_t x) {
+    const uint32_t state = x * 747796405u + 2891336453u;
+    const uint32_t word = ((state >> ((state >> 28u) + 4u)) ^ state) * 277803737u;
+    return (word >> 22u) ^ word;
+}
+__device__ __forceinline__ float noisy_sum(float scaled, float noise, float*) { return __fadd_rn(scaled, noise); }
+__device__ __forceinline__ float noisy_sum(float scaled, float noise, bf16*) {
+    return __bfloat162float(__hadd(__float2bfloat16_rn(scaled), __float2bfloat16_rn(noise)));
+}
+template <typename T> __device__ __forceinline__ float finite_max_t();
+template <> __device__ __forceinline__ float finite_max_t<float>() { return FLT_MAX; }
+template <> __device__ __forceinline__ float finite_max_t<bf16>() { return 3.38953139e38f; }
+
+template <typename T>
+__global__ void __launch_bounds__(512) convrot_requant_kernel(const T* __restrict__ x, int8_t* __restrict__ q,
+                                                              float* __restrict__ scales, int K, uint64_t seed) {
+    extern __shared__ float row[];
+    __shared__ float red[32];
+    const int64_t m = blockIdx.x;
+    const T* r = x + m * (int64_t)K;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) row[pad(k)] = to_f<T>(r[k]);
+    __syncthreads();
+    rotate_row_smem(row, K, 256);
+    float amax = 0.f;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) amax = fmaxf(amax, fabsf(row[pad(k)]));
+    amax = block_max(amax, red);
+    const float scale = fmaxf(fminf(amax, finite_max_t<T>()) * (1.f / 127.f), 1.0e-30f);
+    if (threadIdx.x == 0) scales[m] = scale;
+    const float st = rnd<T>(scale);
+    for (int c = threadIdx.x; c < K / 4; c += blockDim.x) {
+        uint32_t w = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int k = c * 4 + j;
+            const float scaled = rnd<T>(__fdiv_rn(rnd<T>(row[pad(k)]), st));
+            int qi;
+            if (seed == 0) {
+                qi = clamp_rint_i8(scaled, -128.f);
+            } else {
+                const uint64_t key = (uint64_t)(m * K + k) + seed;
+                const uint32_t folded = (uint32_t)key ^ (uint32_t)(key >> 32);
+                const float v = floorf(noisy_sum(scaled, (float)(pcg_hash(folded) >> 8) * 0x1.0p-24f, (T*)nullptr));
+                qi = (int)fminf(127.f, fmaxf(-128.f, v));
+            }
+            w |= (uint32_t)(qi & 0xff) << (8 * j);
+        }
+        reinterpret_cast<uint32_t*>(q + m * (int64_t)K)[c] = w;
+    }
+}
+
+// OUT_BF16_IN_F32: embed_dequant writes f32 rows holding bf16-rounded values
+template <typename T, bool ROUND_BF16>
+__global__ void __launch_bounds__(512) convrot_dequant_kernel(const int8_t* __restrict__ q, const float* __restrict__ s,
+                                                              T* __restrict__ out, int K) {
+    extern __shared__ float row[];
+    const int64_t m = blockIdx.x;
+    const float sc = s[m];
+    for (int c = threadIdx.x; c < K / 4; c += blockDim.x) {
+        const char4 v = reinterpret_cast<const char4*>(q + m * (int64_t)K)[c];
+        float* d = row + pad(c * 4);
+        d[0] = __fmul_rn((float)v.x, sc), d[1] = __fmul_rn((float)v.y, sc);
+        d[2] = __fmul_rn((float)v.z, sc), d[3] = __fmul_rn((float)v.w, sc);
+    }
+    __syncthreads();
+    rotate_row_smem(row, K, 256);
+    for (int k = threadIdx.x; k < K; k += blockDim.x) {
+        const float v = row[pad(k)];
+        out[m * (int64_t)K + k] = from_f<T>(ROUND_BF16 ? rnd<bf16>(v) : v);
+    }
+}
+
+__global__ void dequant_i8_kernel(const int8_t* __restrict__ q, const float* __restrict__ s, float* __restrict__ out,
+                                  int64_t N, int64_t K) {
+    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= N * K) return;
+    const char4 v = *reinterpret_cast<const char4*>(q + i);
+    const float sc = s[i / K];
+    *reinterpret_cast<float4*>(out + i) =
+        make_float4(__fmul_rn(v.x, sc), __fmul_rn(v.y, sc), __fmul_rn(v.z, sc), __fmul_rn(v.w, sc));
+}
+
+// ---- W6 decode ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float e4m3_to_f(uint8_t v) {
+    return __half2float(__half(__nv_cvt_fp8_to_halfraw(v, __NV_E4M3)));
+}
+// One thread decodes 16 consecutive codes: 8 nibble bytes, 4 top-bit bytes, one group scale (G % 16 == 0).
+__global__ void __launch_bounds__(256) w6_decode_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ s_rel,
+                                                        int8_t* __restrict__ out, int64_t N, int K, int G) {
+    const int64_t per = K / 16;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N * per) return;
+    const int64_t n = i / per;
+    const int c = (int)(i - n * per);
+    const uint8_t* row = q + n * (int64_t)(K / 4 * 3);
+    const uint2 lo = __ldg(reinterpret_cast<const uint2*>(row + c * 8));
+    const uint32_t hi = __ldg(reinterpret_cast<const uint32_t*>(row + K / 2 + c * 4));
+    const float sc = e4m3_to_f(s_rel[n * (K / G) + c * 16 / G]);
+    const uint32_t lw[2] = {lo.x, lo.y};
+    uint32_t o[4];
+#pragma unroll
+    for (int e4 = 0; e4 < 4; ++e4) {  // four output words of four codes
+        uint32_t w = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int e = e4 * 4 + j;  // code index 0..15
+            const uint32_t nib = (lw[e >> 3] >> (4 * (e & 7))) & 15u;
+            const uint32_t top = (hi >> (2 * e)) & 3u;
+            const float cv = (float)(int)(nib | (top << 4)) - 32.f;
+            const int d = (int)fminf(127.f, fmaxf(-127.f, nearbyintf(__fmul_rn(cv, sc))));
+            w |= (uint32_t)(d & 0xff) << (8 * j);
+        }
+        o[e4] = w;
+    }
+    *reinterpret_cast<uint4*>(out + n * (int64_t)K + c * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+int set_smem(const void* fn, size_t bytes) {
+    if (bytes <= 48 * 1024) return 0;
+    const cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    return e == cudaSuccess ? 0 : (int)e;
+}
+int row_threads(int work_items, int cap) {
+    int t = (work_items + 31) / 32 * 32;
+    return t < 32 ? 32 : (t > cap ? cap : t);
+}
+
+}  // namespace
+
+// x fp16 [M, K] (row pitch x_stride elements) -> q int8 [M, K], scales f32 [M]; rotate 0, 64 or 256 (must divide K).
+GPU_API int gpu_sd_quant_rows(const void* x, int64_t x_stride, int8_t* q, float* scales, int M, int K, int rotate,
+                              void* stream) {
+    if ((rotate != 0 && rotate != 64 && rotate != 256) || (rotate && K % rotate)) return -1;
+    if (M <= 0 || K <= 0) return 0;
+    const size_t smem = (size_t)padded_words(K) * sizeof(float);
+    if (int rc = set_smem((const void*)sd_quant_rows_kernel, smem)) return rc;
+    const int vec = (K % 8 == 0) && (x_stride % 8 == 0) && (((uintptr_t)x & 15) == 0) && (((uintptr_t)q & 7) == 0);
+    sd_quant_rows_kernel<<<M, row_threads(K / 8, 256), smem, (cudaStream_t)stream>>>((const half*)x, x_stride, q, scales, K,
+                                                                                     rotate, vec);
+    KCHECK();
+    return 0;
+}
+
+// x [N, K] f32 or bf16 in its original basis -> rotated q [N, K] int8 and row scales s [N].
+GPU_API int gpu_convrot_requant(int dtype, const void* x, void* q, void* s, int64_t N, int K, uint64_t seed, void* stream) {
+    if (K % 256) return -1;
+    if (N <= 0) return 0;
+    const size_t smem = (size_t)padded_words(K) * sizeof(float);
+    const int threads = row_threads(K / 16, 512);
+    if (dtype == DT_F32) {
+        if (int rc = set_smem((const void*)convrot_requant_kernel<float>, smem)) return rc;
+        convrot_requant_kernel<float><<<(unsigned)N, threads, smem, (cudaStream_t)stream>>>((const float*)x, (int8_t*)q, (float*)s, K, seed);
+    } else if (dtype == DT_BF16) {
+        if (int rc = set_smem((const void*)convrot_requant_kernel<bf16>, smem)) return rc;
+        convrot_requant_kernel<bf16><<<(unsigned)N, threads, smem, (cudaStream_t)stream>>>((const bf16*)x, (int8_t*)q, (float*)s, K, seed);
+    } else {
+        return -4;
+    }
+    KCHECK();
+    return 0;
+}
+
+// q [N, K] int8 ConvRot weight, s [N] -> out [N, K] f32 or bf16 in the original basis.
+GPU_API int gpu_convrot_dequant(int dtype, const void* q, const void* s, void* out, int64_t N, int K, void* stream) {
+    if (K % 256) return -1;
+    if (N <= 0) return 0;
+    const size_t smem = (size_t)padded_words(K) * sizeof(float);
+    const int threads = row_threads(K / 16, 512);
+    if (dtype == DT_F32) {
+        if (int rc = set_smem((const void*)convrot_dequant_kernel<float, false>, smem)) return rc;
+        convrot_dequant_kernel<float, false><<<(unsigned)N, threads, smem, (cudaStream_t)stream>>>((const int8_t*)q, (const float*)s, (float*)out, K);
+    } else if (dtype == DT_BF16) {
+        if (int rc = set_smem((const void*)convrot_dequant_kernel<bf16, false>, smem)) return rc;
+        convrot_dequant_kernel<bf16, false><<<(unsigned)N, threads, smem, (cudaStream_t)stream>>>((const int8_t*)q, (const float*)s, (bf16*)out, K);
+    } else {
+        return -4;
+    }
+    KCHECK();
+    return 0;
+}
+
+// q [M, K] int8 ConvRot embedding rows, s [M] -> out f32 [M, K] holding bf16-rounded values; rotate must be set.
+GPU_API int gpu_embed_dequant(const int8_t* q, const float* s, float* out, int M, int K, int rotate, void* stream) {
+    if (!rotate || K % 256) return -1;
+    if (M <= 0) return 0;
+    const size_t smem = (size_t)padded_words(K) * sizeof(float);
+    if (int rc = set_smem((const void*)convrot_dequant_kernel<float, true>, smem)) return rc;
+    convrot_dequant_kernel<float, true><<<M, row_threads(K / 16, 512), smem, (cudaStream_t)stream>>>(q, s, out, K);
+    KCHECK();
+    return 0;
+}
+
+// out[n, k] = q[n, k] * s[n], f32.
+GPU_API int gpu_dequant_i8(const int8_t* q, const float* s, float* out, int64_t N, int64_t K, void* stream) {
+    if (K % 4) return -1;
+    const int64_t n4 = N * K / 4;
+    if (n4 <= 0) return 0;
+    dequant_i8_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(q, s, out, N, K);
+    KCHECK();
+    return 0;
+}
+
+// q [N, 3K/4] (per row: K/2 nibble bytes, then K/4 bytes of top bits), s_rel [N, K/G] e4m3 -> out int8 [N, K]:
+// out = clamp(rint((code - 32) * s_rel), +-127). K % 32 == 0 and G % 16 == 0, as the reference requires.
+GPU_API int gpu_w6_decode(const void* q, const void* s_rel, void* out, int64_t N, int K, int G, void* stream) {
+    if (K % 32 || G % 16) return -1;
+    const int64_t n = N * (K / 16);
+    if (n <= 0) return 0;
+    w6_decode_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const uint8_t*)q, (const uint8_t*)s_rel,
+                                                                                 (int8_t*)out, N, K, G);
+    KCHECK();
+    return 0;
+}
+
+// The reference's Rust side imports this Windows (DXCore) video-memory budget query unconditionally
+// (src/cuda.rs:136-153); non-zero means "no budget known", which is the answer everywhere else.
+GPU_API int gpu_wddm_budget(uint64_t* budget, uint64_t* usage) {
+    if (budget) *budget = 0;
+    if (usage) *usage = 0;
+    return 1;
+}

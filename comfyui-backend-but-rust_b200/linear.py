@@ -1,0 +1,174 @@
+"""Host side of the quantized linear over torch CUDA tensors.
+
+Mirrors how the reference's model code drives the path (e.g. src/qwen21.rs:365-418, src/dit.rs:539-614,
+src/unet.rs:359-457): ``gpu_quant_rows`` produces the int8 A operand and per-row scales, ``gpu_int8_gemm`` /
+``gpu_int8_gemm_residual`` consume them together with an int8 weight and per-channel scales. torch supplies device
+memory and the stream only; every computation is one of the library's kernels.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import ffi
+from .ffi import ok
+
+_DT = {torch.float32: ffi.DT_F32, torch.float16: ffi.DT_F16, torch.bfloat16: ffi.DT_BF16}
+
+
+def _lib():
+    from . import lib
+    return lib
+
+
+def _ptr(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _cuda(t: torch.Tensor) -> torch.Tensor:
+    if not t.is_cuda:
+        raise ValueError("this path runs on CUDA tensors only")
+    return t
+
+
+def quant_rows(x: torch.Tensor, prologue: int = ffi.PRO_PLAIN, rotate: int = 0, *, K: Optional[int] = None,
+               g: Optional[torch.Tensor] = None, up_offset: int = 0, q: Optional[torch.Tensor] = None,
+               scales: Optional[torch.Tensor] = None):
+    """gpu_quant_rows: x [M, >=K] bf16/f32 -> (q int8 [M, K], scales f32 [M])."""
+    _cuda(x)
+    M = x.shape[0]
+    K = K if K is not None else x.shape[1]
+    q = q if q is not None else torch.empty((M, K), dtype=torch.int8, device=x.device)
+    scales = scales if scales is not None else torch.empty((M,), dtype=torch.float32, device=x.device)
+    ok(_lib().gpu_quant_rows(_DT[x.dtype], prologue, _ptr(x), x.stride(0), _ptr(g), g.stride(0) if g is not None else 0,
+                             up_offset, 0, 0.0, 0, 0, _ptr(q), _ptr(scales), M, K, rotate, _stream()), "gpu_quant_rows")
+    return q, scales
+
+
+def rotate_rows_f32(x: torch.Tensor, prologue: int = ffi.PRO_PLAIN, *, K: Optional[int] = None, up_offset: int = 0):
+    _cuda(x)
+    M = x.shape[0]
+    K = K if K is not None else x.shape[1]
+    out = torch.empty((M, K), dtype=torch.float32, device=x.device)
+    ok(_lib().gpu_rotate_rows_f32(prologue, _ptr(x), x.stride(0), up_offset, 0, 0.0, _ptr(out), M, K, _stream()),
+       "gpu_rotate_rows_f32")
+    return out
+
+
+def sd_quant_rows(x: torch.Tensor, rotate: int = 0):
+    """gpu_sd_quant_rows: fp16 rows (activations, or weights at load) -> (q int8, scales f32)."""
+    _cuda(x)
+    M, K = x.shape
+    q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    s = torch.empty((M,), dtype=torch.float32, device=x.device)
+    ok(_lib().gpu_sd_quant_rows(_ptr(x), x.stride(0), _ptr(q), _ptr(s), M, K, rotate, _stream()), "gpu_sd_quant_rows")
+    return q, s
+
+
+def convrot_requant(x: torch.Tensor, seed: int = 0):
+    _cuda(x)
+    N, K = x.shape
+    q = torch.empty((N, K), dtype=torch.int8, device=x.device)
+    s = torch.empty((N,), dtype=torch.float32, device=x.device)
+    ok(_lib().gpu_convrot_requant(_DT[x.dtype], _ptr(x), _ptr(q), _ptr(s), N, K, seed, _stream()), "gpu_convrot_requant")
+    return q, s
+
+
+def convrot_dequant(q: torch.Tensor, s: torch.Tensor, dtype=torch.float32):
+    N, K = q.shape
+    out = torch.empty((N, K), dtype=dtype, device=q.device)
+    ok(_lib().gpu_convrot_dequant(_DT[dtype], _ptr(q), _ptr(s), _ptr(out), N, K, _stream()), "gpu_convrot_dequant")
+    return out
+
+
+def dequant_i8(q: torch.Tensor, s: torch.Tensor):
+    N, K = q.shape
+    out = torch.empty((N, K), dtype=torch.float32, device=q.device)
+    ok(_lib().gpu_dequant_i8(_ptr(q), _ptr(s), _ptr(out), N, K, _stream()), "gpu_dequant_i8")
+    return out
+
+
+def embed_dequant(q: torch.Tensor, s: torch.Tensor, rotate: int = 1):
+    M, K = q.shape
+    out = torch.empty((M, K), dtype=torch.float32, device=q.device)
+    ok(_lib().gpu_embed_dequant(_ptr(q), _ptr(s), _ptr(out), M, K, rotate, _stream()), "gpu_embed_dequant")
+    return out
+
+
+def w6_decode(packed: torch.Tensor, s_rel: torch.Tensor, K: int, G: int = 32):
+    N = packed.shape[0]
+    out = torch.empty((N, K), dtype=torch.int8, device=packed.device)
+    ok(_lib().gpu_w6_decode(_ptr(packed), _ptr(s_rel), _ptr(out), N, K, G, _stream()), "gpu_w6_decode")
+    return out
+
+
+def int8_gemm(A, W, xs, ws, bias=None, *, out_dtype=torch.bfloat16, act: int = 0, rscale=None, resid=None, out=None):
+    """gpu_int8_gemm / gpu_int8_gemm_act / gpu_int8_gemm_residual, chosen by the arguments given."""
+    _cuda(A)
+    M, K = A.shape
+    N = W.shape[0]
+    D = out if out is not None else torch.empty((M, N), dtype=out_dtype, device=A.device)
+    lib = _lib()
+    if resid is not None:
+        ok(lib.gpu_int8_gemm_residual(_ptr(A), _ptr(W), _ptr(xs), _ptr(ws), _ptr(bias), _ptr(rscale), _ptr(resid), _ptr(D),
+                                      M, N, K, _DT[D.dtype], _stream()), "gpu_int8_gemm_residual")
+    elif act:
+        ok(lib.gpu_int8_gemm_act(_ptr(A), _ptr(W), _ptr(xs), _ptr(ws), _ptr(bias), _ptr(D), M, N, K, _DT[D.dtype], act,
+                                 _stream()), "gpu_int8_gemm_act")
+    else:
+        ok(lib.gpu_int8_gemm(_ptr(A), _ptr(W), _ptr(xs), _ptr(ws), _ptr(bias), _ptr(D), M, N, K, _DT[D.dtype], _stream()),
+           "gpu_int8_gemm")
+    return D
+
+
+def int8_gemm_acc_i32(A, W):
+    M, K = A.shape
+    N = W.shape[0]
+    D = torch.empty((M, N), dtype=torch.int32, device=A.device)
+    ok(_lib().gpu_int8_gemm_acc_i32(_ptr(A), _ptr(W), _ptr(D), M, N, K, _stream()), "gpu_int8_gemm_acc_i32")
+    return D
+
+
+def kernel_status() -> int:
+    """Device status word (0 = every kernel completed its waits); synchronises the device and clears the word."""
+    import ctypes as C
+    v = C.c_int(0)
+    ok(_lib().gpu_kernels_status(C.byref(v)), "gpu_kernels_status")
+    return v.value
+
+
+@dataclass
+class QuantLinear:
+    """An int8 linear as the reference's DiT blocks hold it: weight int8 [N, K] (already rotated when `rotate`),
+    per-output-channel scales f32 [N], optional bias in the activation dtype."""
+    weight: torch.Tensor
+    scale: torch.Tensor
+    bias: Optional[torch.Tensor] = None
+    rotate: int = 0
+
+    @staticmethod
+    def from_float(w: torch.Tensor, bias=None, rotate: int = 0) -> "QuantLinear":
+        """Quantize-at-load: fp16 weights through gpu_sd_quant_rows (src/unet.rs:367-383), f32/bf16 weights through
+        gpu_convrot_requant with seed 0 (src/moss.rs:88-94; always R256)."""
+        if w.dtype == torch.float16:
+            q, s = sd_quant_rows(w.contiguous(), rotate)
+        else:
+            if rotate not in (1, 256):
+                raise ValueError("f32/bf16 weights are packed by gpu_convrot_requant, which always rotates (R256)")
+            q, s = convrot_requant(w.contiguous(), 0)
+        return QuantLinear(q, s, bias, rotate)
+
+    def forward(self, x: torch.Tensor, *, prologue: int = ffi.PRO_PLAIN, act: int = 0, rscale=None, resid=None,
+                out=None) -> torch.Tensor:
+        if x.dtype == torch.float16:
+            a8, xs = sd_quant_rows(x, self.rotate)
+        else:
+            a8, xs = quant_rows(x, prologue, 1 if self.rotate else 0)
+        return int8_gemm(a8, self.weight, xs, self.scale, self.bias, out_dtype=x.dtype, act=act, rscale=rscale,
+                         resid=resid, out=out)

@@ -1,0 +1,116 @@
+/* C ABI of libgpu_kernels.so: the quantized-linear path of BetaDoggo/comfyui-backend-but-rust for sm_100a.
+ *
+ * Every function keeps the name, argument order and meaning of the symbol the reference's Rust side declares in
+ * src/ffi.rs and its CUDA side defines (cited per function as file:line inside the reference project), so the
+ * Rust code links against this library unchanged for these calls.
+ *
+ * Conventions (reference: csrc/common.cuh:12,15,128; src/ffi.rs:336-355):
+ *   - return 0 on success; a negative launcher code on a rejected argument; a positive cudaError_t otherwise
+ *   - every pointer is a DEVICE pointer owned by the caller unless stated; nothing is allocated for the caller
+ *   - `stream` is a cudaStream_t; calls only enqueue work on it and never synchronise
+ *   - dtype / out_dt codes: 0 = f32, 1 = f16, 2 = bf16
+ *   - no C++ exception crosses this boundary; nothing is printed
+ */
+#ifndef GPU_KERNELS_H
+#define GPU_KERNELS_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { GPU_DT_F32 = 0, GPU_DT_F16 = 1, GPU_DT_BF16 = 2 }; /* src/ffi.rs:11-13 */
+
+/* quantizer prologues, src/ffi.rs:15-29 */
+enum {
+    GPU_PRO_PLAIN = 0, GPU_PRO_RMS = 1, GPU_PRO_GATE = 2, GPU_PRO_SWIGLU = 3, GPU_PRO_LAYERNORM = 4, GPU_PRO_SILU = 5,
+    GPU_PRO_GELU = 6, GPU_PRO_ADALN = 7, GPU_PRO_SITU = 8, GPU_PRO_LN_MOD = 9, GPU_PRO_LN_AFFINE = 10,
+    GPU_PRO_GELU_TANH = 11, GPU_PRO_LN_AFFINE_SILU = 12, GPU_PRO_SITU_FAST = 13
+};
+
+/* ---- kernel 1: activation quantizer ------------------------------------------------------------------- */
+
+/* Row prologue -> optional ConvRot rotation (R256 per 256-wide group when rotate != 0) -> per-row absmax int8.
+ * x [M, x_stride] bf16 or f32, rows 16-byte aligned; q int8 [M, K]; scales f32 [M].
+ * Errors: -1 K % 256 != 0, -2 K > 32768, -3 prologue not available, -4 dtype.
+ * Replaces csrc/kernels.cu:271-298 (declared at src/ffi.rs:74). */
+int gpu_quant_rows(int dtype, int prologue, const void* x, int64_t x_stride, const void* g, int64_t g_stride,
+                   int64_t up_offset, const float* norm_w, float eps, const void* mod_scale, const void* mod_shift,
+                   int8_t* q, float* scales, int M, int K, int rotate, void* stream);
+
+/* Prologue + rotation, rotated rows written as f32 [M, K] (weight-only int8 layers' activation side).
+ * Replaces csrc/kernels.cu:316-327 (src/ffi.rs:35). */
+int gpu_rotate_rows_f32(int prologue, const float* x, int64_t x_stride, int64_t up_offset, const float* norm_w, float eps,
+                        float* out, int M, int K, void* stream);
+
+/* fp16 rows (SD/SDXL activations, and fp16 weights at load) -> rotate 0 | 64 | 256 -> int8 + f32 row scale.
+ * Errors: -1 bad rotate. Replaces csrc/sd.cu:599-606 (src/ffi.rs:246). */
+int gpu_sd_quant_rows(const void* x, int64_t x_stride, int8_t* q, float* scales, int M, int K, int rotate, void* stream);
+
+/* ---- kernels 2 + 3: int8 GEMM mainloop with the fused dequant epilogue -------------------------------- */
+
+/* D[M,N] = out( (A[M,K] . W[N,K]^T) * xs[m] * ws[n] + bias[n] ).  A, W int8 row-major (K contiguous), 16-byte
+ * aligned, K % 16 == 0; xs f32 [M]; ws f32 [N]; bias [N] in the OUTPUT dtype or NULL; D [M,N] row-major.
+ * M == 0, N == 0 or K == 0 succeed without work. Errors: -200 bad out_dt, -202 alignment, -203 descriptor.
+ * Replaces csrc/gemm.cu:123-129 over csrc/vendor/cutlass_gemm_int8.cu:373-388 (src/ffi.rs:38). */
+int gpu_int8_gemm(const int8_t* A, const int8_t* W, const float* xs, const float* ws, const void* bias, void* D,
+                  int64_t M, int64_t N, int64_t K, int out_dt, void* stream);
+
+/* D = out( resid[m,n] + rscale[n] * out( acc * xs[m] * ws[n] + bias[n] ) ); rscale [N] and resid [M,N] in the
+ * output dtype, both required (-201 when NULL, or when K == 0); D may alias resid.
+ * Replaces csrc/gemm.cu:131-140 over csrc/vendor/cutlass_gemm_int8.cu:348-371 (src/ffi.rs:39). */
+int gpu_int8_gemm_residual(const int8_t* A, const int8_t* W, const float* xs, const float* ws, const void* bias,
+                           const void* rscale, const void* resid, void* D, int64_t M, int64_t N, int64_t K, int out_dt,
+                           void* stream);
+
+/* New (the reference applies the activation in the NEXT quantizer's prologue, csrc/kernels.cu:121-130):
+ * D = out( act( out( acc * xs[m] * ws[n] + bias[n] ) ) ), act 0 none, 1 gelu-tanh, 2 silu, 3 gelu-erf, so that
+ * "this call, then a PLAIN quantizer" equals "gpu_int8_gemm, then the quantizer with that prologue". -204 bad act. */
+int gpu_int8_gemm_act(const int8_t* A, const int8_t* W, const float* xs, const float* ws, const void* bias, void* D,
+                      int64_t M, int64_t N, int64_t K, int out_dt, int act, void* stream);
+
+/* New, for tests: the raw int32 accumulators D[m,n] = sum_k A[m,k] * W[n,k] that the fused forms never expose. */
+int gpu_int8_gemm_acc_i32(const int8_t* A, const int8_t* W, int32_t* D, int64_t M, int64_t N, int64_t K, void* stream);
+
+/* W6A8: q [N, 3K/4] u8 (per row K/2 nibble bytes then K/4 bytes of top bits), s_rel [N, K/G] fp8-e4m3 ->
+ * out int8 [N, K] = clamp(rint((code - 32) * s_rel), +-127). -1 when K % 32 or G % 16.
+ * Replaces csrc/h3.cu:40-46 (src/ffi.rs:121). */
+int gpu_w6_decode(const void* q, const void* s_rel, void* out, int64_t N, int K, int G, void* stream);
+
+/* ---- kernel 4: quantize-at-load weight packers and their inverses ------------------------------------- */
+
+/* x [N, K] f32 or bf16 -> R256 -> q int8 [N, K] + s f32 [N]; seed 0 rounds to nearest even, any other seed rounds
+ * stochastically (PCG hash of element index + seed). -1 K % 256, -4 dtype.
+ * Replaces csrc/kernels.cu:1409-1420 (src/ffi.rs:119). */
+int gpu_convrot_requant(int dtype, const void* x, void* q, void* s, int64_t N, int K, uint64_t seed, void* stream);
+
+/* q int8 [N, K] (rotated), s [N] -> out [N, K] f32 or bf16 in the original basis.
+ * Replaces csrc/kernels.cu:1393-1405 (src/ffi.rs:118). */
+int gpu_convrot_dequant(int dtype, const void* q, const void* s, void* out, int64_t N, int K, void* stream);
+
+/* out[n, k] = q[n, k] * s[n] as f32; -1 when K % 4. Replaces csrc/kernels.cu:337-343 (src/ffi.rs:37). */
+int gpu_dequant_i8(const int8_t* q, const float* s, float* out, int64_t N, int64_t K, void* stream);
+
+/* int8 ConvRot embedding rows -> f32 rows holding bf16 values; -1 unless rotate.
+ * Replaces csrc/kernels.cu:633-638 (src/ffi.rs:82). */
+int gpu_embed_dequant(const int8_t* q, const float* s, float* out, int M, int K, int rotate, void* stream);
+
+/* Windows video-memory budget query the Rust side imports unconditionally (src/cuda.rs:136-153; the reference
+ * defines it in csrc/wddm.cu). HOST pointers. Always returns non-zero here: no budget is known. */
+int gpu_wddm_budget(uint64_t* budget, uint64_t* usage);
+
+/* ---- library housekeeping (new) ------------------------------------------------------------------------ */
+
+/* Reads and clears the device status word of the current device (synchronises it). *status (HOST pointer) is 0
+ * unless a kernel gave up one of its bounded waits (1-5: which wait). */
+int gpu_kernels_status(int* status);
+
+/* Float forms of the GEMM epilogue: bit 0 computes (acc*xs)*ws + bias with one fused multiply-add, bit 1 does the
+ * same for y*rscale + resid. Process-wide; the default is the form that matches the reference build bit for bit. */
+void gpu_kernels_set_epilogue_contract(int bits);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GPU_KERNELS_H */
