@@ -6,32 +6,51 @@
 //
 // These are the entry points the reference exports from csrc/gemm.cu:123-140 over its CUTLASS 2.x
 // mma.sync kernels (csrc/vendor/cutlass_gemm_int8.cu); the rounding points are those of its epilogue
-// visitor trees (:84-95 plain, :143-161 residual).
+// visitor trees (:84-95 plain, :143-161 residual), with the two multiply-adds fused as nvcc fuses them there.
 //
-// One persistent CTA per SM, 192 threads:
-//   warp 0      TMA producer: 128-byte-swizzled int8 tiles of A [128 x 128] and W [BN x 128] into a ring of
-//               shared-memory stages (cp.async.bulk.tensor, no multicast), completion on mbarriers
-//   warp 1      allocates tensor memory; one thread issues tcgen05.mma kind::i8 (M=128, N=BN, K=32), four per
-//               stage, and commits each stage back to the producer and each finished tile to the epilogue
-//   warps 2-5   epilogue: tcgen05.ld the int32 accumulator (two TMEM buffers, so the epilogue of tile i runs
-//               under the mainloop of tile i+1), scale, bias, optional activation or residual, round, store
-// Every wait is bounded; a wait that runs out records a code in g_kernel_status and the CTA unwinds.
+// A cluster of two CTAs (two SMs) computes a 256 x bn tile with tcgen05.mma cta_group::2, kind::i8:
+//   - each CTA stages its own 128 rows of A and its own bn/2 rows of W, 128 bytes of K per TMA box with the
+//     128-byte swizzle (cp.async.bulk.tensor, never multicast), in a ring of shared-memory stages of one or two
+//     boxes per operand; the byte counts of both CTAs are credited to the leader's "full" mbarrier
+//   - warp 1 of the leader CTA (cluster rank 0) issues the MMAs for both SMs (M = 256, N = bn, K = 32 each) into
+//     one of two tensor-memory accumulators; a commit releases a stage in both CTAs, another hands the finished
+//     accumulator to both epilogues
+//   - warps 2-9 of each CTA drain that CTA's 128 accumulator rows (two warps per TMEM lane quarter, splitting the
+//     32-column chunks), apply scales / bias / activation or residual, round, and write through shared memory with
+//     TMA stores (full-line writes; a direct-store path serves outputs that TMA cannot address)
+//   - the persistent grid walks the tiles round-robin; bn is chosen per shape so the last round is not mostly idle
+// Every wait is bounded; a wait that runs out records a code in g_kernel_status and the CTA pair unwinds.
 #include <atomic>
+#include <cmath>
+#include <cstdlib>
 #include <cuda.h>
 #include <mutex>
-#include <unordered_map>
+#include <type_traits>
 
 #include "common.cuh"
 
 __device__ int g_kernel_status = 0;
+#ifdef GEMM_PROFILE
+// debug build only: per-CTA cycle counts
+__device__ unsigned long long g_prof[160][8];
+#define PROF_T0() const long long prof_t0__ = clock64()
+#define PROF_ADD(slot) g_prof[blockIdx.x][slot] += (unsigned long long)(clock64() - prof_t0__)
+#else
+#define PROF_T0()
+#define PROF_ADD(slot)
+#endif
 
 namespace {
 
-constexpr int BM = 128;        // rows of A per tile = UMMA M = TMEM lanes
-constexpr int BK = 128;        // int8 elements (= bytes) of K per stage: one 128-byte swizzle row
+constexpr int BM = 128;        // rows of A per CTA = TMEM lanes
+constexpr int BK = 128;        // int8 elements (= bytes) of K per TMA box: one 128-byte swizzle row
 constexpr int UMMA_K = 32;     // K of one tcgen05.mma kind::i8
-constexpr int kThreads = 192;
-constexpr int kEpiThreads = 128;
+constexpr int kThreads = 320;  // warp 0 producer, warp 1 MMA, warps 2-9 epilogue
+constexpr int kEpiWarps = 8;
+constexpr int kMaxStages = 8;
+constexpr int kSmemBytes = 232448;            // the per-CTA maximum (227 KB)
+constexpr int kStagingBytes = kEpiWarps * 4096;  // per epilogue warp: 32 rows x 128 B of output staging
+constexpr int kTailBytes = 256;               // barriers, tensor-memory pointer, abort flag
 
 enum EpiMode { EPI_PLAIN = 0, EPI_RESID = 1, EPI_ACT = 2, EPI_ACC = 3 };
 enum Act { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_SILU = 2, ACT_GELU_ERF = 3 };
@@ -46,21 +65,18 @@ struct GemmParams {
     int M, N, K;
     int tiles_m, tiles_n, num_tiles, k_iters;
     int act;
-    int contract;        // bit 0: acc*xs*ws + bias ends in one fma; bit 1: y*rscale + resid is one fma
-    int vec_ok;          // rows of D (and resid) start 16-byte aligned and N % 8 == 0
+    int vec_ok;          // per-column vectors and rows of D / resid can be read and written 16 bytes at a time
+    int tma_store;       // D is written through shared memory with TMA stores
+    int bn;              // columns per tile (multiple of 32, <= 256); each CTA of the pair stages bn/2 rows of W
+    int stages;          // shared-memory ring depth
+    int ksub;            // 128-byte K boxes per stage (1 or 2): one barrier round trip per 4 or 8 MMAs
+    uint32_t idesc;      // instruction descriptor for M = 256, N = bn
+#ifdef GEMM_PROFILE
+    int dbg;             // debug build: bit 0 skips the TMA loads, bit 1 skips the MMAs
+#endif
 };
 
-template <int BN> struct Cfg {
-    static constexpr int kStages = BN == 256 ? 4 : 6;
-    static constexpr int kABytes = BM * BK;
-    static constexpr int kBBytes = BN * BK;
-    static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers; 512 or 256 columns
-    // tiles | barriers + tmem pointer + abort flag | 1024 B alignment slack
-    static constexpr int kSmemBytes = kStages * kStageBytes + 256 + 1024;
-};
-
-// Tile order: bands of 8 row tiles, column tile fastest-varying across the band's rows, so that the CTAs
+// Tile order: bands of 8 row tiles, column tile fastest-varying across the band's rows, so that the clusters
 // running at one time share a few A row-panels and W column-panels in L2.
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
     constexpr int GROUP_M = 8;
@@ -73,22 +89,18 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
     tn = r / gsize;
 }
 
-template <typename OutT> __device__ __forceinline__ void store8(OutT* p, const float (&y)[8]);
-template <> __device__ __forceinline__ void store8<float>(float* p, const float (&y)[8]) {
-    reinterpret_cast<float4*>(p)[0] = make_float4(y[0], y[1], y[2], y[3]);
-    reinterpret_cast<float4*>(p)[1] = make_float4(y[4], y[5], y[6], y[7]);
-}
-template <> __device__ __forceinline__ void store8<bf16>(bf16* p, const float (&y)[8]) {
+template <typename OutT> __device__ __forceinline__ uint4 pack8(const float (&y)[8]);
+template <> __device__ __forceinline__ uint4 pack8<bf16>(const float (&y)[8]) {
     __nv_bfloat162 h[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(y[2 * i], y[2 * i + 1]);
-    *reinterpret_cast<uint4*>(p) = *reinterpret_cast<uint4*>(h);
+    return *reinterpret_cast<uint4*>(h);
 }
-template <> __device__ __forceinline__ void store8<half>(half* p, const float (&y)[8]) {
+template <> __device__ __forceinline__ uint4 pack8<half>(const float (&y)[8]) {
     __half2 h[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(y[2 * i], y[2 * i + 1]);
-    *reinterpret_cast<uint4*>(p) = *reinterpret_cast<uint4*>(h);
+    return *reinterpret_cast<uint4*>(h);
 }
 template <typename OutT> __device__ __forceinline__ void load8(const OutT* p, float (&y)[8]);
 template <> __device__ __forceinline__ void load8<float>(const float* p, float (&y)[8]) {
@@ -114,27 +126,163 @@ template <> __device__ __forceinline__ void load8<half>(const half* p, float (&y
     }
 }
 
-template <int BN, typename OutT, int EPI>
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) {
-    using C = Cfg<BN>;
-    constexpr int S = C::kStages;
+// The epilogue arithmetic on 8 consecutive columns of one row (accumulators r[0..7] -> y[0..7], not yet rounded
+// to the output type for the last step; the store rounds).
+//   t0 = float(acc) * xs;  v = out(fma(t0, ws, bias));  RESID: fma(v, rscale, resid);  ACT: act(v)
+template <typename OutT, int EPI>
+__device__ __forceinline__ void epilogue8(const GemmParams& p, const uint32_t* r, int row, int col, float xs_r, bool vec,
+                                          float (&y)[8]) {
+    float w8[8], b8[8], rs8[8], rr[8];
+    const OutT* rsd = reinterpret_cast<const OutT*>(p.resid) + (int64_t)row * p.N + col;
+    if (vec) {
+        // every lane reads the same addresses of the per-column vectors: one broadcast per load
+        load8<float>(p.ws + col, w8);
+        if (p.bias) load8<OutT>(reinterpret_cast<const OutT*>(p.bias) + col, b8);
+        if (EPI == EPI_RESID) {
+            load8<OutT>(reinterpret_cast<const OutT*>(p.rscale) + col, rs8);
+            load8<OutT>(rsd, rr);
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int n = col + e;
+            const bool in = n < p.N;
+            w8[e] = in ? p.ws[n] : 0.f;
+            if (p.bias) b8[e] = in ? to_f<OutT>(reinterpret_cast<const OutT*>(p.bias)[n]) : 0.f;
+            if (EPI == EPI_RESID) {
+                rs8[e] = in ? to_f<OutT>(reinterpret_cast<const OutT*>(p.rscale)[n]) : 0.f;
+                rr[e] = in ? to_f<OutT>(rsd[e]) : 0.f;
+            }
+        }
+    }
+    if (!p.bias) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) b8[e] = 0.f;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const float t0 = __fmul_rn(__int2float_rn((int)r[e]), xs_r);
+        float v = rnd<OutT>(__fmaf_rn(t0, w8[e], b8[e]));
+        if (EPI == EPI_RESID) v = __fmaf_rn(v, rs8[e], rr[e]);
+        else if (EPI == EPI_ACT) v = p.act == ACT_GELU_TANH ? gelu_tanh_f(v) : p.act == ACT_SILU ? silu_f(v) : gelu_f(v);
+        y[e] = v;
+    }
+}
+
+// One 32-column chunk of one accumulator row, written straight to global memory (the path for outputs whose row
+// pitch or base TMA cannot address, and for ragged N).
+template <typename OutT, int EPI>
+__device__ __forceinline__ void chunk_direct(const GemmParams& p, const uint32_t (&r)[32], int row, int col0, float xs_r) {
+    if (EPI == EPI_ACC) {
+        int32_t* d = reinterpret_cast<int32_t*>(p.D) + (int64_t)row * p.N + col0;
+        if (p.vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) *reinterpret_cast<uint4*>(d + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) d[j] = (int32_t)r[j];
+        }
+        return;
+    }
+    OutT* d = reinterpret_cast<OutT*>(p.D) + (int64_t)row * p.N + col0;
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+        if (col0 + j >= p.N) break;
+        const bool vec = p.vec_ok && col0 + j + 8 <= p.N;
+        float y[8];
+        epilogue8<OutT, EPI>(p, r + j, row, col0 + j, xs_r, vec, y);
+        if (vec) {
+            if constexpr (sizeof(OutT) == 2) {
+                *reinterpret_cast<uint4*>(d + j) = pack8<OutT>(y);
+            } else {
+                reinterpret_cast<float4*>(d + j)[0] = make_float4(y[0], y[1], y[2], y[3]);
+                reinterpret_cast<float4*>(d + j)[1] = make_float4(y[4], y[5], y[6], y[7]);
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                if (col0 + j + e < p.N) d[j + e] = from_f<OutT>(y[e]);
+        }
+    }
+}
+
+// One 32-column chunk of the warp's 32 rows, staged in shared memory in the layout a TMA store with the 64-byte
+// (2-byte outputs) or 128-byte (4-byte outputs) swizzle expects: row r at r * pitch, its 16-byte piece j at
+// piece j ^ f(r). Eight consecutive lanes then hit eight different bank groups.
+template <typename OutT, int EPI>
+__device__ __forceinline__ void chunk_to_smem(const GemmParams& p, const uint32_t (&r)[32], int row, int col0, float xs_r,
+                                              uint8_t* stage, int lane) {
+    constexpr int kEsz = EPI == EPI_ACC ? 4 : (int)sizeof(OutT);
+    if constexpr (kEsz == 2) {
+        uint8_t* rowp = stage + lane * 64;
+        const int sw = (lane >> 1) & 3;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float y[8];
+            epilogue8<OutT, EPI>(p, r + 8 * j, row, col0 + 8 * j, xs_r, p.vec_ok && col0 + 8 * j + 8 <= p.N, y);
+            *reinterpret_cast<uint4*>(rowp + ((j ^ sw) << 4)) = pack8<OutT>(y);
+        }
+    } else {
+        uint8_t* rowp = stage + lane * 128;
+        const int sw = lane & 7;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float y[8];
+            if (EPI == EPI_ACC) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) y[e] = __uint_as_float(r[8 * j + e]);  // raw int32 bits
+            } else {
+                epilogue8<OutT, EPI>(p, r + 8 * j, row, col0 + 8 * j, xs_r, p.vec_ok && col0 + 8 * j + 8 <= p.N, y);
+            }
+            *reinterpret_cast<float4*>(rowp + (((2 * j) ^ sw) << 4)) = make_float4(y[0], y[1], y[2], y[3]);
+            *reinterpret_cast<float4*>(rowp + (((2 * j + 1) ^ sw) << 4)) = make_float4(y[4], y[5], y[6], y[7]);
+        }
+    }
+}
+
+// 2-D tiled TMA store, shared memory -> global; rows and columns beyond the tensor are clipped.
+__device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(tmap), "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+template <typename OutT, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                    const __grid_constant__ CUtensorMap tmap_d, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
-    // 128-byte-swizzled operand tiles need a 1024-byte aligned base
     const uint32_t raw_addr = smem_u32(smem_raw);
-    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;   // same offset in both CTAs of the pair
     uint8_t* sm = smem_raw + (base - raw_addr);
-    const uint32_t sA = base;                          // S x [128 x 128]
-    const uint32_t sB = base + S * C::kABytes;         // S x [BN x 128]
-    uint8_t* tail = sm + S * C::kStageBytes;
-    const uint32_t bar_full = smem_u32(tail);             // S barriers
-    const uint32_t bar_empty = bar_full + 8 * S;          // S
-    const uint32_t bar_tfull = bar_empty + 8 * S;         // 2
-    const uint32_t bar_tempty = bar_tfull + 16;           // 2
-    uint32_t* tmem_ptr_s = reinterpret_cast<uint32_t*>(tail + 8 * (2 * S + 4));
+    const int S = p.stages;
+    const int BN = p.bn;
+    const int KS = p.ksub;
+    const uint32_t a_bytes = BM * BK;                     // one 128-byte K box of this CTA's A rows
+    const uint32_t b_bytes = (uint32_t)(BN / 2) * BK;     // ... and of this CTA's half of the W tile
+    const uint32_t stage_bytes = KS * (a_bytes + b_bytes);
+    uint8_t* staging = sm;                                 // kEpiWarps x 4 KB of output staging
+    const uint32_t sA = base + kStagingBytes;              // S x KS x [128 x 128]
+    const uint32_t sB = sA + S * KS * a_bytes;             // S x KS x [bn/2 x 128]
+    uint8_t* tail = sm + kStagingBytes + S * stage_bytes;
+    const uint32_t bar_full = smem_u32(tail);              // kMaxStages barriers (the leader's are used)
+    const uint32_t bar_empty = bar_full + 8 * kMaxStages;  // kMaxStages, one set per CTA
+    const uint32_t bar_tfull = bar_empty + 8 * kMaxStages; // 2, per CTA
+    const uint32_t bar_tempty = bar_tfull + 16;            // 2 (the leader's are used)
+    uint32_t* tmem_ptr_s = reinterpret_cast<uint32_t*>(tail + 8 * (2 * kMaxStages + 4));
     volatile int* abort_s = reinterpret_cast<volatile int*>(tmem_ptr_s + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int nclusters = gridDim.x >> 1, cluster_id = blockIdx.x >> 1;
+    PROF_T0();
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < S; ++i) {
@@ -143,175 +291,188 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar_tfull + 8 * i, 1);
-            mbar_init(bar_tempty + 8 * i, kEpiThreads);
+            mbar_init(bar_tempty + 8 * i, 2 * kEpiWarps);
         }
         *abort_s = 0;
         fence_mbar_init();
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_w);
+        if (p.tma_store) prefetch_tmap(&tmap_d);
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_ptr_s), C::kTmemCols);
-        tmem_relinquish();
+        tmem_alloc_pair(smem_u32(tmem_ptr_s), 512);
+        tmem_relinquish_pair();
     }
     tc_fence_before();
     __syncthreads();
+    cluster_sync_all();   // the peer's barriers exist before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr_s;
 
     if (warp == 0) {
-        // ---------------- TMA producer ----------------
+        // ---------------- TMA producer (both CTAs) ----------------
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+            for (int t = cluster_id; t < p.num_tiles && ok; t += nclusters) {
                 int tm, tn;
                 tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+                const int row_a = tm * (2 * BM) + (int)rank * BM;
+                const int row_w = tn * BN + (int)rank * (BN / 2);
                 for (int kb = 0; kb < p.k_iters; ++kb) {
                     if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_s, ST_TIMEOUT_EMPTY)) { ok = false; break; }
-                    const uint32_t full = bar_full + 8 * stage;
-                    mbar_arrive_expect_tx(full, C::kStageBytes);
-                    tma_load_2d(sA + stage * C::kABytes, &tmap_a, kb * BK, tm * BM, full);
-                    tma_load_2d(sB + stage * C::kBBytes, &tmap_w, kb * BK, tn * BN, full);
+#ifdef GEMM_PROFILE
+                    if (p.dbg & 1) {
+                        if (!leader) { ok = false; break; }
+                        mbar_arrive(bar_full + 8 * stage);
+                        if (++stage == S) { stage = 0; phase ^= 1u; }
+                        continue;
+                    }
+#endif
+                    if (leader) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * stage_bytes);
+                    const uint32_t full = mapa_shared(bar_full + 8 * stage, 0);
+                    for (int ks = 0; ks < KS; ++ks) {
+                        tma_load_2d_pair(sA + (stage * KS + ks) * a_bytes, &tmap_a, (kb * KS + ks) * BK, row_a, full);
+                        tma_load_2d_pair(sB + (stage * KS + ks) * b_bytes, &tmap_w, (kb * KS + ks) * BK, row_w, full);
+                    }
                     if (++stage == S) { stage = 0; phase ^= 1u; }
                 }
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_i8(BM, BN);
+        // ---------------- MMA issuer (leader CTA) ----------------
+        // One thread feeds the tensor cores of both SMs. An MMA of this shape lasts 128 cycles and the tensor core
+        // queues only a few; a lone thread retires a dependent instruction every few cycles and a barrier
+        // operation costs it on the order of a hundred. The loop is therefore kept to a few dozen instructions per
+        // stage: descriptor low words advance by adds, nothing 64-bit, one commit (its arrival multicast to both
+        // CTAs), no fence between stages (TMA writes and MMA reads are async-proxy accesses ordered by the
+        // mbarrier itself), and stages of two K boxes halve the barrier traffic per MMA.
+        if (leader && lane == 0) {
+            const uint32_t a_lo0 = umma_desc_lo(sA), b_lo0 = umma_desc_lo(sB);
+            const uint32_t a_sub = a_bytes >> 4, b_sub = b_bytes >> 4;        // next K box of a stage
+            const uint32_t a_step = KS * a_sub, b_step = KS * b_sub;          // next stage
+            const uint32_t idesc = p.idesc;
             int stage = 0;
             uint32_t phase = 0;
+            uint32_t a_lo = a_lo0, b_lo = b_lo0, bar_f = bar_full, bar_e = bar_empty;
             int buf = 0;
             uint32_t tphase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+            for (int t = cluster_id; t < p.num_tiles && ok; t += nclusters) {
                 if (!mbar_wait(bar_tempty + 8 * buf, tphase ^ 1u, abort_s, ST_TIMEOUT_TMEM_EMPTY)) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * BN;
+                const uint32_t d_tmem = tmem_base + buf * 256;
                 for (int kb = 0; kb < p.k_iters; ++kb) {
-                    if (!mbar_wait(bar_full + 8 * stage, phase, abort_s, ST_TIMEOUT_FULL)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint64_t da = umma_desc_sw128(sA + stage * C::kABytes);
-                    const uint64_t db = umma_desc_sw128(sB + stage * C::kBBytes);
-#pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        // advancing the start address by 32 bytes inside the swizzle row selects the next K slice
-                        umma_i8(d_tmem, da + (uint64_t)(k * UMMA_K / 16), db + (uint64_t)(k * UMMA_K / 16), idesc,
-                                (kb | k) != 0);
+                    if (!mbar_try_wait(bar_f, phase)) {
+                        if (!mbar_wait(bar_f, phase, abort_s, ST_TIMEOUT_FULL)) { ok = false; break; }
                     }
-                    umma_commit(bar_empty + 8 * stage);  // stage is free once these MMAs have read it
-                    if (++stage == S) { stage = 0; phase ^= 1u; }
+#ifdef GEMM_PROFILE
+                    if (!(p.dbg & 2))
+#endif
+                    {
+                        umma_i8_pair_lo(d_tmem, a_lo, b_lo, idesc, kb);
+                        umma_i8_pair_lo(d_tmem, a_lo + 2, b_lo + 2, idesc, 1);   // +32 bytes inside the swizzle row
+                        umma_i8_pair_lo(d_tmem, a_lo + 4, b_lo + 4, idesc, 1);
+                        umma_i8_pair_lo(d_tmem, a_lo + 6, b_lo + 6, idesc, 1);
+                        if (KS == 2) {
+                            const uint32_t a2 = a_lo + a_sub, b2 = b_lo + b_sub;
+                            umma_i8_pair_lo(d_tmem, a2, b2, idesc, 1);
+                            umma_i8_pair_lo(d_tmem, a2 + 2, b2 + 2, idesc, 1);
+                            umma_i8_pair_lo(d_tmem, a2 + 4, b2 + 4, idesc, 1);
+                            umma_i8_pair_lo(d_tmem, a2 + 6, b2 + 6, idesc, 1);
+                        }
+                    }
+                    umma_commit_pair(bar_e);   // the stage is free in both CTAs once these MMAs have read it
+                    ++stage, a_lo += a_step, b_lo += b_step, bar_f += 8, bar_e += 8;
+                    if (stage == S) stage = 0, phase ^= 1u, a_lo = a_lo0, b_lo = b_lo0, bar_f = bar_full, bar_e = bar_empty;
                 }
                 if (!ok) break;
-                umma_commit(bar_tfull + 8 * buf);  // accumulator complete
+                umma_commit_pair(bar_tfull + 8 * buf);   // accumulator complete: both epilogues may drain it
                 buf ^= 1;
                 if (buf == 0) tphase ^= 1u;
             }
         }
     } else {
-        // ---------------- epilogue ----------------
-        const int quad = warp & 3;         // the TMEM lane quarter this warp may read
+        // ---------------- epilogue (both CTAs, 8 warps) ----------------
+        constexpr int kEsz = EPI == EPI_ACC ? 4 : (int)sizeof(OutT);
+        constexpr int kChunkBytes = 32 * 32 * kEsz;      // 2 KB or 4 KB of staging per chunk
+        constexpr int kBufs = 4096 / kChunkBytes;        // 2-byte outputs alternate between two staging buffers
+        const int ew = warp - 2;
+        const int quad = warp & 3;               // TMEM lane quarter this warp may read
+        const int half = ew >> 2;                // which half of the 32-column chunks
+        const int nchunks = BN / 32;
+        uint8_t* my_stage = staging + ew * 4096;
+        const uint32_t my_stage_u32 = smem_u32(my_stage);
         int buf = 0;
         uint32_t tphase = 0;
-        for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+        uint32_t nstore = 0;                     // TMA stores this warp has issued
+        for (int t = cluster_id; t < p.num_tiles; t += nclusters) {
             int tm, tn;
             tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
             const int n0 = tn * BN;
-            // the whole warp takes the same way out, so that the aligned TMEM loads below stay warp-wide
+            PROF_T0();
             const bool got = mbar_wait(bar_tfull + 8 * buf, tphase, abort_s, ST_TIMEOUT_TMEM_FULL);
             if (!__all_sync(0xffffffffu, got)) break;
+            if (threadIdx.x == 64) PROF_ADD(3);
             tc_fence_after();
-            const int row = tm * BM + quad * 32 + lane;
+            const int row0 = tm * (2 * BM) + (int)rank * BM + quad * 32;
+            const int row = row0 + lane;
             const bool row_ok = row < p.M;
-            const float xs_r = (EPI != EPI_ACC && row_ok) ? p.xs[row] : 0.f;
-            const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quad * 32) << 16);
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld32(taddr + c * 32, r);
-                tmem_ld_wait();
-                if (!row_ok) continue;
+            const int rrow = row_ok ? row : p.M - 1;     // rows past M compute on the last row; their output is clipped
+            const float xs_r = EPI != EPI_ACC ? p.xs[rrow] : 0.f;
+            const uint32_t taddr = tmem_base + buf * 256 + ((uint32_t)(quad * 32) << 16);
+            // two register sets: the load of the next chunk is in flight while this one is processed
+            uint32_t ra[32], rb[32];
+            auto emit = [&](const uint32_t (&r)[32], int c) {
                 const int col0 = n0 + c * 32;
-                if (EPI == EPI_ACC) {
-                    int32_t* d = reinterpret_cast<int32_t*>(p.D) + (int64_t)row * p.N + col0;
-                    if (p.vec_ok && col0 + 32 <= p.N) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            *reinterpret_cast<uint4*>(d + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < p.N) d[j] = (int32_t)r[j];
+                if (col0 >= p.N) return;
+                if (p.tma_store) {
+                    uint8_t* sb = my_stage + (nstore % kBufs) * kChunkBytes;
+                    // the store that last read this buffer must be done with it
+                    if (lane == 0) bulk_wait_read<kBufs - 1>();
+                    __syncwarp();
+                    chunk_to_smem<OutT, EPI>(p, r, rrow, col0, xs_r, sb, lane);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tmap_d, my_stage_u32 + (nstore % kBufs) * kChunkBytes, col0, row0);
+                        bulk_commit();
                     }
-                    continue;
+                    ++nstore;
+                } else if (row_ok) {
+                    chunk_direct<OutT, EPI>(p, r, row, col0, xs_r);
                 }
-                OutT* d = reinterpret_cast<OutT*>(p.D) + (int64_t)row * p.N + col0;
-                const OutT* rsd = reinterpret_cast<const OutT*>(p.resid) + (int64_t)row * p.N + col0;
-#pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                    if (col0 + j >= p.N) break;
-                    const bool vec = p.vec_ok && col0 + j + 8 <= p.N;
-                    // per-column vectors: every lane reads the same addresses (one broadcast per load)
-                    float w8[8], b8[8], rs8[8], rr[8];
-                    if (vec) {
-                        load8<float>(p.ws + col0 + j, w8);
-                        if (p.bias) load8<OutT>(reinterpret_cast<const OutT*>(p.bias) + col0 + j, b8);
-                        if (EPI == EPI_RESID) {
-                            load8<OutT>(reinterpret_cast<const OutT*>(p.rscale) + col0 + j, rs8);
-                            load8<OutT>(rsd + j, rr);
-                        }
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            const int n = col0 + j + e;
-                            const bool in = n < p.N;
-                            w8[e] = in ? p.ws[n] : 0.f;
-                            if (p.bias) b8[e] = in ? to_f<OutT>(reinterpret_cast<const OutT*>(p.bias)[n]) : 0.f;
-                            if (EPI == EPI_RESID) {
-                                rs8[e] = in ? to_f<OutT>(reinterpret_cast<const OutT*>(p.rscale)[n]) : 0.f;
-                                rr[e] = in ? to_f<OutT>(rsd[j + e]) : 0.f;
-                            }
-                        }
-                    }
-                    if (!p.bias) {
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) b8[e] = 0.f;
-                    }
-                    float y[8];
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        const float t0 = __fmul_rn(__int2float_rn((int)r[j + e]), xs_r);
-                        float v = (p.contract & 1) ? __fmaf_rn(t0, w8[e], b8[e]) : __fadd_rn(__fmul_rn(t0, w8[e]), b8[e]);
-                        v = rnd<OutT>(v);
-                        if (EPI == EPI_RESID) {
-                            v = (p.contract & 2) ? __fmaf_rn(v, rs8[e], rr[e]) : __fadd_rn(__fmul_rn(v, rs8[e]), rr[e]);
-                        } else if (EPI == EPI_ACT) {
-                            v = p.act == ACT_GELU_TANH ? gelu_tanh_f(v) : p.act == ACT_SILU ? silu_f(v) : gelu_f(v);
-                        }
-                        y[e] = v;
-                    }
-                    if (vec) store8<OutT>(d + j, y);
-                    else {
-#pragma unroll
-                        for (int e = 0; e < 8; ++e)
-                            if (col0 + j + e < p.N) d[j + e] = from_f<OutT>(y[e]);
-                    }
+            };
+            int c = half;
+            if (c < nchunks) tmem_ld32(taddr + c * 32, ra);
+#pragma unroll 1
+            for (; c < nchunks; c += 4) {
+                tmem_ld_wait();
+                if (c + 2 < nchunks) tmem_ld32(taddr + (c + 2) * 32, rb);
+                emit(ra, c);
+                if (c + 2 < nchunks) {
+                    tmem_ld_wait();
+                    if (c + 4 < nchunks) tmem_ld32(taddr + (c + 4) * 32, ra);
+                    emit(rb, c + 2);
                 }
             }
             tc_fence_before();
-            mbar_arrive(bar_tempty + 8 * buf);
+            __syncwarp();
+            if (threadIdx.x == 64) PROF_ADD(5);   // wait + drain of this tile
+            if (lane == 0) mbar_arrive_cluster(mapa_shared(bar_tempty + 8 * buf, 0));
             buf ^= 1;
             if (buf == 0) tphase ^= 1u;
         }
+        if (p.tma_store && lane == 0) bulk_wait_all();   // staged rows have left shared memory before the CTA exits
     }
 
     // ---------------- teardown ----------------
     __syncwarp();
     tc_fence_before();
     __syncthreads();
+    cluster_sync_all();   // nobody leaves while the peer may still signal its barriers or read its tiles
+    if (threadIdx.x == 0) PROF_ADD(4);
     if (*abort_s != 0) {
         // a wait ran out: leave time for copies and MMAs still in flight, then report
         for (int i = 0; i < 2000; ++i) __nanosleep(1000);
@@ -320,7 +481,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, C::kTmemCols);
+        tmem_dealloc_pair(tmem_base, 512);
     }
 }
 
@@ -345,7 +506,7 @@ EncodeTiledFn encode_fn() {
 
 // Tensor map of a row-major int8 matrix [rows, cols] (cols contiguous), box 128 bytes x box_rows, 128-byte swizzle.
 // Rows and columns beyond the matrix read as zero.
-bool make_tmap(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t cols, int box_rows) {
+bool make_operand_tmap(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t cols, int box_rows) {
     EncodeTiledFn enc = encode_fn();
     if (!enc) return false;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -356,57 +517,77 @@ bool make_tmap(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t cols, int
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
-
-struct DeviceInfo {
-    int sm_count = 0;
-};
-DeviceInfo& device_info(int dev) {
-    static DeviceInfo info[64];
-    static std::mutex mu;
-    std::lock_guard<std::mutex> lk(mu);
-    DeviceInfo& d = info[dev & 63];
-    if (d.sm_count == 0) cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
-    return d;
+// Tensor map of the output [M, N] for stores of 32 x 32-element boxes: 64-byte rows (64-byte swizzle) for 2-byte
+// elements, 128-byte rows (128-byte swizzle) for 4-byte elements.
+bool make_output_tmap(CUtensorMap* tm, void* ptr, int64_t M, int64_t N, int esz) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)(N * esz)};
+    const cuuint32_t box[2] = {32, 32};
+    const cuuint32_t estr[2] = {1, 1};
+    return enc(tm, esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, ptr, dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, esz == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-std::atomic<int> g_contract{0};
+int device_sm_count(int dev) {
+    static int count[64];
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lk(mu);
+    int& c = count[dev & 63];
+    if (c == 0) cudaDeviceGetAttribute(&c, cudaDevAttrMultiProcessorCount, dev);
+    return c;
+}
 
-template <int BN, typename OutT, int EPI>
-int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, int grid, cudaStream_t st) {
-    auto kern = gemm_i8_kernel<BN, OutT, EPI>;
+int env_int(const char* name, int dflt) {
+    const char* v = getenv(name);
+    return v && *v ? atoi(v) : dflt;
+}
+
+template <typename OutT, int EPI>
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& td, const GemmParams& p, int grid,
+                cudaStream_t st) {
+    auto kern = gemm_i8_pair_kernel<OutT, EPI>;
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     cudaGetDevice(&dev);
     const uint64_t bit = 1ull << (dev & 63);
     if (!(configured.load(std::memory_order_acquire) & bit)) {
-        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::kSmemBytes);
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return (int)e;
         configured.fetch_or(bit, std::memory_order_release);
     }
-    kern<<<grid, kThreads, Cfg<BN>::kSmemBytes, st>>>(ta, tw, p);
+    kern<<<grid, kThreads, kSmemBytes, st>>>(ta, tw, td, p);
     KCHECK();
     return 0;
 }
-
-template <int BN, typename OutT>
-int launch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, int grid, cudaStream_t st) {
+template <typename OutT>
+int launch_pair_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& td, const GemmParams& p,
+                    int grid, cudaStream_t st) {
     switch (epi) {
-        case EPI_PLAIN: return launch_gemm<BN, OutT, EPI_PLAIN>(ta, tw, p, grid, st);
-        case EPI_RESID: return launch_gemm<BN, OutT, EPI_RESID>(ta, tw, p, grid, st);
-        case EPI_ACT: return launch_gemm<BN, OutT, EPI_ACT>(ta, tw, p, grid, st);
+        case EPI_PLAIN: return launch_pair<OutT, EPI_PLAIN>(ta, tw, td, p, grid, st);
+        case EPI_RESID: return launch_pair<OutT, EPI_RESID>(ta, tw, td, p, grid, st);
+        case EPI_ACT: return launch_pair<OutT, EPI_ACT>(ta, tw, td, p, grid, st);
         default: return -200;
     }
 }
 
-// Chooses the column-tile width: 256 unless 128 loses fewer SM-slots to the last partial wave.
-int choose_bn(int64_t M, int64_t N, int sms) {
-    const int64_t tm = (M + BM - 1) / BM;
-    auto cost = [&](int bn, double per_tile) {
-        const double tiles = (double)(tm * ((N + bn - 1) / bn));
-        const double waves = tiles / sms;
-        return ceil(waves) * per_tile;  // time in units of one 128x256 tile
-    };
-    return cost(256, 1.0) <= cost(128, 0.54) ? 256 : 128;
+// Column-tile width: the candidate whose rounds x (width + fixed per-tile cost) is smallest, so that a shape
+// leaving the last round nearly empty at 256 takes a narrower tile instead.
+int choose_bn(int64_t M, int64_t N, int clusters) {
+    static const int forced = env_int("GPU_KERNELS_BN", 0);
+    if (forced >= 32 && forced <= 256 && forced % 32 == 0) return forced;
+    const int64_t tm = (M + 2 * BM - 1) / (2 * BM);
+    int best = 256;
+    int64_t best_cost = INT64_MAX;
+    for (int bn = 256; bn >= 64; bn -= 32) {
+        const int64_t tiles = tm * ((N + bn - 1) / bn);
+        const int64_t rounds = (tiles + clusters - 1) / clusters;
+        const int64_t cost = rounds * (bn + 32);
+        if (cost < best_cost) best_cost = cost, best = bn;
+    }
+    return best;
 }
 
 int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const float* ws, const void* bias,
@@ -421,32 +602,43 @@ int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const f
     if ((K % 16) != 0 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return -202;
     int dev = 0;
     cudaGetDevice(&dev);
-    const int sms = device_info(dev).sm_count;
-    const int bn = choose_bn(M, N, sms);
-    CUtensorMap ta, tw;
-    if (!make_tmap(&ta, A, M, K, BM) || !make_tmap(&tw, W, N, K, bn)) return -203;
+    const int clusters = device_sm_count(dev) / 2;
     GemmParams p{};
     p.xs = xs, p.ws = ws, p.bias = bias, p.rscale = rscale, p.resid = resid, p.D = D;
     p.M = (int)M, p.N = (int)N, p.K = (int)K;
-    p.tiles_m = (int)((M + BM - 1) / BM);
+    p.act = act;
+#ifdef GEMM_PROFILE
+    p.dbg = env_int("GEMM_DBG", 0);
+#endif
+    const int esz = epi == EPI_ACC ? 4 : (out_dt == DT_F32 ? 4 : 2);
+    auto al16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
+    p.vec_ok = (N % 8 == 0) && al16(D) && al16(ws) && al16(bias) && al16(rscale) && al16(resid);
+    static const int no_tma_store = env_int("GPU_KERNELS_DIRECT_STORE", 0);
+    p.tma_store = !no_tma_store && al16(D) && ((N * esz) % 16 == 0);
+    const int bn = choose_bn(M, N, clusters);
+    static const int ksub_env = env_int("GPU_KERNELS_KSUB", 2);
+    p.bn = bn;
+    p.idesc = umma_idesc_i8(2 * BM, bn);
+    p.ksub = (ksub_env == 1 || K <= BK) ? 1 : 2;
+    p.k_iters = (int)((K + p.ksub * BK - 1) / (p.ksub * BK));
+    const int stage_bytes = p.ksub * (BM * BK + (bn / 2) * BK);
+    const int stages = (kSmemBytes - 1024 - kTailBytes - kStagingBytes) / stage_bytes;
+    p.stages = stages > kMaxStages ? kMaxStages : stages;
+    p.tiles_m = (int)((M + 2 * BM - 1) / (2 * BM));
     p.tiles_n = (int)((N + bn - 1) / bn);
     p.num_tiles = p.tiles_m * p.tiles_n;
-    p.k_iters = (int)((K + BK - 1) / BK);
-    p.act = act;
-    p.contract = g_contract.load(std::memory_order_relaxed);
-    const int esz = epi == EPI_ACC ? 4 : (out_dt == DT_F32 ? 4 : 2);
-    const int per16 = 16 / esz;
-    auto al16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
-    p.vec_ok = (N % 8 == 0) && (N % per16 == 0) && al16(D) && al16(ws) && al16(bias) && al16(rscale) && al16(resid);
-    const int grid = p.num_tiles < sms ? p.num_tiles : sms;
-#define BN_DISPATCH(BN_)                                                                          \
-    if (epi == EPI_ACC) return launch_gemm<BN_, float, EPI_ACC>(ta, tw, p, grid, st);             \
-    if (out_dt == DT_F32) return launch_epi<BN_, float>(epi, ta, tw, p, grid, st);                \
-    if (out_dt == DT_F16) return launch_epi<BN_, half>(epi, ta, tw, p, grid, st);                 \
-    return launch_epi<BN_, bf16>(epi, ta, tw, p, grid, st);
-    if (bn == 256) { BN_DISPATCH(256) }
-    BN_DISPATCH(128)
-#undef BN_DISPATCH
+    CUtensorMap ta, tw, td;
+    if (!make_operand_tmap(&ta, A, M, K, BM) || !make_operand_tmap(&tw, W, N, K, bn / 2)) return -203;
+    if (p.tma_store) {
+        if (!make_output_tmap(&td, D, M, N, esz)) return -203;
+    } else {
+        td = ta;  // unused
+    }
+    const int grid = 2 * (p.num_tiles < clusters ? p.num_tiles : clusters);
+    if (epi == EPI_ACC) return launch_pair<float, EPI_ACC>(ta, tw, td, p, grid, st);
+    if (out_dt == DT_F32) return launch_pair_epi<float>(epi, ta, tw, td, p, grid, st);
+    if (out_dt == DT_F16) return launch_pair_epi<half>(epi, ta, tw, td, p, grid, st);
+    return launch_pair_epi<bf16>(epi, ta, tw, td, p, grid, st);
 }
 
 }  // namespace
@@ -479,9 +671,17 @@ GPU_API int gpu_int8_gemm_acc_i32(const int8_t* A, const int8_t* W, int32_t* D, 
     return run_gemm(EPI_ACC, A, W, nullptr, nullptr, nullptr, nullptr, nullptr, D, M, N, K, 0, 0, (cudaStream_t)stream);
 }
 
-// Which float forms the epilogue uses: bit 0 fuses (acc*xs)*ws + bias into one fma, bit 1 fuses y*rscale + resid.
-// The default matches the reference binary's epilogue as compiled by nvcc 12.9 for sm_100a.
-GPU_API void gpu_kernels_set_epilogue_contract(int bits) { g_contract.store(bits & 3); }
+#ifdef GEMM_PROFILE
+GPU_API int gpu_kernels_prof(unsigned long long* out, int clear) {
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_prof, sizeof(g_prof));
+    if (e != cudaSuccess) return (int)e;
+    if (clear) {
+        static unsigned long long z[160][8];
+        cudaMemcpyToSymbol(g_prof, z, sizeof(z));
+    }
+    return 0;
+}
+#endif
 
 // Reads and clears the device status word (synchronises the device). 0 = no kernel gave up a wait.
 GPU_API int gpu_kernels_status(int* status) {

@@ -37,9 +37,8 @@ SIGNATURES = {
     "gpu_embed_dequant": [P, P, P, i32, i32, i32, P],
     "gpu_wddm_budget": [C.POINTER(u64), C.POINTER(u64)],
     "gpu_kernels_status": [C.POINTER(i32)],
-    "gpu_kernels_set_epilogue_contract": [i32],
 }
-_VOID = {"gpu_kernels_set_epilogue_contract"}
+_VOID = set()
 
 
 def load(path: str = LIB_PATH) -> C.CDLL:

@@ -106,10 +106,6 @@ int gpu_wddm_budget(uint64_t* budget, uint64_t* usage);
  * unless a kernel gave up one of its bounded waits (1-5: which wait). */
 int gpu_kernels_status(int* status);
 
-/* Float forms of the GEMM epilogue: bit 0 computes (acc*xs)*ws + bias with one fused multiply-add, bit 1 does the
- * same for y*rscale + resid. Process-wide; the default is the form that matches the reference build bit for bit. */
-void gpu_kernels_set_epilogue_contract(int bits);
-
 #ifdef __cplusplus
 }
 #endif
