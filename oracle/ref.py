@@ -39,11 +39,11 @@ def _st():
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def quant_rows(x, prologue=0, rotate=0, *, K=None, g=None, up_offset=0):
+def quant_rows(x, prologue=0, rotate=0, *, K=None, g=None, up_offset=0, q=None, scales=None):
     M = x.shape[0]
     K = K if K is not None else x.shape[1]
-    q = torch.empty((M, K), dtype=torch.int8, device=x.device)
-    s = torch.empty((M,), dtype=torch.float32, device=x.device)
+    q = q if q is not None else torch.empty((M, K), dtype=torch.int8, device=x.device)
+    s = scales if scales is not None else torch.empty((M,), dtype=torch.float32, device=x.device)
     rc = lib().gpu_quant_rows(C.c_int(_DT[x.dtype]), C.c_int(prologue), _p(x), C.c_int64(x.stride(0)), _p(g),
                               C.c_int64(g.stride(0) if g is not None else 0), C.c_int64(up_offset), _p(None),
                               C.c_float(0.0), _p(None), _p(None), _p(q), _p(s), C.c_int(M), C.c_int(K), C.c_int(rotate),

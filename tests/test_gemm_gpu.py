@@ -1,0 +1,143 @@
+"""GPU parity of the int8 GEMM and its fused epilogues (through the C ABI). int32 accumulators are bit-exact against
+the CPU oracle; outputs are bit-exact against the oracle's fused-multiply-add form and against the reference's own
+CUTLASS kernel where it is built. Where a different float form or a host libm is on the other side, the tolerance
+is the path's stated one: one ulp of a 16-bit output (half an ulp of bf16 is a relative 4e-3), 1e-5 relative for f32."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from conftest import assert_bits_equal, assert_close_out
+
+pytestmark = pytest.mark.gpu
+
+
+def _operands(M, N, K, seed):
+    g = torch.Generator().manual_seed(seed)
+    A = torch.randint(-128, 128, (M, K), generator=g, dtype=torch.int8)
+    W = torch.randint(-128, 128, (N, K), generator=g, dtype=torch.int8)
+    xs = torch.rand(M, generator=g) * 0.05 + 1e-3
+    ws = torch.rand(N, generator=g) * 1e-3 + 1e-4
+    return g, A, W, xs, ws
+
+
+SHAPES = [(1, 8, 16), (1, 256, 256), (17, 40, 48), (127, 129, 144), (128, 256, 128), (129, 257 * 8, 272), (256, 512, 1024),
+          (300, 520, 1024), (154, 640, 2048), (513, 1000, 80), (260, 96, 4096), (2048, 640, 640)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_int32_accumulators_bit_exact(pkg, oracle, dev, M, N, K):
+    _, A, W, _, _ = _operands(M, N, K, M + N + K)
+    acc = pkg.linear.int8_gemm_acc_i32(A.to(dev), W.to(dev))
+    assert_bits_equal(acc, oracle.int8_gemm_acc(A, W), "accumulators")
+    assert pkg.linear.kernel_status() == 0
+
+
+def test_extreme_values_do_not_saturate(pkg, dev):
+    K = 8192
+    A = torch.full((130, K), -128, dtype=torch.int8, device=dev)
+    W = torch.full((72, K), -128, dtype=torch.int8, device=dev)
+    W[1] = 127
+    acc = pkg.linear.int8_gemm_acc_i32(A, W)
+    assert int(acc[0, 0]) == 128 * 128 * K and int(acc[5, 1]) == -128 * 127 * K
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(300, 520, 1024), (72, 88, 512), (640, 1284, 256)])
+def test_epilogues_against_the_oracle(pkg, oracle, dev, dtype, M, N, K):
+    g, A, W, xs, ws = _operands(M, N, K, 11)
+    bias = (torch.randn(N, generator=g) * 0.5).to(dtype)
+    rs = torch.randn(N, generator=g).to(dtype)
+    rr = torch.randn(M, N, generator=g).to(dtype)
+    acc = oracle.int8_gemm_acc(A, W)
+    d = lambda t: t.to(dev)
+    L = pkg.linear
+    got = L.int8_gemm(d(A), d(W), d(xs), d(ws), d(bias), out_dtype=dtype)
+    want = oracle.epilogue(acc, xs, ws, bias, out_dtype=dtype, contract=3)
+    assert_bits_equal(got, want, "plain")
+    got = L.int8_gemm(d(A), d(W), d(xs), d(ws), None, out_dtype=dtype)
+    assert_bits_equal(got, oracle.epilogue(acc, xs, ws, None, out_dtype=dtype, contract=3), "no bias")
+    resid = d(rr).clone()
+    got = L.int8_gemm(d(A), d(W), d(xs), d(ws), d(bias), out_dtype=dtype, rscale=d(rs), resid=resid, out=resid)  # D aliases resid
+    want = oracle.epilogue(acc, xs, ws, bias, rs, rr, out_dtype=dtype, contract=3)
+    assert_bits_equal(got, want, "residual, in place")
+    # the unfused float form differs by at most one ulp of the output type
+    loose = oracle.epilogue(acc, xs, ws, bias, out_dtype=dtype, contract=0)
+    assert_close_out(L.int8_gemm(d(A), d(W), d(xs), d(ws), d(bias), out_dtype=dtype), loose, "unfused form")
+    for act in (1, 2, 3):
+        got = L.int8_gemm(d(A), d(W), d(xs), d(ws), d(bias), out_dtype=dtype, act=act)
+        assert_close_out(got, oracle.epilogue(acc, xs, ws, bias, out_dtype=dtype, act=act, contract=7), f"act {act}", tiny=1e-3)
+    assert L.kernel_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_bit_exact_against_the_reference_gemm(pkg, ref, dev, dtype):
+    for (M, N, K) in [(300, 520, 1024), (1024, 3072, 768), (154, 640, 2048)]:
+        g, A, W, xs, ws = _operands(M, N, K, 21)
+        A, W, xs, ws = A.to(dev), W.to(dev), xs.to(dev), ws.to(dev)
+        bias = (torch.randn(N, generator=g) * 0.5).to(dtype).to(dev)
+        rs = torch.randn(N, generator=g).to(dtype).to(dev)
+        rr = torch.randn(M, N, generator=g).to(dtype).to(dev)
+        assert_bits_equal(pkg.linear.int8_gemm(A, W, xs, ws, bias, out_dtype=dtype),
+                          ref.int8_gemm(A, W, xs, ws, bias, out_dtype=dtype), f"plain {M}x{N}x{K}")
+        assert_bits_equal(pkg.linear.int8_gemm(A, W, xs, ws, bias, out_dtype=dtype, rscale=rs, resid=rr),
+                          ref.int8_gemm(A, W, xs, ws, bias, out_dtype=dtype, rscale=rs, resid=rr), f"residual {M}x{N}x{K}")
+
+
+@pytest.mark.parametrize("act,pro", [(1, 11), (2, 5), (3, 6)])
+def test_activation_epilogue_equals_the_reference_prologue_flow(pkg, ref, dev, act, pro):
+    """epilogue-activation then a PLAIN quantizer == the reference's plain GEMM then its quantizer with that prologue."""
+    g, A, W, xs, ws = _operands(256, 1024, 1024, 31)
+    A, W, xs, ws = A.to(dev), W.to(dev), (xs * 0.3).to(dev), ws.to(dev)
+    y = ref.int8_gemm(A, W, xs, ws, None)
+    q_ref, s_ref = ref.quant_rows(y, pro, 1)
+    ya = pkg.linear.int8_gemm(A, W, xs, ws, None, act=act)
+    q, s = pkg.linear.quant_rows(ya, 0, 1)
+    assert_bits_equal(q, q_ref, "codes")
+    assert_bits_equal(s, s_ref, "scales")
+
+
+def test_golden_vectors(pkg, dev, golden_inputs, golden_reference):
+    I = {k: v.to(dev) for k, v in golden_inputs.items()}
+    for name, dt in (("bf16", torch.bfloat16), ("f16", torch.float16), ("f32", torch.float32)):
+        got = pkg.linear.int8_gemm(I["A"], I["W"], I["xs"], I["ws"], I[f"bias_{name}"], out_dtype=dt)
+        assert_bits_equal(got, golden_reference[f"gemm_plain_{name}"], f"plain {name}")
+        got = pkg.linear.int8_gemm(I["A"], I["W"], I["xs"], I["ws"], None, out_dtype=dt)
+        assert_bits_equal(got, golden_reference[f"gemm_nobias_{name}"], f"nobias {name}")
+        got = pkg.linear.int8_gemm(I["A"], I["W"], I["xs"], I["ws"], I[f"bias_{name}"], out_dtype=dt,
+                                   rscale=I[f"rscale_{name}"], resid=I[f"resid_{name}"])
+        assert_bits_equal(got, golden_reference[f"gemm_resid_{name}"], f"resid {name}")
+
+
+def test_unaligned_output_takes_the_direct_store_path(pkg, oracle, dev):
+    g, A, W, xs, ws = _operands(200, 100, 256, 41)      # N * 2 bytes is not a multiple of 16: no TMA store
+    acc = oracle.int8_gemm_acc(A, W)
+    got = pkg.linear.int8_gemm(A.to(dev), W.to(dev), xs.to(dev), ws.to(dev), None)
+    assert_bits_equal(got, oracle.epilogue(acc, xs, ws, None, contract=3), "ragged N")
+    with pytest.raises(pkg.GpuKernelError, match="-202"):
+        pkg.linear.int8_gemm(A[:, :250].contiguous().to(dev), W[:, :250].contiguous().to(dev), xs.to(dev), ws.to(dev), None)
+
+
+def test_full_size_linearity_and_guard_bands(pkg, dev):
+    """Benchmark-size shape (M=4352, K=3072, N=12288): accumulators are linear in A, and nothing is written outside D."""
+    M, K, N = 4352, 3072, 12288
+    g = torch.Generator(device=dev).manual_seed(5)
+    A1 = torch.randint(-64, 64, (M, K), generator=g, dtype=torch.int8, device=dev)
+    A2 = torch.randint(-63, 64, (M, K), generator=g, dtype=torch.int8, device=dev)
+    W = torch.randint(-128, 128, (N, K), generator=g, dtype=torch.int8, device=dev)
+    L = pkg.linear
+    s = L.int8_gemm_acc_i32(A1, W)
+    s += L.int8_gemm_acc_i32(A2, W)
+    assert torch.equal(s, L.int8_gemm_acc_i32(A1 + A2, W))
+    rows = torch.randint(0, M, (64,), device=dev)
+    want = (A1[rows].double() @ W.double().T + A2[rows].double() @ W.double().T).to(torch.int32)
+    assert torch.equal(s[rows], want), "sampled rows against an fp64 product"
+    # canary bands around the output
+    pad = 4096
+    buf = torch.full((M * N + 2 * pad,), -7.0, dtype=torch.bfloat16, device=dev)
+    D = buf[pad:pad + M * N].view(M, N)
+    xs = torch.rand(M, device=dev) * 1e-2
+    ws = torch.rand(N, device=dev) * 1e-3
+    L.int8_gemm(A1, W, xs, ws, None, out=D)
+    assert bool((buf[:pad] == -7).all()) and bool((buf[-pad:] == -7).all())
+    assert L.kernel_status() == 0

@@ -1,0 +1,114 @@
+"""GPU parity of the quantize-at-load packers, their inverses, the fp16 (SD) row quantizer and the W6 decode."""
+from __future__ import annotations
+
+import importlib
+
+import pytest
+import torch
+
+from conftest import assert_bits_equal
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("M,K,rot", [(50, 640, 0), (50, 640, 64), (30, 1280, 256), (20, 2048, 256), (9, 5120, 0), (7, 77, 0),
+                                     (12, 320, 64), (3, 10240, 256), (1, 64, 64)])
+def test_sd_quant_rows(pkg, oracle, dev, M, K, rot):
+    g = torch.Generator().manual_seed(K + rot)
+    x = (torch.randn(M, K, generator=g) * 0.02).half()
+    x[0, 0] = 3.0                                     # an outlier
+    q, s = pkg.linear.sd_quant_rows(x.to(dev), rot)
+    qo, so = oracle.sd_quant_rows(x, rot)
+    assert_bits_equal(q, qo, "codes")
+    assert_bits_equal(s, so, "scales")
+
+
+def test_sd_quant_rows_tiny_scale_and_stride(pkg, oracle, dev):
+    x = torch.zeros(3, 256).half()
+    x[1] = 6e-8           # scale below half's range: the division stays in float (csrc/sd.cu:592-593)
+    x[2, 3] = 65504.0
+    q, s = pkg.linear.sd_quant_rows(x.to(dev), 0)
+    qo, so = oracle.sd_quant_rows(x, 0)
+    assert_bits_equal(q, qo, "codes")
+    assert_bits_equal(s, so, "scales")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("seed", [0, 12345, (7 << 32) + 99])
+def test_convrot_requant_and_dequant(pkg, oracle, dev, dtype, seed):
+    g = torch.Generator().manual_seed(9)
+    w = (torch.randn(48, 3072, generator=g) * 0.02).to(dtype)
+    q, s = pkg.linear.convrot_requant(w.to(dev), seed)
+    qo, so = oracle.convrot_requant(w, seed)
+    assert_bits_equal(q, qo, "codes")
+    assert_bits_equal(s, so, "scales")
+    back = pkg.linear.convrot_dequant(q, s, dtype)
+    assert_bits_equal(back, oracle.convrot_dequant(qo, so, dtype), "dequant")
+    assert_bits_equal(pkg.linear.dequant_i8(q, s), oracle.dequant_i8(qo, so), "dequant_i8")
+    assert_bits_equal(pkg.linear.embed_dequant(q, s), oracle.embed_dequant(qo, so), "embed_dequant")
+
+
+def test_packers_against_the_reference_kernels(pkg, ref, dev):
+    g = torch.Generator().manual_seed(10)
+    for K, rot in ((640, 64), (1280, 256), (2560, 0)):
+        x = (torch.randn(64, K, generator=g) * 0.02).half().to(dev)
+        q, s = pkg.linear.sd_quant_rows(x, rot)
+        qr, sr = ref.sd_quant_rows(x, rot)
+        assert_bits_equal(q, qr, f"sd codes K={K}")
+        assert_bits_equal(s, sr, f"sd scales K={K}")
+    for dtype in (torch.float32, torch.bfloat16):
+        w = (torch.randn(40, 12288, generator=g) * 0.02).to(dtype).to(dev)
+        for seed in (0, 4242):
+            q, s = pkg.linear.convrot_requant(w, seed)
+            qr, sr = ref.convrot_requant(w, seed)
+            assert_bits_equal(q, qr, "requant codes")
+            assert_bits_equal(s, sr, "requant scales")
+        assert_bits_equal(pkg.linear.convrot_dequant(q, s, dtype), ref.convrot_dequant(q, s, dtype), "dequant")
+    # a weight packed by the reference's own W6 packer decodes identically
+    w = (torch.randn(32, 2048, generator=g) * 0.015).bfloat16().to(dev)
+    packed, s_rel, _ = ref.w6_requant(w, 3)
+    assert_bits_equal(pkg.linear.w6_decode(packed, s_rel, 2048), ref.w6_decode(packed, s_rel, 2048), "w6 decode")
+
+
+def test_w6_decode(pkg, oracle, dev):
+    wl = importlib.import_module("cbr_b200.workloads")
+    g = torch.Generator().manual_seed(12)
+    codes = torch.randint(1, 64, (40, 1024), generator=g).to(torch.uint8)
+    packed = oracle.w6_pack_codes(codes)
+    s_rel = torch.randint(0x20, 0x50, (40, 32), generator=g).to(torch.uint8)   # e4m3 from 2^-3 to 8: some codes clamp
+    got = pkg.linear.w6_decode(packed.to(dev), s_rel.to(dev), 1024)
+    assert_bits_equal(got, oracle.w6_decode(packed, s_rel, 1024), "decode")
+    w = wl.weight(24, 5120, 2031, 0.015)
+    for fitted in (False, True):
+        packed, s_rel, _ = wl.w6_pack(w, fitted)
+        assert_bits_equal(pkg.linear.w6_decode(packed.to(dev), s_rel.to(dev), 5120), oracle.w6_decode(packed, s_rel, 5120),
+                          f"decode fitted={fitted}")
+
+
+def test_golden_vectors(pkg, dev, golden_inputs, golden_reference):
+    import make_golden
+    I, L = golden_inputs, pkg.linear
+    for rot in (0, 64):
+        q, s = L.sd_quant_rows(I["sd_x640"].to(dev), rot)
+        assert_bits_equal(q, golden_reference[f"sd640_rot{rot}_q"], "sd codes")
+        assert_bits_equal(s, golden_reference[f"sd640_rot{rot}_s"], "sd scales")
+    for name in ("w_f32", "w_bf16"):
+        for seed in (0, 12345):
+            q, s = L.convrot_requant(I[name].to(dev), seed)
+            assert_bits_equal(q, golden_reference[f"requant_{name}_seed{seed}_q"], f"requant {name} {seed}")
+            assert_bits_equal(s, golden_reference[f"requant_{name}_seed{seed}_s"], f"requant scales {name} {seed}")
+    got = L.w6_decode(make_golden.w6_pack_codes(I["w6_codes"]).to(dev), I["w6_srel"].to(dev), 512)
+    assert_bits_equal(got, golden_reference["w6_decode"], "w6 decode")
+
+
+def test_quantize_at_load_full_size_round_trip(pkg, dev):
+    """A benchmark-size weight (12288 x 3072): requant -> dequant returns the weight within half a step per rotated
+    coordinate, and packing the dequantized weight again reproduces the codes (idempotence)."""
+    wl = importlib.import_module("cbr_b200.workloads")
+    w = wl.weight(12288, 3072, 2011).to(dev)
+    q, s = pkg.linear.convrot_requant(w, 0)
+    back = pkg.linear.convrot_dequant(q, s, torch.float32)
+    err = (pkg.linear.rotate_rows_f32(back) - pkg.linear.rotate_rows_f32(w)).abs()
+    assert bool((err <= 0.5001 * s[:, None] + 1e-7).all())
+    q2, s2 = pkg.linear.convrot_requant(back, 0)
+    assert float((q2 != q).float().mean()) < 1e-4 and torch.allclose(s2, s, rtol=1e-5)
