@@ -186,6 +186,7 @@ def cpu_baseline(wl, rows: int):
     """The CPU oracle on the first `rows` rows of the batch (weights quantized once, outside the timed part)."""
     import torch
     from oracle import oracle as O
+    O.use_all_cores()
     up, down, x, w1, w2, b1, b2 = host_inputs(wl, 0)
     rows = min(rows, up.M)
     xr = x[:rows].contiguous()

@@ -7,13 +7,22 @@
 //   scale = max(min(amax, finite_max) * (1/127), 1e-30)      stored fp32
 //   q = clamp(rint(T(T(v) / T(scale))), -128, 127)            T = activation dtype (csrc/kernels.cu:241-255)
 //
-// Layout of the work: a 256-wide group belongs to 8 consecutive lanes; each lane holds four 8-element chunks
-// (16-byte loads) in registers. Of the eight index bits of an element inside its group, bits 0-2 are the position
-// in the chunk, bits 4 and 6 select the chunk, bits 3, 5 and 7 select the lane. Stage 0 (bits 0,1) runs inside a
-// lane; stages 1-3 each pair one register bit with one lane bit, so a lane sends two values to its partner
-// (one shuffle per element and stage) and computes the two butterfly outputs that it keeps. Every butterfly adds
-// in the reference's order, so the result is bit-identical whichever thread computes it. The row maximum goes
-// through shared memory once. No shared-memory staging of the row, no second pass over global memory.
+// The kernel is bound by instruction issue, not by HBM, so it is organised around instruction count:
+//   - a 256-wide group belongs to 8 consecutive lanes; a lane loads 32 consecutive elements (16-byte loads)
+//   - stages 0 and 1 (index bits 0-3) run in registers on packed f32x2 pairs (element i with element i+16)
+//   - the group is transposed through a padded per-warp shared-memory buffer; a lane then holds element pairs
+//     (2t, 2t+1) + 16 r, r = 0..15, and runs stages 2 and 3 (index bits 4-7) in registers, again on packed pairs
+//   - every butterfly adds in the reference's left-to-right order (a - b is fma(b, -1, a): one rounding, the same),
+//     so results are bit-identical whichever thread computes them
+//   - bf16 prologues of one variable (SiLU, GELU, GELU-tanh, the sigmoid of GATE) are a 65536-entry table built on
+//     the device from the very expressions of the reference and read through L1 (staging it in shared memory left
+//     room for too few warps and measured slower)
+//   - quantization rounds with cvt.rni and packs with saturation; the codes go back through shared memory so that
+//     each lane stores 32 contiguous bytes
+#include <atomic>
+#include <cstdlib>
+#include <mutex>
+
 #include "common.cuh"
 
 namespace {
@@ -21,6 +30,25 @@ namespace {
 enum { PRO_PLAIN = 0, PRO_RMS = 1, PRO_GATE = 2, PRO_SWIGLU = 3, PRO_LAYERNORM = 4, PRO_SILU = 5, PRO_GELU = 6,
        PRO_ADALN = 7, PRO_SITU = 8, PRO_LN_MOD = 9, PRO_LN_AFFINE = 10, PRO_GELU_TANH = 11, PRO_LN_AFFINE_SILU = 12,
        PRO_SITU_FAST = 13 };  // the reference's src/ffi.rs:15-29
+
+enum { LUT_SILU = 0, LUT_GELU = 1, LUT_GELU_TANH = 2, LUT_SIGMOID = 3, LUT_COUNT = 4 };
+
+// bf16 -> bf16 tables of the one-variable prologues: entry b = bf16(act(float(bf16 with bits b)))
+__device__ uint16_t g_act_lut[LUT_COUNT][65536];
+
+__global__ void build_lut_kernel(int which) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= 65536) return;
+    const float x = __uint_as_float((uint32_t)b << 16);
+    float y;
+    switch (which) {
+        case LUT_SILU: y = silu_f(x); break;
+        case LUT_GELU: y = gelu_f(x); break;
+        case LUT_GELU_TANH: y = gelu_tanh_f(x); break;
+        default: y = sigmoid_f(x); break;
+    }
+    g_act_lut[which][b] = __bfloat16_as_ushort(__float2bfloat16_rn(y));
+}
 
 struct QuantArgs {
     const void* x;
@@ -35,194 +63,277 @@ struct QuantArgs {
     int rotate;
     int tpr;            // threads per row = K / 32
     int rows_per_cta;
+    int nblocks;        // row blocks; CTAs stride over them
+    int lut;            // table index of the prologue (read through L1), or -1
 };
 
-template <typename T> __device__ __forceinline__ void load8(const T* p, float (&v)[8]);
-template <> __device__ __forceinline__ void load8<bf16>(const bf16* p, float (&v)[8]) {
-    const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
-    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        v[2 * i] = __uint_as_float(w[i] << 16);
-        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
-}
-template <> __device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
-    const float4 a = __ldg(reinterpret_cast<const float4*>(p));
-    const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
-    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
-}
+constexpr int kGroupWords = 304;   // 256 elements + 4 words of padding per 32, rounded so that groups sit 16 banks apart
+
+__device__ __forceinline__ int tpad(int e) { return e + ((e >> 5) << 2); }
 
 template <typename T> __device__ __forceinline__ float finite_max();
 template <> __device__ __forceinline__ float finite_max<float>() { return FLT_MAX; }
 template <> __device__ __forceinline__ float finite_max<bf16>() { return 3.38953139e38f; }
 
-// One radix-4 stage whose four inputs sit in two registers (a0, a1: register bit 0/1) of two lanes (lane bit
-// b = 0/1, partner = lane ^ LX). x0 = (reg 0, lane 0), x1 = (reg 1, lane 0), x2 = (reg 0, lane 1), x3 = (reg 1, lane 1).
-// Lane 0 keeps rows 0 and 1 of the block, lane 1 rows 2 and 3:
-//   row 0 = ((x0+x1)+x2)-x3   row 1 = ((x0+x1)-x2)+x3   row 2 = ((x0-x1)+x2)+x3   row 3 = ((-x0+x1)+x2)+x3
-// With T = X+Y: lane 0 has X=x0, Y=x1, U=x2, V=-x3 and lane 1 has X=x0, Y=-x1, U=x2, V=x3; then
-// (T+U)+V is row 0 or row 2, and (T-U)-V is row 1 or minus row 3 (negation commutes with rounding).
-template <int LX>
-__device__ __forceinline__ void mixed_stage(float& a0, float& a1, bool b, float half_lo, float half_hi) {
-    const float p0 = __shfl_xor_sync(0xffffffffu, a0, LX);
-    const float p1 = __shfl_xor_sync(0xffffffffu, a1, LX);
-    const float X = b ? p0 : a0;
-    const float Y = b ? -p1 : a1;
-    const float U = b ? a0 : p0;
-    const float V = b ? a1 : -p1;
-    const float Tt = __fadd_rn(X, Y);
-    a0 = __fmul_rn(half_lo, __fadd_rn(__fadd_rn(Tt, U), V));
-    a1 = __fmul_rn(half_hi, __fsub_rn(__fsub_rn(Tt, U), V));
-}
-
-// R256 of the group held by 8 lanes x v[4][8]. lane8 = lane index inside the group's 8 lanes.
-__device__ __forceinline__ void rotate256(float (&v)[4][8], int lane8) {
-    // stage 0: index bits 0,1 -- both inside a chunk
+// 32 consecutive elements -> floats (and, for bf16, their raw 16-bit patterns when a table prologue wants them)
+template <typename T> __device__ __forceinline__ void load32(const T* p, float (&v)[32]);
+template <> __device__ __forceinline__ void load32<bf16>(const bf16* p, float (&v)[32]) {
 #pragma unroll
-    for (int qd = 0; qd < 4; ++qd) {
+    for (int c = 0; c < 4; ++c) {
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(p) + c);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-        for (int h = 0; h < 8; h += 4) {
-            const float x0 = v[qd][h], x1 = v[qd][h + 1], x2 = v[qd][h + 2], x3 = v[qd][h + 3];
-            const float s = __fadd_rn(x0, x1), d = __fsub_rn(x0, x1);
-            v[qd][h] = __fmul_rn(0.5f, __fsub_rn(__fadd_rn(s, x2), x3));
-            v[qd][h + 1] = __fmul_rn(0.5f, __fadd_rn(__fsub_rn(s, x2), x3));
-            v[qd][h + 2] = __fmul_rn(0.5f, __fadd_rn(__fadd_rn(d, x2), x3));
-            v[qd][h + 3] = __fmul_rn(0.5f, __fadd_rn(__fadd_rn(-d, x2), x3));
+        for (int i = 0; i < 4; ++i) {
+            v[8 * c + 2 * i] = __uint_as_float(w[i] << 16);
+            v[8 * c + 2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
         }
     }
-    // stage 1: index bit 2 (position in chunk, bit 2) with bit 3 (lane bit 0)
-    {
-        const bool b = lane8 & 1;
-        const float hl = 0.5f, hh = b ? -0.5f : 0.5f;
+}
+template <> __device__ __forceinline__ void load32<float>(const float* p, float (&v)[32]) {
 #pragma unroll
-        for (int qd = 0; qd < 4; ++qd)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) mixed_stage<1>(v[qd][j], v[qd][j + 4], b, hl, hh);
-    }
-    // stage 2: index bit 4 (chunk bit 0) with bit 5 (lane bit 1)
-    {
-        const bool b = (lane8 >> 1) & 1;
-        const float hl = 0.5f, hh = b ? -0.5f : 0.5f;
-#pragma unroll
-        for (int qh = 0; qh < 4; qh += 2)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) mixed_stage<2>(v[qh][j], v[qh + 1][j], b, hl, hh);
-    }
-    // stage 3: index bit 6 (chunk bit 1) with bit 7 (lane bit 2)
-    {
-        const bool b = (lane8 >> 2) & 1;
-        const float hl = 0.5f, hh = b ? -0.5f : 0.5f;
-#pragma unroll
-        for (int ql = 0; ql < 2; ++ql)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) mixed_stage<4>(v[ql][j], v[ql + 2][j], b, hl, hh);
+    for (int c = 0; c < 8; ++c) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(p) + c);
+        v[4 * c] = a.x, v[4 * c + 1] = a.y, v[4 * c + 2] = a.z, v[4 * c + 3] = a.w;
     }
 }
 
-// Element offset, inside its 256-group, of chunk qd of lane lane8 (8 consecutive elements from there).
-__device__ __forceinline__ int chunk_offset(int lane8, int qd) {
-    return 8 * (lane8 & 1) + 16 * (qd & 1) + 32 * ((lane8 >> 1) & 1) + 64 * (qd >> 1) + 128 * (lane8 >> 2);
+__device__ __forceinline__ float lut_f(const uint16_t* lut, float x) {   // x holds a bf16 value
+    return __uint_as_float((uint32_t)lut[__float_as_uint(x) >> 16] << 16);
 }
 
-template <typename T, int PRO>
-__global__ void __launch_bounds__(1024) quant_rows_kernel(const QuantArgs p) {
-    __shared__ unsigned amax_s[128];
+// Radix-4 butterfly of the regular Hadamard block on packed pairs; outputs in the reference's association:
+//   r0 = .5*(((x0+x1)+x2)-x3)  r1 = .5*(((x0+x1)-x2)+x3)  r2 = .5*(((x0-x1)+x2)+x3)  r3 = .5*(((-x0+x1)+x2)+x3)
+__device__ __forceinline__ void h4x2(float2& x0, float2& x1, float2& x2, float2& x3) {
+    const float2 m1 = make_float2(-1.f, -1.f), hf = make_float2(0.5f, 0.5f);
+    const float2 s = __fadd2_rn(x0, x1);
+    const float2 d = __ffma2_rn(x1, m1, x0);                         // x0 - x1
+    const float2 r0 = __fmul2_rn(hf, __ffma2_rn(x3, m1, __fadd2_rn(s, x2)));
+    const float2 r1 = __fmul2_rn(hf, __fadd2_rn(__ffma2_rn(x2, m1, s), x3));
+    const float2 r2 = __fmul2_rn(hf, __fadd2_rn(__fadd2_rn(d, x2), x3));
+    const float2 r3 = __fmul2_rn(hf, __fadd2_rn(__ffma2_rn(d, m1, x2), x3));   // (-d + x2) + x3
+    x0 = r0, x1 = r1, x2 = r2, x3 = r3;
+}
+// two radix-4 stages over 16 packed values: index bits (0,1) then (2,3) of the position in P
+__device__ __forceinline__ void two_stages(float2 (&P)[16]) {
+#pragma unroll
+    for (int i = 0; i < 16; i += 4) h4x2(P[i], P[i + 1], P[i + 2], P[i + 3]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h4x2(P[i], P[i + 4], P[i + 8], P[i + 12]);
+}
+
+// Codes of two values: q = sat8(rint(T(T(v) / T(scale)))). bf16 fast path: both operands of the division carry 8
+// significant bits, so the exact quotient is either representable in fp32 or further than 2^-17 (relative) from every
+// bf16 rounding boundary; a reciprocal multiply with one correction step then rounds to the same bf16 as the IEEE
+// division. cvt.rni + saturating pack equal clamp(rint(.)) except for NaN (0 instead of -128): `nanacc` turns NaN
+// (and stays finite otherwise) so the caller can redo such a lane exactly.
+template <typename T>
+__device__ __forceinline__ uint32_t quant2(float2 v, float st, float rcp, bool fast, float2& nanacc) {
+    if (sizeof(T) == 2 && fast) {
+        const __nv_bfloat162 ab = __floats2bfloat162_rn(v.x, v.y);
+        const uint32_t au = *reinterpret_cast<const uint32_t*>(&ab);
+        const float2 a = make_float2(__uint_as_float(au << 16), __uint_as_float(au & 0xffff0000u));
+        const float2 q0 = __fmul2_rn(a, make_float2(rcp, rcp));
+        const float2 r = __ffma2_rn(q0, make_float2(-st, -st), a);
+        const float2 t = __ffma2_rn(r, make_float2(rcp, rcp), q0);
+        const __nv_bfloat162 tb = __floats2bfloat162_rn(t.x, t.y);
+        const uint32_t tu = *reinterpret_cast<const uint32_t*>(&tb);
+        const float tx = __uint_as_float(tu << 16), ty = __uint_as_float(tu & 0xffff0000u);
+        nanacc = __ffma2_rn(make_float2(tx, ty), make_float2(0.f, 0.f), nanacc);
+        uint32_t packed;
+        asm("{\n\t.reg .s32 a, b;\n\t"
+            "cvt.rni.s32.f32 a, %1;\n\t"
+            "cvt.rni.s32.f32 b, %2;\n\t"
+            "cvt.pack.sat.s8.s32.b32 %0, b, a, 0;\n\t}"
+            : "=r"(packed)
+            : "f"(tx), "f"(ty));
+        return packed;   // byte 0 = code of v.x, byte 1 = code of v.y
+    }
+    const int qx = clamp_rint_i8(rnd<T>(__fdiv_rn(rnd<T>(v.x), st)), -128.f);
+    const int qy = clamp_rint_i8(rnd<T>(__fdiv_rn(rnd<T>(v.y), st)), -128.f);
+    return (uint32_t)(qx & 0xff) | ((uint32_t)(qy & 0xff) << 8);
+}
+
+template <typename T, int PRO, int MAXT>
+__global__ void __launch_bounds__(MAXT) quant_rows_kernel(const QuantArgs p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const uint16_t* lut = g_act_lut[p.lut >= 0 ? p.lut : 0];
+    uint8_t* after_lut = smem;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    float* tbuf = reinterpret_cast<float*>(after_lut) + (warp * 4 + (lane >> 3)) * kGroupWords;   // this group's buffer
+    unsigned* amax_s = reinterpret_cast<unsigned*>(after_lut + (size_t)nwarps * 4 * kGroupWords * 4);   // [3][rows]
+
+    for (int i = threadIdx.x; i < 3 * p.rows_per_cta; i += blockDim.x) amax_s[i] = 0u;
+    __syncthreads();
+
     const int tpr = p.tpr;
     const int rloc = threadIdx.x / tpr;               // row inside the CTA
     const int tin = threadIdx.x - rloc * tpr;         // thread inside the row
-    const int64_t m_raw = (int64_t)blockIdx.x * p.rows_per_cta + rloc;
-    const bool live = m_raw < p.M;
-    const int64_t m = live ? m_raw : p.M - 1;          // idle rows recompute the last row and store nothing
-    const int grp = tin >> 3, lane8 = tin & 7;
-    const T* x = reinterpret_cast<const T*>(p.x) + m * p.x_stride + (grp << 8);
+    const int grp = tin >> 3, t8 = tin & 7;
+    int it = 0;
+    for (int blk = blockIdx.x; blk < p.nblocks; blk += gridDim.x, ++it) {
+        const int64_t m_raw = (int64_t)blk * p.rows_per_cta + rloc;
+        const bool live = m_raw < p.M;
+        const int64_t m = live ? m_raw : p.M - 1;      // idle rows recompute the last row and store nothing
+        const int col = (grp << 8) + (t8 << 5);
+        const T* x = reinterpret_cast<const T*>(p.x) + m * p.x_stride + col;
 
-    if (threadIdx.x < 128) amax_s[threadIdx.x] = 0u;
-
-    float v[4][8];
-#pragma unroll
-    for (int qd = 0; qd < 4; ++qd) {
-        const int c = chunk_offset(lane8, qd);
-        load8<T>(x + c, v[qd]);
+        float v[32];
+        load32<T>(x, v);
         if (PRO == PRO_GATE) {
-            float gg[8];
-            load8<T>(reinterpret_cast<const T*>(p.g) + m * p.g_stride + (grp << 8) + c, gg);
+            float gg[32];
+            load32<T>(reinterpret_cast<const T*>(p.g) + m * p.g_stride + col, gg);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[qd][j] = rnd<T>(v[qd][j] * rnd<T>(sigmoid_f(gg[j])));
+            for (int i = 0; i < 32; ++i)
+                v[i] = rnd<T>(v[i] * ((sizeof(T) == 2 && p.lut >= 0) ? lut_f(lut, gg[i]) : rnd<T>(sigmoid_f(gg[i]))));
         } else if (PRO == PRO_SWIGLU) {
-            float u[8];
-            load8<T>(x + p.up_offset + c, u);
+            float u[32];
+            load32<T>(x + p.up_offset, u);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[qd][j] = rnd<T>(rnd<T>(silu_f(v[qd][j])) * u[j]);
-        } else if (PRO == PRO_SILU) {
+            for (int i = 0; i < 32; ++i)
+                v[i] = rnd<T>(((sizeof(T) == 2 && p.lut >= 0) ? lut_f(lut, v[i]) : rnd<T>(silu_f(v[i]))) * u[i]);
+        } else if (PRO == PRO_SILU || PRO == PRO_GELU || PRO == PRO_GELU_TANH) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[qd][j] = rnd<T>(silu_f(v[qd][j]));
-        } else if (PRO == PRO_GELU) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[qd][j] = rnd<T>(gelu_f(v[qd][j]));
-        } else if (PRO == PRO_GELU_TANH) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[qd][j] = rnd<T>(gelu_tanh_f(v[qd][j]));
-        }
-    }
-
-    if (p.rotate) rotate256(v, lane8);
-
-    if (p.out_f) {
-        if (live) {
-            float* o = p.out_f + m * (int64_t)p.K + (grp << 8);
-#pragma unroll
-            for (int qd = 0; qd < 4; ++qd) {
-                const int c = chunk_offset(lane8, qd);
-                *reinterpret_cast<float4*>(o + c) = make_float4(v[qd][0], v[qd][1], v[qd][2], v[qd][3]);
-                *reinterpret_cast<float4*>(o + c + 4) = make_float4(v[qd][4], v[qd][5], v[qd][6], v[qd][7]);
+            for (int i = 0; i < 32; ++i) {
+                if (sizeof(T) == 2 && p.lut >= 0) v[i] = lut_f(lut, v[i]);
+                else v[i] = rnd<T>(PRO == PRO_SILU ? silu_f(v[i]) : PRO == PRO_GELU ? gelu_f(v[i]) : gelu_tanh_f(v[i]));
             }
         }
-        return;
-    }
 
-    float amax = 0.f;
+        float2 P[16];
+        if (p.rotate) {
+            // stages 0, 1 on the lane's two runs of 16, packed as (element i, element i + 16)
 #pragma unroll
-    for (int qd = 0; qd < 4; ++qd)
+            for (int i = 0; i < 16; ++i) P[i] = make_float2(v[i], v[i + 16]);
+            two_stages(P);
+            // transpose inside the group: lane t8 wrote elements 32 t8 + i, now takes (2 t8, 2 t8 + 1) + 16 r
+            const int wbase = tpad(t8 << 5);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[qd][j]));
-    // the group's 8 lanes first, then one shared-memory atomic per group (non-negative floats order as integers)
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-    __syncthreads();
-    if (lane8 == 0) atomicMax(&amax_s[rloc], __float_as_uint(amax));
-    __syncthreads();
-    amax = __uint_as_float(amax_s[rloc]);
-
-    const float scale = fmaxf(fminf(amax, finite_max<T>()) * (1.f / 127.f), 1.0e-30f);
-    if (live && tin == 0) p.scales[m] = scale;
-    const float st = rnd<T>(scale);
-    // bf16: both operands of the division carry 8 significant bits, so the exact quotient is either representable
-    // in fp32 or further than 2^-17 (relative) from every bf16 rounding boundary; a reciprocal multiply with one
-    // correction step then rounds to the same bf16 as the IEEE division. Rows holding an infinity keep the division.
-    const bool fast = sizeof(T) == 2 && amax <= FLT_MAX;
-    const float rcp = fast ? __frcp_rn(st) : 0.f;
-    if (!live) return;
-    int8_t* q = p.q + m * (int64_t)p.K + (grp << 8);
-#pragma unroll
-    for (int qd = 0; qd < 4; ++qd) {
-        uint32_t w[2] = {0u, 0u};
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float a = rnd<T>(v[qd][j]);
-            float t;
-            if (fast) {
-                const float q0 = __fmul_rn(a, rcp);
-                t = __fmaf_rn(__fmaf_rn(-q0, st, a), rcp, q0);
-            } else {
-                t = __fdiv_rn(a, st);
+            for (int i = 0; i < 16; ++i) {
+                tbuf[wbase + i] = P[i].x;
+                tbuf[wbase + 16 + i] = P[i].y;   // element 32 t8 + 16 + i: same 32-run, no pad in between
             }
-            const int qi = clamp_rint_i8(rnd<T>(t), -128.f);
-            w[j >> 2] |= (uint32_t)(qi & 0xff) << (8 * (j & 3));
+            __syncwarp();
+#pragma unroll
+            for (int r = 0; r < 16; ++r) P[r] = *reinterpret_cast<const float2*>(tbuf + tpad(2 * t8 + 16 * r));
+            two_stages(P);   // index bits 4-7 = r
+            __syncwarp();
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) P[i] = make_float2(v[2 * i], v[2 * i + 1]);   // natural order
         }
-        *reinterpret_cast<uint2*>(q + chunk_offset(lane8, qd)) = make_uint2(w[0], w[1]);
+
+        if (p.out_f) {   // gpu_rotate_rows_f32: always rotated, so P holds (2 t8, 2 t8 + 1) + 16 r
+            if (live) {
+                float* o = p.out_f + m * (int64_t)p.K + (grp << 8) + 2 * t8;
+#pragma unroll
+                for (int r = 0; r < 16; ++r) *reinterpret_cast<float2*>(o + 16 * r) = P[r];
+            }
+            continue;
+        }
+
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fmaxf(fabsf(P[i].x), fabsf(P[i].y)));
+        // the group's 8 lanes first, then one shared-memory atomic per group (non-negative floats order as integers)
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+        unsigned* slot = amax_s + (it % 3) * p.rows_per_cta + rloc;
+        if (t8 == 0) atomicMax(slot, __float_as_uint(amax));
+        __syncthreads();
+        amax = __uint_as_float(*slot);
+        amax_s[((it + 2) % 3) * p.rows_per_cta + rloc] = 0u;   // next use is two barriers away, last use one barrier back
+
+        const float scale = fmaxf(fminf(amax, finite_max<T>()) * (1.f / 127.f), 1.0e-30f);
+        if (live && tin == 0) p.scales[m] = scale;
+        const float st = rnd<T>(scale);
+        const bool fast = sizeof(T) == 2 && amax <= FLT_MAX;   // rows holding an infinity keep the IEEE division
+        const float rcp = fast ? __frcp_rn(st) : 0.f;
+        float2 nanacc = make_float2(0.f, 0.f);
+        uint32_t c16[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) c16[i] = quant2<T>(P[i], st, rcp, fast, nanacc);
+        if (fast && (nanacc.x != nanacc.x || nanacc.y != nanacc.y)) {   // a NaN in this lane: redo it with exact clamping
+#pragma unroll
+            for (int i = 0; i < 16; ++i) c16[i] = quant2<T>(P[i], st, rcp, false, nanacc);
+        }
+        int8_t* q = p.q + m * (int64_t)p.K + col;
+        if (p.rotate) {
+            // codes of (2 t8, 2 t8 + 1) + 16 r back through the group's buffer, so each lane stores 32 contiguous bytes
+            uint16_t* cb = reinterpret_cast<uint16_t*>(tbuf);
+#pragma unroll
+            for (int r = 0; r < 16; ++r) cb[t8 + 8 * r] = (uint16_t)c16[r];
+            __syncwarp();
+            const uint4 lo = reinterpret_cast<const uint4*>(tbuf)[2 * t8], hi = reinterpret_cast<const uint4*>(tbuf)[2 * t8 + 1];
+            __syncwarp();
+            if (live) {
+                reinterpret_cast<uint4*>(q)[0] = lo;
+                reinterpret_cast<uint4*>(q)[1] = hi;
+            }
+        } else if (live) {
+            uint32_t w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w[i] = (c16[2 * i] & 0xffffu) | (c16[2 * i + 1] << 16);
+            reinterpret_cast<uint4*>(q)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            reinterpret_cast<uint4*>(q)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        }
     }
+}
+
+// ---- host side ------------------------------------------------------------------------------------------------
+struct LutState {
+    std::mutex mu;
+    bool launched[LUT_COUNT] = {};
+    bool done[LUT_COUNT] = {};
+    cudaEvent_t ev[LUT_COUNT] = {};
+};
+LutState g_lut_state[64];
+
+// Makes table `which` of the current device usable by work enqueued on `st` afterwards. The first call per device
+// and table launches the builder on `st` (so it should come before any stream capture); later calls on other
+// streams are ordered behind it until it is known complete.
+int ensure_lut(int which, cudaStream_t st) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    LutState& s = g_lut_state[dev & 63];
+    std::lock_guard<std::mutex> lk(s.mu);
+    if (!s.launched[which]) {
+        build_lut_kernel<<<256, 256, 0, st>>>(which);
+        KCHECK();
+        cudaError_t e = cudaEventCreateWithFlags(&s.ev[which], cudaEventDisableTiming);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaEventRecord(s.ev[which], st);
+        if (e != cudaSuccess) return (int)e;
+        s.launched[which] = true;
+        return 0;
+    }
+    if (!s.done[which]) {
+        if (cudaEventQuery(s.ev[which]) == cudaSuccess) s.done[which] = true;
+        else {
+            const cudaError_t e = cudaStreamWaitEvent(st, s.ev[which], 0);
+            if (e != cudaSuccess) return (int)e;
+        }
+    }
+    return 0;
+}
+
+template <typename T, int PRO, int MAXT>
+int launch_cfg(QuantArgs& p, int threads, size_t smem, int grid, cudaStream_t st) {
+    auto kern = quant_rows_kernel<T, PRO, MAXT>;
+    static std::atomic<uint64_t> configured{0};
+    if (smem > 48 * 1024) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        const uint64_t bit = 1ull << (dev & 63);
+        if (!(configured.load(std::memory_order_acquire) & bit)) {
+            const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (e != cudaSuccess) return (int)e;
+            configured.fetch_or(bit, std::memory_order_release);
+        }
+    }
+    kern<<<grid, threads, smem, st>>>(p);
+    KCHECK();
+    return 0;
 }
 
 template <typename T, int PRO>
@@ -230,15 +341,27 @@ int launch_quant(QuantArgs& p, cudaStream_t st) {
     p.tpr = p.K / 32;
     if (p.tpr > 1024) return -2;  // the reference's limit: K <= 32768 (csrc/kernels.cu:264)
     if (p.M <= 0) return 0;
+    static const bool lut_off = [] { const char* e = getenv("GPU_KERNELS_QUANT_LUT"); return e && e[0] == '0'; }();
+    int lut = -1;
+    if (sizeof(T) == 2 && !lut_off && (int64_t)p.M * p.K >= (1 << 20)) {
+        lut = PRO == PRO_SILU || PRO == PRO_SWIGLU ? LUT_SILU : PRO == PRO_GELU ? LUT_GELU : PRO == PRO_GELU_TANH ? LUT_GELU_TANH
+              : PRO == PRO_GATE ? LUT_SIGMOID : -1;
+    }
+    if (lut >= 0) {
+        if (int rc = ensure_lut(lut, st)) return rc;
+    }
+    p.lut = lut;
     const int gcd32 = p.tpr % 32 == 0 ? 32 : (p.tpr % 16 == 0 ? 16 : 8);
     const int r0 = 32 / gcd32;    // rows that make the CTA a whole number of warps
-    int rows = r0 * (256 / (p.tpr * r0) > 0 ? 256 / (p.tpr * r0) : 1);
-    if (rows > 128) rows = 128;
+    const int target = 256;
+    int rows = r0 * (target / (p.tpr * r0) > 0 ? target / (p.tpr * r0) : 1);
     p.rows_per_cta = rows;
-    const unsigned grid = (unsigned)((p.M + rows - 1) / rows);
-    quant_rows_kernel<T, PRO><<<grid, rows * p.tpr, 0, st>>>(p);
-    KCHECK();
-    return 0;
+    p.nblocks = (p.M + rows - 1) / rows;
+    const int threads = rows * p.tpr;
+    const size_t smem = (size_t)(threads / 32) * 4 * kGroupWords * 4 + 3 * rows * 4;
+    const int grid = p.nblocks;
+    if (threads > 512) return launch_cfg<T, PRO, 1024>(p, threads, smem, grid, st);
+    return launch_cfg<T, PRO, 512>(p, threads, smem, grid, st);
 }
 
 template <typename T>
@@ -255,8 +378,6 @@ int dispatch_prologue(int prologue, QuantArgs& p, cudaStream_t st) {
     }
 }
 
-bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
-
 }  // namespace
 
 // Same contract as the reference's gpu_quant_rows (csrc/kernels.cu:271-298): K % 256 == 0 (-1), K <= 32768 (-2),
@@ -266,7 +387,7 @@ GPU_API int gpu_quant_rows(int dtype, int prologue, const void* x, int64_t x_str
                            int8_t* q, float* scales, int M, int K, int rotate, void* stream) {
     (void)norm_w, (void)eps, (void)mod_scale, (void)mod_shift;
     if ((K % 256) != 0) return -1;
-    QuantArgs p{x, x_stride, g, g_stride, up_offset, q, scales, nullptr, M, K, rotate, 0, 0};
+    QuantArgs p{x, x_stride, g, g_stride, up_offset, q, scales, nullptr, M, K, rotate, 0, 0, 0, -1};
     if (dtype == DT_BF16) return dispatch_prologue<bf16>(prologue, p, (cudaStream_t)stream);
     if (dtype == DT_F32) return dispatch_prologue<float>(prologue, p, (cudaStream_t)stream);
     return -4;
@@ -277,7 +398,7 @@ GPU_API int gpu_rotate_rows_f32(int prologue, const float* x, int64_t x_stride, 
                                 float eps, float* out, int M, int K, void* stream) {
     (void)norm_w, (void)eps;
     if ((K % 256) != 0) return -1;
-    QuantArgs p{x, x_stride, nullptr, 0, up_offset, nullptr, nullptr, out, M, K, 1, 0, 0};
+    QuantArgs p{x, x_stride, nullptr, 0, up_offset, nullptr, nullptr, out, M, K, 1, 0, 0, 0, -1};
     switch (prologue) {
         case PRO_PLAIN: return launch_quant<float, PRO_PLAIN>(p, (cudaStream_t)stream);
         case PRO_SWIGLU: return launch_quant<float, PRO_SWIGLU>(p, (cudaStream_t)stream);

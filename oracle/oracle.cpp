@@ -434,6 +434,15 @@ ORC_API int orc_int8_gemm(const int8_t* A, const int8_t* W, const float* xs, con
     return orc_epilogue(acc.data(), xs, ws, bias, rscale, resid, D, M, N, out_dt, act, contract);
 }
 
+// Overrides the OpenMP thread count (launchers such as torchrun export OMP_NUM_THREADS=1).
+ORC_API void orc_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 ORC_API int orc_num_threads() {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -60,6 +60,13 @@ def num_threads() -> int:
     return lib().orc_num_threads()
 
 
+def use_all_cores() -> int:
+    """Use every host core the process may run on, whatever OMP_NUM_THREADS says; returns the thread count."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().orc_set_threads(C.c_int(n))
+    return num_threads()
+
+
 def fht_rows(x: torch.Tensor, group: int = 256) -> torch.Tensor:
     """Rotated copy of f32 rows (groups of 256 or 64 along the last dim)."""
     y = _chk(x.clone(), torch.float32)
