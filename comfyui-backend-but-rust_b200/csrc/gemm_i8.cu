@@ -129,12 +129,25 @@ template <> __device__ __forceinline__ void load8<half>(const half* p, float (&y
 // The epilogue arithmetic on 8 consecutive columns of one row (accumulators r[0..7] -> y[0..7], not yet rounded
 // to the output type for the last step; the store rounds).
 //   t0 = float(acc) * xs;  v = out(fma(t0, ws, bias));  RESID: fma(v, rscale, resid);  ACT: act(v)
+// `vs`, when set, points at this warp's staged per-column vectors for these 8 columns in shared memory
+// (ws at vs[0..], bias at vs[128..], rscale at vs[256..], all as f32, zero beyond N).
 template <typename OutT, int EPI>
 __device__ __forceinline__ void epilogue8(const GemmParams& p, const uint32_t* r, int row, int col, float xs_r, bool vec,
-                                          float (&y)[8]) {
+                                          float (&y)[8], const float* vs = nullptr) {
     float w8[8], b8[8], rs8[8], rr[8];
     const OutT* rsd = reinterpret_cast<const OutT*>(p.resid) + (int64_t)row * p.N + col;
-    if (vec) {
+    if (vs) {
+        load8<float>(vs, w8);            // every lane reads the same words: broadcasts
+        load8<float>(vs + 128, b8);
+        if (EPI == EPI_RESID) {
+            load8<float>(vs + 256, rs8);
+            if (vec) load8<OutT>(rsd, rr);
+            else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) rr[e] = col + e < p.N ? to_f<OutT>(rsd[e]) : 0.f;
+            }
+        }
+    } else if (vec) {
         // every lane reads the same addresses of the per-column vectors: one broadcast per load
         load8<float>(p.ws + col, w8);
         if (p.bias) load8<OutT>(reinterpret_cast<const OutT*>(p.bias) + col, b8);
@@ -155,7 +168,7 @@ __device__ __forceinline__ void epilogue8(const GemmParams& p, const uint32_t* r
             }
         }
     }
-    if (!p.bias) {
+    if (!vs && !p.bias) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) b8[e] = 0.f;
     }
@@ -210,19 +223,30 @@ __device__ __forceinline__ void chunk_direct(const GemmParams& p, const uint32_t
 // One 32-column chunk of the warp's 32 rows, staged in shared memory in the layout a TMA store with the 64-byte
 // (2-byte outputs) or 128-byte (4-byte outputs) swizzle expects: row r at r * pitch, its 16-byte piece j at
 // piece j ^ f(r). Eight consecutive lanes then hit eight different bank groups.
+// 2-byte outputs: the chunk's 32 values of this lane's row, computed and packed (no shared-memory traffic yet)
+template <typename OutT, int EPI>
+__device__ __forceinline__ void chunk_compute16(const GemmParams& p, const uint32_t (&r)[32], int row, int col0, float xs_r,
+                                                const float* vs, uint4 (&pk)[4]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float y[8];
+        epilogue8<OutT, EPI>(p, r + 8 * j, row, col0 + 8 * j, xs_r, p.vec_ok && col0 + 8 * j + 8 <= p.N, y, vs + 8 * j);
+        if constexpr (sizeof(OutT) == 2) pk[j] = pack8<OutT>(y);
+    }
+}
+__device__ __forceinline__ void chunk_write16(const uint4 (&pk)[4], uint8_t* stage, int lane) {
+    uint8_t* rowp = stage + lane * 64;
+    const int sw = (lane >> 1) & 3;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(rowp + ((j ^ sw) << 4)) = pk[j];
+}
+
 template <typename OutT, int EPI>
 __device__ __forceinline__ void chunk_to_smem(const GemmParams& p, const uint32_t (&r)[32], int row, int col0, float xs_r,
                                               uint8_t* stage, int lane) {
     constexpr int kEsz = EPI == EPI_ACC ? 4 : (int)sizeof(OutT);
     if constexpr (kEsz == 2) {
-        uint8_t* rowp = stage + lane * 64;
-        const int sw = (lane >> 1) & 3;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            float y[8];
-            epilogue8<OutT, EPI>(p, r + 8 * j, row, col0 + 8 * j, xs_r, p.vec_ok && col0 + 8 * j + 8 <= p.N, y);
-            *reinterpret_cast<uint4*>(rowp + ((j ^ sw) << 4)) = pack8<OutT>(y);
-        }
+        return;   // 2-byte outputs go through chunk_compute16 / chunk_write16
     } else {
         uint8_t* rowp = stage + lane * 128;
         const int sw = lane & 7;
@@ -396,31 +420,45 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     } else {
         // ---------------- epilogue (both CTAs, 8 warps) ----------------
         constexpr int kEsz = EPI == EPI_ACC ? 4 : (int)sizeof(OutT);
-        constexpr int kChunkBytes = 32 * 32 * kEsz;      // 2 KB or 4 KB of staging per chunk
-        constexpr int kBufs = 4096 / kChunkBytes;        // 2-byte outputs alternate between two staging buffers
+        constexpr bool kStageVec = kEsz == 2;            // 2-byte outputs: 2 KB chunk + 1.5 KB of per-column vectors
         const int ew = warp - 2;
         const int quad = warp & 3;               // TMEM lane quarter this warp may read
         const int half = ew >> 2;                // which half of the 32-column chunks
         const int nchunks = BN / 32;
         uint8_t* my_stage = staging + ew * 4096;
         const uint32_t my_stage_u32 = smem_u32(my_stage);
+        float* my_vec = reinterpret_cast<float*>(my_stage + 2048);   // ws[128] | bias[128] | rscale[128]
         int buf = 0;
         uint32_t tphase = 0;
-        uint32_t nstore = 0;                     // TMA stores this warp has issued
         for (int t = cluster_id; t < p.num_tiles; t += nclusters) {
             int tm, tn;
             tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
             const int n0 = tn * BN;
-            PROF_T0();
-            const bool got = mbar_wait(bar_tfull + 8 * buf, tphase, abort_s, ST_TIMEOUT_TMEM_FULL);
-            if (!__all_sync(0xffffffffu, got)) break;
-            if (threadIdx.x == 64) PROF_ADD(3);
-            tc_fence_after();
             const int row0 = tm * (2 * BM) + (int)rank * BM + quad * 32;
             const int row = row0 + lane;
             const bool row_ok = row < p.M;
             const int rrow = row_ok ? row : p.M - 1;     // rows past M compute on the last row; their output is clipped
             const float xs_r = EPI != EPI_ACC ? p.xs[rrow] : 0.f;
+            const bool staged = kStageVec && p.tma_store;
+            if (staged) {
+                // this warp's columns of ws / bias / rscale, fetched while the mainloop still runs
+                __syncwarp();
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int n = n0 + (half + 2 * k) * 32 + lane;
+                    const bool in = n < p.N && half + 2 * k < nchunks;
+                    my_vec[32 * k + lane] = in ? p.ws[n] : 0.f;
+                    my_vec[128 + 32 * k + lane] = (in && p.bias) ? to_f<OutT>(reinterpret_cast<const OutT*>(p.bias)[n]) : 0.f;
+                    if (EPI == EPI_RESID)
+                        my_vec[256 + 32 * k + lane] = in ? to_f<OutT>(reinterpret_cast<const OutT*>(p.rscale)[n]) : 0.f;
+                }
+                __syncwarp();
+            }
+            PROF_T0();
+            const bool got = mbar_wait(bar_tfull + 8 * buf, tphase, abort_s, ST_TIMEOUT_TMEM_FULL);
+            if (!__all_sync(0xffffffffu, got)) break;
+            if (threadIdx.x == 64) PROF_ADD(3);
+            tc_fence_after();
             const uint32_t taddr = tmem_base + buf * 256 + ((uint32_t)(quad * 32) << 16);
             // two register sets: the load of the next chunk is in flight while this one is processed
             uint32_t ra[32], rb[32];
@@ -428,18 +466,23 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 const int col0 = n0 + c * 32;
                 if (col0 >= p.N) return;
                 if (p.tma_store) {
-                    uint8_t* sb = my_stage + (nstore % kBufs) * kChunkBytes;
-                    // the store that last read this buffer must be done with it
-                    if (lane == 0) bulk_wait_read<kBufs - 1>();
-                    __syncwarp();
-                    chunk_to_smem<OutT, EPI>(p, r, rrow, col0, xs_r, sb, lane);
+                    if constexpr (kStageVec) {
+                        uint4 pk[4];
+                        chunk_compute16<OutT, EPI>(p, r, rrow, col0, xs_r, my_vec + 32 * ((c - half) >> 1), pk);
+                        if (lane == 0) bulk_wait_read<0>();   // the previous chunk's store has read the buffer
+                        __syncwarp();
+                        chunk_write16(pk, my_stage, lane);
+                    } else {
+                        if (lane == 0) bulk_wait_read<0>();
+                        __syncwarp();
+                        chunk_to_smem<OutT, EPI>(p, r, rrow, col0, xs_r, my_stage, lane);
+                    }
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
-                        tma_store_2d(&tmap_d, my_stage_u32 + (nstore % kBufs) * kChunkBytes, col0, row0);
+                        tma_store_2d(&tmap_d, my_stage_u32, col0, row0);
                         bulk_commit();
                     }
-                    ++nstore;
                 } else if (row_ok) {
                     chunk_direct<OutT, EPI>(p, r, row, col0, xs_r);
                 }
