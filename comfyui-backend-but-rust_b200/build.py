@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libgpu_kernels.so")
-UNITS = ["quant_rows", "gemm_i8", "weight_pack"]
+UNITS = ["quant_rows", "gemm_i8", "gemm_skinny", "weight_pack"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
          "-Xcompiler", "-fPIC,-fvisibility=hidden", "-I" + CSRC, "-I" + os.path.join(os.path.dirname(HERE), "include")]

@@ -135,6 +135,26 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// The same wait for a whole warp whose wake-up is not urgent: one lane polls, sleeping between polls, so that
+// hundreds of idle threads do not hammer the barrier's shared-memory word while the tensor core reads operands.
+__device__ __forceinline__ bool mbar_wait_warp_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    bool ok = true;
+    if ((threadIdx.x & 31) == 0) {
+        uint64_t t0 = 0;
+        for (uint32_t it = 0;; ++it) {
+            if (mbar_try_wait(bar, parity)) break;
+            __nanosleep(128);
+            if ((it & 15u) == 15u) {
+                if (*abort_flag) { ok = false; break; }
+                const uint64_t now = globaltimer_ns();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > kWaitLimitNs) { *abort_flag = code; ok = false; break; }
+            }
+        }
+    }
+    return __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+}
+
 // 2-D tiled TMA load, global -> this CTA's shared memory, completion on an mbarrier (no multicast).
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int x, int y, uint32_t bar) {
     asm volatile(

@@ -1,0 +1,36 @@
+// The dequant epilogue's arithmetic, shared by the GEMM kernels (one element at a time here; the tensor-core kernel
+// applies the same operations eight columns at a time).
+//   t0 = float(acc) * xs;  y = out(fma(t0, ws, bias));  residual: fma(y, rscale, resid);  activation: act(y)
+// The caller rounds the returned value to the output type when it stores it.
+// Reference: csrc/vendor/cutlass_gemm_int8.cu:84-95 and :143-161 (nvcc fuses both multiply-adds there).
+#pragma once
+
+#include "common.cuh"
+
+enum EpiMode { EPI_PLAIN = 0, EPI_RESID = 1, EPI_ACT = 2, EPI_ACC = 3 };
+enum Act { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_SILU = 2, ACT_GELU_ERF = 3 };
+
+template <typename OutT, int EPI>
+__device__ __forceinline__ float epilogue1(int acc, float xs, float ws, float bias, float rscale, float resid, int act) {
+    const float t0 = __fmul_rn(__int2float_rn(acc), xs);
+    float v = rnd<OutT>(__fmaf_rn(t0, ws, bias));
+    if (EPI == EPI_RESID) v = __fmaf_rn(v, rscale, resid);
+    else if (EPI == EPI_ACT) v = act == ACT_GELU_TANH ? gelu_tanh_f(v) : act == ACT_SILU ? silu_f(v) : gelu_f(v);
+    return v;
+}
+
+// Arguments of the few-rows kernel (gemm_skinny.cu); launched from the GEMM entry points in gemm_i8.cu.
+struct SkinnyParams {
+    const int8_t* A;     // [M, K]
+    const int8_t* W;     // [N, K]
+    const float* xs;
+    const float* ws;
+    const void* bias;
+    const void* rscale;
+    const void* resid;
+    void* D;
+    int M, N, K;
+    int act;
+};
+bool skinny_gemm_applies(int64_t M, int64_t N, int64_t K);
+int launch_skinny_gemm(int epi, const SkinnyParams& p, int out_dt, int sms, cudaStream_t st);

@@ -28,6 +28,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "epilogue.cuh"
 
 __device__ int g_kernel_status = 0;
 #ifdef GEMM_PROFILE
@@ -52,9 +53,6 @@ constexpr int kSmemBytes = 232448;            // the per-CTA maximum (227 KB)
 constexpr int kStagingBytes = kEpiWarps * 4096;  // per epilogue warp: 32 rows x 128 B of output staging
 constexpr int kTailBytes = 256;               // barriers, tensor-memory pointer, abort flag
 
-enum EpiMode { EPI_PLAIN = 0, EPI_RESID = 1, EPI_ACT = 2, EPI_ACC = 3 };
-enum Act { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_SILU = 2, ACT_GELU_ERF = 3 };
-
 struct GemmParams {
     const float* xs;     // [M]
     const float* ws;     // [N]
@@ -70,6 +68,14 @@ struct GemmParams {
     int bn;              // columns per tile (multiple of 32, <= 256); each CTA of the pair stages bn/2 rows of W
     int stages;          // shared-memory ring depth
     int ksub;            // 128-byte K boxes per stage (1 or 2): one barrier round trip per 4 or 8 MMAs
+    // Split tail: when the last round would hold only a few tiles, those tiles are cut along K into `splits` work items
+    // each, so that round runs on every cluster; partial int32 accumulators meet in `scratch`.
+    int whole_tiles;     // tiles computed in one piece (work items [0, whole_tiles))
+    int splits;          // K slices per split tile (>= 2), or 0: work items [whole_tiles, whole_tiles + rem * splits)
+    int kps;             // stages per K slice
+    int num_items;       // whole_tiles + split tiles * splits
+    int* scratch;        // counters [split tiles][2][4][8], zero between launches
+    int* partials;       // [split tiles][2][4][8][32 values][32 lanes] int32 sums, zero between launches
     uint32_t idesc;      // instruction descriptor for M = 256, N = bn
 #ifdef GEMM_PROFILE
     int dbg;             // debug build: bit 0 skips the TMA loads, bit 1 skips the MMAs
@@ -88,6 +94,17 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
     tm = first_m + r % gsize;
     tn = r / gsize;
 }
+
+// Work item -> tile, K range (in stages) and, for a slice of a split tile, its slice and slot numbers.
+struct WorkItem { int tile, k0, kn, split, slot; };
+__device__ __forceinline__ WorkItem decode_item(const GemmParams& p, int w) {
+    if (w < p.whole_tiles) return {w, 0, p.k_iters, -1, 0};
+    const int j = w - p.whole_tiles;
+    const int slot = j / p.splits, sidx = j - slot * p.splits;
+    const int k0 = sidx * p.kps;
+    return {p.whole_tiles + slot, k0, min(p.kps, p.k_iters - k0), sidx, slot};
+}
+constexpr int kCountersPerSlot = 2 * 4 * 8;   // CTA of the pair x TMEM lane quarter x 32-column chunk
 
 template <typename OutT> __device__ __forceinline__ uint4 pack8(const float (&y)[8]);
 template <> __device__ __forceinline__ uint4 pack8<bf16>(const float (&y)[8]) {
@@ -339,12 +356,13 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int t = cluster_id; t < p.num_tiles && ok; t += nclusters) {
+            for (int w = cluster_id; w < p.num_items && ok; w += nclusters) {
+                const WorkItem wi = decode_item(p, w);
                 int tm, tn;
-                tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+                tile_coords(wi.tile, p.tiles_m, p.tiles_n, tm, tn);
                 const int row_a = tm * (2 * BM) + (int)rank * BM;
                 const int row_w = tn * BN + (int)rank * (BN / 2);
-                for (int kb = 0; kb < p.k_iters; ++kb) {
+                for (int kb = wi.k0; kb < wi.k0 + wi.kn; ++kb) {
                     if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_s, ST_TIMEOUT_EMPTY)) { ok = false; break; }
 #ifdef GEMM_PROFILE
                     if (p.dbg & 1) {
@@ -383,11 +401,12 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             int buf = 0;
             uint32_t tphase = 0;
             bool ok = true;
-            for (int t = cluster_id; t < p.num_tiles && ok; t += nclusters) {
+            for (int w = cluster_id; w < p.num_items && ok; w += nclusters) {
+                const int kn = decode_item(p, w).kn;
                 if (!mbar_wait(bar_tempty + 8 * buf, tphase ^ 1u, abort_s, ST_TIMEOUT_TMEM_EMPTY)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * 256;
-                for (int kb = 0; kb < p.k_iters; ++kb) {
+                for (int kb = 0; kb < kn; ++kb) {
                     if (!mbar_try_wait(bar_f, phase)) {
                         if (!mbar_wait(bar_f, phase, abort_s, ST_TIMEOUT_FULL)) { ok = false; break; }
                     }
@@ -430,9 +449,10 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         float* my_vec = reinterpret_cast<float*>(my_stage + 2048);   // ws[128] | bias[128] | rscale[128]
         int buf = 0;
         uint32_t tphase = 0;
-        for (int t = cluster_id; t < p.num_tiles; t += nclusters) {
+        for (int w = cluster_id; w < p.num_items; w += nclusters) {
+            const WorkItem wi = decode_item(p, w);
             int tm, tn;
-            tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+            tile_coords(wi.tile, p.tiles_m, p.tiles_n, tm, tn);
             const int n0 = tn * BN;
             const int row0 = tm * (2 * BM) + (int)rank * BM + quad * 32;
             const int row = row0 + lane;
@@ -455,8 +475,7 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 __syncwarp();
             }
             PROF_T0();
-            const bool got = mbar_wait(bar_tfull + 8 * buf, tphase, abort_s, ST_TIMEOUT_TMEM_FULL);
-            if (!__all_sync(0xffffffffu, got)) break;
+            if (!mbar_wait_warp_relaxed(bar_tfull + 8 * buf, tphase, abort_s, ST_TIMEOUT_TMEM_FULL)) break;
             if (threadIdx.x == 64) PROF_ADD(3);
             tc_fence_after();
             const uint32_t taddr = tmem_base + buf * 256 + ((uint32_t)(quad * 32) << 16);
@@ -487,17 +506,51 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     chunk_direct<OutT, EPI>(p, r, row, col0, xs_r);
                 }
             };
-            int c = half;
-            if (c < nchunks) tmem_ld32(taddr + c * 32, ra);
+            // A slice of a split tile parks its raw accumulators in global scratch; the slice that arrives last at the
+            // chunk's counter adds the others to its own and runs the epilogue (release/acquire through the fences).
+            if (wi.split < 0) {
+                int c = half;
+                if (c < nchunks) tmem_ld32(taddr + c * 32, ra);
 #pragma unroll 1
-            for (; c < nchunks; c += 4) {
-                tmem_ld_wait();
-                if (c + 2 < nchunks) tmem_ld32(taddr + (c + 2) * 32, rb);
-                emit(ra, c);
-                if (c + 2 < nchunks) {
+                for (; c < nchunks; c += 4) {
                     tmem_ld_wait();
-                    if (c + 4 < nchunks) tmem_ld32(taddr + (c + 4) * 32, ra);
-                    emit(rb, c + 2);
+                    if (c + 2 < nchunks) tmem_ld32(taddr + (c + 2) * 32, rb);
+                    emit(ra, c);
+                    if (c + 2 < nchunks) {
+                        tmem_ld_wait();
+                        if (c + 4 < nchunks) tmem_ld32(taddr + (c + 4) * 32, ra);
+                        emit(rb, c + 2);
+                    }
+                }
+            } else {
+                // A slice of a split tile (at most one per cluster, in the last round) adds its raw accumulators into the
+                // tile's int32 buffer in global scratch with atomic adds (integer sums do not depend on the order); the
+                // slice that arrives last at a chunk's counter reads the total, leaves buffer and counter at zero for
+                // the next launch, and runs the epilogue (release / acquire through the fences around the counter).
+#pragma unroll 1
+                for (int c = half; c < nchunks; c += 2) {
+                    tmem_ld32(taddr + c * 32, ra);
+                    tmem_ld_wait();
+                    if (n0 + c * 32 >= p.N) continue;
+                    const int sub = ((int)rank * 4 + quad) * 8 + c;
+                    int* sum = p.partials + ((size_t)wi.slot * kCountersPerSlot + sub) * 1024 + lane;   // [32 values][32 lanes]
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) atomicAdd(sum + 32 * j, (int)ra[j]);
+                    __threadfence();
+                    __syncwarp();
+                    int* cnt = p.scratch + wi.slot * kCountersPerSlot + sub;
+                    int old = 0;
+                    if (lane == 0) old = atomicAdd(cnt, 1);
+                    old = __shfl_sync(0xffffffffu, old, 0);
+                    if (old != p.splits - 1) continue;
+                    if (lane == 0) *cnt = 0;
+                    __threadfence();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        ra[j] = (uint32_t)__ldcg(sum + 32 * j);
+                        __stcg(sum + 32 * j, 0);
+                    }
+                    emit(ra, c);
                 }
             }
             tc_fence_before();
@@ -616,18 +669,50 @@ int launch_pair_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tw, const
     }
 }
 
+// Scratch of the split tail: per device and stream, one buffer allocated on first need and kept (a stream-ordered
+// allocation per call cost more host time than the tail saves). Counters and sums start at zero and every kernel leaves them
+// at zero. A stream beyond the few slots, or a failed allocation, simply runs without the split.
+constexpr size_t kSplitWorkspaceBytes = (size_t)40 * 256 * 256 * 4 + (1 << 16);   // up to clusters/2 split tiles of 256 x 256 int32
+int* split_workspace(int dev, cudaStream_t st, size_t need) {
+    struct Slot { cudaStream_t st; int* buf; bool used; };
+    static Slot slots[64][4];
+    static std::mutex mu;
+    if (need > kSplitWorkspaceBytes) return nullptr;
+    std::lock_guard<std::mutex> lk(mu);
+    Slot* s = slots[dev & 63];
+    for (int i = 0; i < 4; ++i)
+        if (s[i].used && s[i].st == st) return s[i].buf;
+    for (int i = 0; i < 4; ++i) {
+        if (s[i].used) continue;
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+            (void)cudaGetLastError();
+            return nullptr;   // no allocation while the stream is being captured
+        }
+        void* b = nullptr;
+        if (cudaMalloc(&b, kSplitWorkspaceBytes) != cudaSuccess || cudaMemset(b, 0, kSplitWorkspaceBytes) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        s[i] = {st, reinterpret_cast<int*>(b), true};
+        return s[i].buf;
+    }
+    return nullptr;
+}
+
 // Column-tile width: the candidate whose rounds x (width + fixed per-tile cost) is smallest, so that a shape
 // leaving the last round nearly empty at 256 takes a narrower tile instead.
-int choose_bn(int64_t M, int64_t N, int clusters) {
+int choose_bn(int64_t M, int64_t N, int64_t k_iters, int clusters) {
     static const int forced = env_int("GPU_KERNELS_BN", 0);
     if (forced >= 32 && forced <= 256 && forced % 32 == 0) return forced;
     const int64_t tm = (M + 2 * BM - 1) / (2 * BM);
     int best = 256;
-    int64_t best_cost = INT64_MAX;
+    double best_cost = 1e30;
     for (int bn = 256; bn >= 64; bn -= 32) {
         const int64_t tiles = tm * ((N + bn - 1) / bn);
-        const int64_t rounds = (tiles + clusters - 1) / clusters;
-        const int64_t cost = rounds * (bn + 32);
+        const int64_t full = tiles / clusters, rem = tiles % clusters;
+        const double tail = rem ? 1.0 : 0.0;
+        const double cost = ((double)full + tail) * (bn + 32);
         if (cost < best_cost) best_cost = cost, best = bn;
     }
     return best;
@@ -645,6 +730,11 @@ int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const f
     if ((K % 16) != 0 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return -202;
     int dev = 0;
     cudaGetDevice(&dev);
+    static const int no_skinny = env_int("GPU_KERNELS_NO_SKINNY", 0);
+    if (!no_skinny && skinny_gemm_applies(M, N, K)) {
+        SkinnyParams sp{A, W, xs, ws, bias, rscale, resid, D, (int)M, (int)N, (int)K, act};
+        return launch_skinny_gemm(epi, sp, out_dt, device_sm_count(dev), st);
+    }
     const int clusters = device_sm_count(dev) / 2;
     GemmParams p{};
     p.xs = xs, p.ws = ws, p.bias = bias, p.rscale = rscale, p.resid = resid, p.D = D;
@@ -658,12 +748,12 @@ int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const f
     p.vec_ok = (N % 8 == 0) && al16(D) && al16(ws) && al16(bias) && al16(rscale) && al16(resid);
     static const int no_tma_store = env_int("GPU_KERNELS_DIRECT_STORE", 0);
     p.tma_store = !no_tma_store && al16(D) && ((N * esz) % 16 == 0);
-    const int bn = choose_bn(M, N, clusters);
     static const int ksub_env = env_int("GPU_KERNELS_KSUB", 2);
-    p.bn = bn;
-    p.idesc = umma_idesc_i8(2 * BM, bn);
     p.ksub = (ksub_env == 1 || K <= BK) ? 1 : 2;
     p.k_iters = (int)((K + p.ksub * BK - 1) / (p.ksub * BK));
+    const int bn = choose_bn(M, N, p.k_iters, clusters);
+    p.bn = bn;
+    p.idesc = umma_idesc_i8(2 * BM, bn);
     const int stage_bytes = p.ksub * (BM * BK + (bn / 2) * BK);
     const int stages = (kSmemBytes - 1024 - kTailBytes - kStagingBytes) / stage_bytes;
     p.stages = stages > kMaxStages ? kMaxStages : stages;
@@ -677,11 +767,41 @@ int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const f
     } else {
         td = ta;  // unused
     }
-    const int grid = 2 * (p.num_tiles < clusters ? p.num_tiles : clusters);
-    if (epi == EPI_ACC) return launch_pair<float, EPI_ACC>(ta, tw, td, p, grid, st);
-    if (out_dt == DT_F32) return launch_pair_epi<float>(epi, ta, tw, td, p, grid, st);
-    if (out_dt == DT_F16) return launch_pair_epi<half>(epi, ta, tw, td, p, grid, st);
-    return launch_pair_epi<bf16>(epi, ta, tw, td, p, grid, st);
+    // K split: a problem with fewer tiles than clusters and a long K (few rows, few columns) is cut along K so that
+    // more SMs stream it. Measured on B200: worth it only when every slice keeps at least eight stages; splitting the
+    // nearly empty last round of a many-round problem costs as much as that round (fences and atomics) and is not done.
+    p.whole_tiles = p.num_tiles, p.splits = 0, p.kps = p.k_iters, p.num_items = p.num_tiles;
+    p.scratch = nullptr, p.partials = nullptr;
+    static const int split_mode = env_int("GPU_KERNELS_SPLIT", 1);   // 0 never, 1 few-tile problems, 2 also the last round
+    const int rem = p.num_tiles % clusters;
+    const bool few_tiles = p.num_tiles < clusters;
+    if (split_mode && rem > 0 && 2 * rem <= clusters && p.k_iters >= 2 && (few_tiles || split_mode == 2)) {
+        int splits = clusters / rem;
+        const int max_by_k = split_mode == 2 ? p.k_iters : p.k_iters / 8;
+        if (splits > max_by_k) splits = max_by_k;
+        if (splits > 16) splits = 16;
+        if (splits < 1) splits = 1;
+        const int kps = (p.k_iters + splits - 1) / splits;
+        splits = (p.k_iters + kps - 1) / kps;
+        if (splits >= 2) {
+            const size_t counter_bytes = 1 << 16;   // fixed counter region, zeroed once; partials always start behind it
+            const size_t partial_bytes = (size_t)rem * kCountersPerSlot * 32 * 32 * sizeof(int);
+            int* ws = split_workspace(dev, st, counter_bytes + partial_bytes);
+            if (ws) {
+                p.scratch = ws;
+                p.partials = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(ws) + counter_bytes);
+                p.whole_tiles = p.num_tiles - rem, p.splits = splits, p.kps = kps;
+                p.num_items = p.whole_tiles + rem * splits;
+            }
+        }
+    }
+    const int grid = 2 * (p.num_items < clusters ? p.num_items : clusters);
+    int rc;
+    if (epi == EPI_ACC) rc = launch_pair<float, EPI_ACC>(ta, tw, td, p, grid, st);
+    else if (out_dt == DT_F32) rc = launch_pair_epi<float>(epi, ta, tw, td, p, grid, st);
+    else if (out_dt == DT_F16) rc = launch_pair_epi<half>(epi, ta, tw, td, p, grid, st);
+    else rc = launch_pair_epi<bf16>(epi, ta, tw, td, p, grid, st);
+    return rc;
 }
 
 }  // namespace

@@ -1,0 +1,169 @@
+// int8 GEMM for a handful of rows (M <= 8): the adaLN-modulation and pooled-conditioning linears of the DiTs
+// (M = 1 or 3 in the reference's src/anima.rs:733-737), where the work is streaming the weight matrix once.
+// Bound by HBM, so it runs on the CUDA cores: A (a few KB) sits in shared memory, every warp streams four weight
+// rows at a time with 16-byte loads, multiplies with dp4a into int32 (exact, like the tensor path), reduces across
+// the warp and applies the same epilogue arithmetic as the tensor-core kernel.
+#include "common.cuh"
+#include "epilogue.cuh"
+
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kRowsPerWarp = 4;
+
+template <typename OutT, int EPI, int MT>
+__global__ void __launch_bounds__(kWarps * 32) skinny_gemm_kernel(const SkinnyParams p) {
+    extern __shared__ __align__(16) int8_t a_s[];   // [M][K]
+    const int K = p.K;
+    for (int i = threadIdx.x; i < p.M * K / 16; i += blockDim.x)
+        reinterpret_cast<uint4*>(a_s)[i] = __ldg(reinterpret_cast<const uint4*>(p.A) + i);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nblocks = (p.N + kRowsPerWarp - 1) / kRowsPerWarp;
+    for (int nb = blockIdx.x * kWarps + warp; nb < nblocks; nb += gridDim.x * kWarps) {
+        const int n0 = nb * kRowsPerWarp;
+        int acc[kRowsPerWarp][MT];
+#pragma unroll
+        for (int r = 0; r < kRowsPerWarp; ++r)
+#pragma unroll
+            for (int m = 0; m < MT; ++m) acc[r][m] = 0;
+        for (int k0 = lane * 16; k0 < K; k0 += 512) {
+            uint4 w[kRowsPerWarp];
+#pragma unroll
+            for (int r = 0; r < kRowsPerWarp; ++r) {
+                const int n = min(n0 + r, p.N - 1);   // rows past N repeat the last row; their results are dropped
+                w[r] = __ldg(reinterpret_cast<const uint4*>(p.W + (int64_t)n * K + k0));
+            }
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                if (m >= p.M) break;
+                const uint4 a = *reinterpret_cast<const uint4*>(a_s + m * K + k0);
+#pragma unroll
+                for (int r = 0; r < kRowsPerWarp; ++r) {
+                    int s = acc[r][m];
+                    s = __dp4a((int)a.x, (int)w[r].x, s);
+                    s = __dp4a((int)a.y, (int)w[r].y, s);
+                    s = __dp4a((int)a.z, (int)w[r].z, s);
+                    s = __dp4a((int)a.w, (int)w[r].w, s);
+                    acc[r][m] = s;
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < kRowsPerWarp; ++r)
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                int s = acc[r][m];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                acc[r][m] = s;
+            }
+        // lane (r, m) = lane index r * MT + m finishes output (m, n0 + r)
+        if (lane < kRowsPerWarp * MT) {
+            const int r = lane / MT, m = lane % MT;
+            const int n = n0 + r;
+            int s = 0;
+#pragma unroll
+            for (int rr = 0; rr < kRowsPerWarp; ++rr)
+#pragma unroll
+                for (int mm = 0; mm < MT; ++mm)
+                    if (rr == r && mm == m) s = acc[rr][mm];
+            if (n < p.N && m < p.M) {
+                const int64_t o = (int64_t)m * p.N + n;
+                if (EPI == EPI_ACC) reinterpret_cast<int32_t*>(p.D)[o] = s;
+                else {
+                    const float bias = p.bias ? to_f<OutT>(reinterpret_cast<const OutT*>(p.bias)[n]) : 0.f;
+                    const float rs = EPI == EPI_RESID ? to_f<OutT>(reinterpret_cast<const OutT*>(p.rscale)[n]) : 0.f;
+                    const float rr = EPI == EPI_RESID ? to_f<OutT>(reinterpret_cast<const OutT*>(p.resid)[o]) : 0.f;
+                    reinterpret_cast<OutT*>(p.D)[o] = from_f<OutT>(epilogue1<OutT, EPI>(s, p.xs[m], p.ws[n], bias, rs, rr, p.act));
+                }
+            }
+        }
+    }
+}
+
+template <typename OutT, int EPI>
+int launch_mt(const SkinnyParams& p, int grid, size_t smem, cudaStream_t st) {
+    if (smem > 48 * 1024) {
+        cudaFuncSetAttribute(skinny_gemm_kernel<OutT, EPI, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(skinny_gemm_kernel<OutT, EPI, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(skinny_gemm_kernel<OutT, EPI, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(skinny_gemm_kernel<OutT, EPI, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    }
+    if (p.M == 1) skinny_gemm_kernel<OutT, EPI, 1><<<grid, kWarps * 32, smem, st>>>(p);
+    else if (p.M == 2) skinny_gemm_kernel<OutT, EPI, 2><<<grid, kWarps * 32, smem, st>>>(p);
+    else if (p.M <= 4) skinny_gemm_kernel<OutT, EPI, 4><<<grid, kWarps * 32, smem, st>>>(p);
+    else skinny_gemm_kernel<OutT, EPI, 8><<<grid, kWarps * 32, smem, st>>>(p);
+    KCHECK();
+    return 0;
+}
+
+template <typename OutT>
+int launch_epi(int epi, const SkinnyParams& p, int grid, size_t smem, cudaStream_t st) {
+    switch (epi) {
+        case EPI_PLAIN: return launch_mt<OutT, EPI_PLAIN>(p, grid, smem, st);
+        case EPI_RESID: return launch_mt<OutT, EPI_RESID>(p, grid, smem, st);
+        case EPI_ACT: return launch_mt<OutT, EPI_ACT>(p, grid, smem, st);
+        default: return -200;
+    }
+}
+
+// The dequant epilogue alone, over int32 accumulators that already sit in global memory (summed across devices by a
+// reduce-scatter of the partial products of a row-parallel linear).
+template <typename OutT, int EPI>
+__global__ void __launch_bounds__(256) epilogue_i32_kernel(const int32_t* __restrict__ acc, const float* __restrict__ xs,
+                                                           const float* __restrict__ ws, const OutT* __restrict__ bias,
+                                                           const OutT* __restrict__ rscale, const OutT* resid, OutT* D,
+                                                           int64_t M, int64_t N, int act) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= M * N) return;
+    const int64_t m = i / N, n = i - m * N;
+    const float b = bias ? to_f<OutT>(bias[n]) : 0.f;
+    const float rs = EPI == EPI_RESID ? to_f<OutT>(rscale[n]) : 0.f;
+    const float rr = EPI == EPI_RESID ? to_f<OutT>(resid[i]) : 0.f;
+    D[i] = from_f<OutT>(epilogue1<OutT, EPI>(acc[i], xs[m], ws[n], b, rs, rr, act));
+}
+
+template <typename OutT>
+int launch_epilogue_i32(const int32_t* acc, const float* xs, const float* ws, const void* bias, const void* rscale,
+                        const void* resid, void* D, int64_t M, int64_t N, int act, cudaStream_t st) {
+    const unsigned grid = (unsigned)((M * N + 255) / 256);
+    const OutT* b = (const OutT*)bias; const OutT* rs = (const OutT*)rscale; const OutT* rr = (const OutT*)resid;
+    if (resid) epilogue_i32_kernel<OutT, EPI_RESID><<<grid, 256, 0, st>>>(acc, xs, ws, b, rs, rr, (OutT*)D, M, N, act);
+    else if (act) epilogue_i32_kernel<OutT, EPI_ACT><<<grid, 256, 0, st>>>(acc, xs, ws, b, rs, rr, (OutT*)D, M, N, act);
+    else epilogue_i32_kernel<OutT, EPI_PLAIN><<<grid, 256, 0, st>>>(acc, xs, ws, b, rs, rr, (OutT*)D, M, N, act);
+    KCHECK();
+    return 0;
+}
+
+}  // namespace
+
+// New: D = epilogue(acc) for int32 accumulators [M, N] in global memory: the arithmetic of gpu_int8_gemm (resid == NULL,
+// act == 0), gpu_int8_gemm_act (act != 0) or gpu_int8_gemm_residual (resid and rscale given). D may alias resid.
+GPU_API int gpu_int8_epilogue(const int32_t* acc, const float* xs, const float* ws, const void* bias, const void* rscale,
+                              const void* resid, void* D, int64_t M, int64_t N, int out_dt, int act, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if ((resid != nullptr) != (rscale != nullptr)) return -201;
+    if (act < 0 || act > 3) return -204;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (out_dt == DT_F32) return launch_epilogue_i32<float>(acc, xs, ws, bias, rscale, resid, D, M, N, act, st);
+    if (out_dt == DT_F16) return launch_epilogue_i32<half>(acc, xs, ws, bias, rscale, resid, D, M, N, act, st);
+    if (out_dt == DT_BF16) return launch_epilogue_i32<bf16>(acc, xs, ws, bias, rscale, resid, D, M, N, act, st);
+    return -200;
+}
+
+bool skinny_gemm_applies(int64_t M, int64_t N, int64_t K) {
+    return M >= 1 && M <= 8 && K % 16 == 0 && M * K <= 160 * 1024 && N >= 1;
+}
+
+int launch_skinny_gemm(int epi, const SkinnyParams& p, int out_dt, int sms, cudaStream_t st) {
+    const size_t smem = (size_t)p.M * p.K;
+    const int nblocks = (p.N + kRowsPerWarp - 1) / kRowsPerWarp;
+    int grid = (nblocks + kWarps - 1) / kWarps;
+    const int cap = sms * 4;
+    if (grid > cap) grid = cap;
+    if (epi == EPI_ACC) return launch_mt<float, EPI_ACC>(p, grid, smem, st);
+    if (out_dt == DT_F32) return launch_epi<float>(epi, p, grid, smem, st);
+    if (out_dt == DT_F16) return launch_epi<half>(epi, p, grid, smem, st);
+    return launch_epi<bf16>(epi, p, grid, smem, st);
+}

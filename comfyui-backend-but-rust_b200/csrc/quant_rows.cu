@@ -65,6 +65,8 @@ struct QuantArgs {
     int rows_per_cta;
     int nblocks;        // row blocks; CTAs stride over them
     int lut;            // table index of the prologue (read through L1), or -1
+    const float* amax_in;   // when set: row maxima to quantize with (rows whose columns are split across devices)
+    float* amax_out;        // when set: write each row's maximum here and stop (first pass of the same)
 };
 
 constexpr int kGroupWords = 304;   // 256 elements + 4 words of padding per 32, rounded so that groups sit 16 banks apart
@@ -243,6 +245,11 @@ __global__ void __launch_bounds__(MAXT) quant_rows_kernel(const QuantArgs p) {
         __syncthreads();
         amax = __uint_as_float(*slot);
         amax_s[((it + 2) % 3) * p.rows_per_cta + rloc] = 0u;   // next use is two barriers away, last use one barrier back
+        if (p.amax_out) {
+            if (live && tin == 0) p.amax_out[m] = amax;
+            continue;
+        }
+        if (p.amax_in) amax = p.amax_in[m];
 
         const float scale = fmaxf(fminf(amax, finite_max<T>()) * (1.f / 127.f), 1.0e-30f);
         if (live && tin == 0) p.scales[m] = scale;
@@ -387,7 +394,7 @@ GPU_API int gpu_quant_rows(int dtype, int prologue, const void* x, int64_t x_str
                            int8_t* q, float* scales, int M, int K, int rotate, void* stream) {
     (void)norm_w, (void)eps, (void)mod_scale, (void)mod_shift;
     if ((K % 256) != 0) return -1;
-    QuantArgs p{x, x_stride, g, g_stride, up_offset, q, scales, nullptr, M, K, rotate, 0, 0, 0, -1};
+    QuantArgs p{x, x_stride, g, g_stride, up_offset, q, scales, nullptr, M, K, rotate, 0, 0, 0, -1, nullptr, nullptr};
     if (dtype == DT_BF16) return dispatch_prologue<bf16>(prologue, p, (cudaStream_t)stream);
     if (dtype == DT_F32) return dispatch_prologue<float>(prologue, p, (cudaStream_t)stream);
     return -4;
@@ -398,10 +405,33 @@ GPU_API int gpu_rotate_rows_f32(int prologue, const float* x, int64_t x_stride, 
                                 float eps, float* out, int M, int K, void* stream) {
     (void)norm_w, (void)eps;
     if ((K % 256) != 0) return -1;
-    QuantArgs p{x, x_stride, nullptr, 0, up_offset, nullptr, nullptr, out, M, K, 1, 0, 0, 0, -1};
+    QuantArgs p{x, x_stride, nullptr, 0, up_offset, nullptr, nullptr, out, M, K, 1, 0, 0, 0, -1, nullptr, nullptr};
     switch (prologue) {
         case PRO_PLAIN: return launch_quant<float, PRO_PLAIN>(p, (cudaStream_t)stream);
         case PRO_SWIGLU: return launch_quant<float, PRO_SWIGLU>(p, (cudaStream_t)stream);
         default: return -3;
     }
+}
+
+// New, for rows whose K columns are split across devices (row-parallel linears): the per-token scale must come from
+// the maximum over the whole row, so quantization runs in two passes around a max-reduction between the devices.
+//   pass 1  gpu_quant_rows_amax: prologue + rotation of the local columns, row maxima -> amax [M] (f32)
+//   pass 2  gpu_quant_rows_scaled: the same, quantized with the given (reduced) maxima; `scales` receives the scale
+// With the reduced maxima the codes equal the corresponding columns of the single-device result bit for bit.
+GPU_API int gpu_quant_rows_amax(int dtype, int prologue, const void* x, int64_t x_stride, const void* g, int64_t g_stride,
+                                int64_t up_offset, float* amax, int M, int K, int rotate, void* stream) {
+    if ((K % 256) != 0) return -1;
+    QuantArgs p{x, x_stride, g, g_stride, up_offset, nullptr, nullptr, nullptr, M, K, rotate, 0, 0, 0, -1, nullptr, amax};
+    if (dtype == DT_BF16) return dispatch_prologue<bf16>(prologue, p, (cudaStream_t)stream);
+    if (dtype == DT_F32) return dispatch_prologue<float>(prologue, p, (cudaStream_t)stream);
+    return -4;
+}
+GPU_API int gpu_quant_rows_scaled(int dtype, int prologue, const void* x, int64_t x_stride, const void* g, int64_t g_stride,
+                                  int64_t up_offset, const float* amax, int8_t* q, float* scales, int M, int K, int rotate,
+                                  void* stream) {
+    if ((K % 256) != 0) return -1;
+    QuantArgs p{x, x_stride, g, g_stride, up_offset, q, scales, nullptr, M, K, rotate, 0, 0, 0, -1, amax, nullptr};
+    if (dtype == DT_BF16) return dispatch_prologue<bf16>(prologue, p, (cudaStream_t)stream);
+    if (dtype == DT_F32) return dispatch_prologue<float>(prologue, p, (cudaStream_t)stream);
+    return -4;
 }

@@ -51,6 +51,41 @@ def quant_rows(x: torch.Tensor, prologue: int = ffi.PRO_PLAIN, rotate: int = 0, 
     return q, scales
 
 
+def quant_rows_amax(x: torch.Tensor, prologue: int = ffi.PRO_PLAIN, rotate: int = 0, *, K: Optional[int] = None,
+                    g: Optional[torch.Tensor] = None, up_offset: int = 0) -> torch.Tensor:
+    """gpu_quant_rows_amax: row maxima after prologue and rotation, f32 [M]."""
+    _cuda(x)
+    M = x.shape[0]
+    K = K if K is not None else x.shape[1]
+    amax = torch.empty((M,), dtype=torch.float32, device=x.device)
+    ok(_lib().gpu_quant_rows_amax(_DT[x.dtype], prologue, _ptr(x), x.stride(0), _ptr(g), g.stride(0) if g is not None else 0,
+                                  up_offset, _ptr(amax), M, K, rotate, _stream()), "gpu_quant_rows_amax")
+    return amax
+
+
+def quant_rows_scaled(x: torch.Tensor, amax: torch.Tensor, prologue: int = ffi.PRO_PLAIN, rotate: int = 0, *,
+                      K: Optional[int] = None, g: Optional[torch.Tensor] = None, up_offset: int = 0):
+    """gpu_quant_rows_scaled: quantize with given row maxima -> (q int8 [M, K], scales f32 [M])."""
+    _cuda(x)
+    M = x.shape[0]
+    K = K if K is not None else x.shape[1]
+    q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    scales = torch.empty((M,), dtype=torch.float32, device=x.device)
+    ok(_lib().gpu_quant_rows_scaled(_DT[x.dtype], prologue, _ptr(x), x.stride(0), _ptr(g),
+                                    g.stride(0) if g is not None else 0, up_offset, _ptr(amax), _ptr(q), _ptr(scales), M, K,
+                                    rotate, _stream()), "gpu_quant_rows_scaled")
+    return q, scales
+
+
+def int8_epilogue(acc, xs, ws, bias=None, *, out_dtype=torch.bfloat16, act: int = 0, rscale=None, resid=None, out=None):
+    """gpu_int8_epilogue: the dequant epilogue over int32 accumulators [M, N] in global memory."""
+    M, N = acc.shape
+    D = out if out is not None else torch.empty((M, N), dtype=out_dtype, device=acc.device)
+    ok(_lib().gpu_int8_epilogue(_ptr(acc), _ptr(xs), _ptr(ws), _ptr(bias), _ptr(rscale), _ptr(resid), _ptr(D), M, N,
+                                _DT[D.dtype], act, _stream()), "gpu_int8_epilogue")
+    return D
+
+
 def rotate_rows_f32(x: torch.Tensor, prologue: int = ffi.PRO_PLAIN, *, K: Optional[int] = None, up_offset: int = 0):
     _cuda(x)
     M = x.shape[0]

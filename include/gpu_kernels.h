@@ -73,6 +73,22 @@ int gpu_int8_gemm_act(const int8_t* A, const int8_t* W, const float* xs, const f
 /* New, for tests: the raw int32 accumulators D[m,n] = sum_k A[m,k] * W[n,k] that the fused forms never expose. */
 int gpu_int8_gemm_acc_i32(const int8_t* A, const int8_t* W, int32_t* D, int64_t M, int64_t N, int64_t K, void* stream);
 
+/* New, for tensor-parallel linears whose K columns are split across devices (the reference is single-device):
+ * two-pass quantization around a max-reduction of the row maxima between the devices. Pass 1 writes the local row
+ * maxima (after prologue and rotation) to amax [M]; pass 2 quantizes with the given maxima. Same argument meaning
+ * and error codes as gpu_quant_rows. With the reduced maxima the codes equal the single-device ones bit for bit. */
+int gpu_quant_rows_amax(int dtype, int prologue, const void* x, int64_t x_stride, const void* g, int64_t g_stride,
+                        int64_t up_offset, float* amax, int M, int K, int rotate, void* stream);
+int gpu_quant_rows_scaled(int dtype, int prologue, const void* x, int64_t x_stride, const void* g, int64_t g_stride,
+                          int64_t up_offset, const float* amax, int8_t* q, float* scales, int M, int K, int rotate,
+                          void* stream);
+
+/* New: the dequant epilogue alone over int32 accumulators [M, N] already in global memory (e.g. partial products of a
+ * row-parallel linear summed by a reduce-scatter): the arithmetic of gpu_int8_gemm (resid == NULL, act == 0),
+ * gpu_int8_gemm_act (act != 0) or gpu_int8_gemm_residual (rscale and resid given; D may alias resid). */
+int gpu_int8_epilogue(const int32_t* acc, const float* xs, const float* ws, const void* bias, const void* rscale,
+                      const void* resid, void* D, int64_t M, int64_t N, int out_dt, int act, void* stream);
+
 /* W6A8: q [N, 3K/4] u8 (per row K/2 nibble bytes then K/4 bytes of top bits), s_rel [N, K/G] fp8-e4m3 ->
  * out int8 [N, K] = clamp(rint((code - 32) * s_rel), +-127). -1 when K % 32 or G % 16.
  * Replaces csrc/h3.cu:40-46 (src/ffi.rs:121). */

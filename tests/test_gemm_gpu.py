@@ -141,3 +141,74 @@ def test_full_size_linearity_and_guard_bands(pkg, dev):
     L.int8_gemm(A1, W, xs, ws, None, out=D)
     assert bool((buf[:pad] == -7).all()) and bool((buf[-pad:] == -7).all())
     assert L.kernel_status() == 0
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 5, 8])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_few_rows_kernel(pkg, oracle, dev, M, dtype):
+    """M <= 8 takes the weight-streaming kernel (adaLN modulation, pooled conditioning): same results, bit for bit."""
+    N, K = 1003 if dtype == torch.float32 else 1000, 3072
+    g, A, W, xs, ws = _operands(M, N, K, 51 + M)
+    bias = (torch.randn(N, generator=g) * 0.5).to(dtype)
+    rs = torch.randn(N, generator=g).to(dtype)
+    rr = torch.randn(M, N, generator=g).to(dtype)
+    acc = oracle.int8_gemm_acc(A, W)
+    d = lambda t: t.to(dev)
+    L = pkg.linear
+    assert_bits_equal(L.int8_gemm_acc_i32(d(A), d(W)), acc, "accumulators")
+    assert_bits_equal(L.int8_gemm(d(A), d(W), d(xs), d(ws), d(bias), out_dtype=dtype),
+                      oracle.epilogue(acc, xs, ws, bias, out_dtype=dtype, contract=3), "plain")
+    assert_bits_equal(L.int8_gemm(d(A), d(W), d(xs), d(ws), None, out_dtype=dtype),
+                      oracle.epilogue(acc, xs, ws, None, out_dtype=dtype, contract=3), "no bias")
+    resid = d(rr).clone()
+    L.int8_gemm(d(A), d(W), d(xs), d(ws), d(bias), out_dtype=dtype, rscale=d(rs), resid=resid, out=resid)
+    assert_bits_equal(resid, oracle.epilogue(acc, xs, ws, bias, rs, rr, out_dtype=dtype, contract=3), "residual in place")
+    got = L.int8_gemm(d(A), d(W), d(xs), d(ws), d(bias), out_dtype=dtype, act=1)
+    assert_close_out(got, oracle.epilogue(acc, xs, ws, bias, out_dtype=dtype, act=1, contract=7), "gelu-tanh", tiny=1e-3)
+
+
+def test_adaln_shape_matches_the_reference(pkg, ref, dev):
+    g, A, W, xs, ws = _operands(1, 18432, 3072, 61)
+    A, W, xs, ws = A.to(dev), W.to(dev), xs.to(dev), ws.to(dev)
+    bias = torch.randn(18432, generator=g).bfloat16().to(dev)
+    assert_bits_equal(pkg.linear.int8_gemm(A, W, xs, ws, bias), ref.int8_gemm(A, W, xs, ws, bias), "adaLN M=1")
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 8192), (100, 384, 16384), (300, 96, 4096), (1000, 256, 6144)])
+def test_k_split_problems(pkg, oracle, dev, M, N, K):
+    """Few tiles and a long K: the tiles are cut along K and meet through atomic adds in global scratch. Two launches in
+    a row also check that the first leaves the scratch (sums and counters) at zero."""
+    g, A, W, xs, ws = _operands(M, N, K, 71)
+    bias = (torch.randn(N, generator=g) * 0.5).bfloat16()
+    acc = oracle.int8_gemm_acc(A, W)
+    want = oracle.epilogue(acc, xs, ws, bias, contract=3)
+    d = lambda t: t.to(dev)
+    for _ in range(2):
+        assert_bits_equal(pkg.linear.int8_gemm_acc_i32(d(A), d(W)), acc, "accumulators")
+        assert_bits_equal(pkg.linear.int8_gemm(d(A), d(W), d(xs), d(ws), d(bias)), want, "bf16 output")
+    assert pkg.linear.kernel_status() == 0
+
+
+def test_two_pass_quantizer_and_epilogue_only(pkg, oracle, dev):
+    """The entry points of the tensor-parallel row-parallel linear: column halves quantized with the reduced row maxima
+    equal the halves of the one-pass codes; the epilogue over summed int32 partials equals the fused one."""
+    g = torch.Generator().manual_seed(81)
+    x = torch.randn(96, 2048, generator=g).bfloat16().to(dev)
+    L = pkg.linear
+    q, s = L.quant_rows(x, 11, 1)
+    halves = [x[:, :1024].contiguous(), x[:, 1024:].contiguous()]
+    amax = torch.stack([L.quant_rows_amax(h, 11, 1) for h in halves]).amax(0)
+    for i, h in enumerate(halves):
+        qi, si = L.quant_rows_scaled(h, amax, 11, 1)
+        assert_bits_equal(qi, q[:, 1024 * i:1024 * (i + 1)].contiguous(), f"codes of half {i}")
+        assert_bits_equal(si, s, "scales")
+    W = torch.randint(-128, 128, (320, 2048), generator=g, dtype=torch.int8).to(dev)
+    ws = (torch.rand(320, generator=g) * 1e-3).to(dev)
+    bias = torch.randn(320, generator=g).bfloat16().to(dev)
+    rs = torch.randn(320, generator=g).bfloat16().to(dev)
+    rr = torch.randn(96, 320, generator=g).bfloat16().to(dev)
+    part = sum(L.int8_gemm_acc_i32(q[:, 1024 * i:1024 * (i + 1)].contiguous(), W[:, 1024 * i:1024 * (i + 1)].contiguous()) for i in range(2))
+    assert_bits_equal(part, L.int8_gemm_acc_i32(q, W), "int32 partials sum to the whole")
+    assert_bits_equal(L.int8_epilogue(part, s, ws, bias), L.int8_gemm(q, W, s, ws, bias), "plain")
+    assert_bits_equal(L.int8_epilogue(part, s, ws, bias, rscale=rs, resid=rr), L.int8_gemm(q, W, s, ws, bias, rscale=rs, resid=rr), "residual")
+    assert_bits_equal(L.int8_epilogue(part, s, ws, bias, act=1), L.int8_gemm(q, W, s, ws, bias, act=1), "gelu")
