@@ -834,6 +834,105 @@ GPU_API int gpu_int8_gemm_acc_i32(const int8_t* A, const int8_t* W, int32_t* D, 
     return run_gemm(EPI_ACC, A, W, nullptr, nullptr, nullptr, nullptr, nullptr, D, M, N, K, 0, 0, (cudaStream_t)stream);
 }
 
+namespace {
+
+// ---- the entry point that allocates nothing ----------------------------------------------------------------------
+// Some hosts of this library cannot call cudaMalloc once they are running: the reference's engine, for one, fills the
+// card up to a watermark with its own allocator and then lives inside that budget (src/comfy_memory.rs), so a library
+// that asks the driver for memory in the middle of a denoising step can fail there, or stall every stream of the device
+// while the driver serves it. For those callers the K-split form of the GEMM gets its scratch (per-chunk arrival
+// counters, then int32 tile sums) from this array, which is part of the loaded module on every GPU until the process
+// exits: 64 KiB of counters + 16 tiles x 256 x 256 x 4 B of sums = 4,259,840 bytes.
+constexpr int kStaticMaxTiles = 16;
+constexpr size_t kStaticCounterBytes = 1 << 16;
+constexpr size_t kStaticScratchBytes = kStaticCounterBytes + (size_t)kStaticMaxTiles * 256 * 256 * sizeof(int);
+static __device__ __align__(256) int g_static_scratch[kStaticScratchBytes / sizeof(int)];
+
+// Device address of the array for the current device. In host code the array's name is only a handle for the runtime,
+// not an address a kernel could use, so the address is looked up once per device and remembered.
+int static_scratch_ptr(int dev, int** out) {
+    static int* ptr[64];
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lk(mu);
+    int*& p = ptr[dev & 63];
+    if (!p) {
+        void* addr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&addr, g_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        p = reinterpret_cast<int*>(addr);
+    }
+    *out = p;
+    return 0;
+}
+
+}  // namespace
+
+// D[M,N] = out((A . W^T) * xs[m] * ws[n] + bias[n]) like gpu_int8_gemm, for problems of at most 16 output tiles
+// (a few hundred rows or columns) with a long K, cut along K so that more SMs stream them. No cudaMalloc, cudaFree or
+// other allocating call is made, now or later: the scratch is the static array above.
+//   -205  the problem needs more than 16 tiles: beyond the array. Use gpu_int8_gemm.
+// The first call on a device looks up the array's address (cudaGetSymbolAddress); make that call before any stream
+// capture starts. Every call zeroes the part of the array it will use (an asynchronous memset on `stream`) because
+// the array keeps whatever the previous call left; two calls that overlap on the GPU (different streams, no
+// dependency) would share counters and sums and corrupt each other: serialise them.
+GPU_API int gpu_int8_gemm_noalloc(const int8_t* A, const int8_t* W, const float* xs, const float* ws, const void* bias,
+                                  void* D, int64_t M, int64_t N, int64_t K, int out_dt, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (M == 0 || N == 0 || K == 0) return 0;
+    if (out_dt < 0 || out_dt > 2) return -200;
+    if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return -200;
+    if ((K % 16) != 0 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return -202;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int clusters = device_sm_count(dev) / 2;
+    GemmParams p{};
+    p.xs = xs, p.ws = ws, p.bias = bias, p.D = D;
+    p.M = (int)M, p.N = (int)N, p.K = (int)K;
+    const int esz = out_dt == DT_F32 ? 4 : 2;
+    auto al16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
+    p.vec_ok = (N % 8 == 0) && al16(D) && al16(ws) && al16(bias);
+    p.tma_store = al16(D) && ((N * esz) % 16 == 0);
+    p.ksub = K <= BK ? 1 : 2;
+    p.k_iters = (int)((K + p.ksub * BK - 1) / (p.ksub * BK));
+    const int bn = choose_bn(M, N, p.k_iters, clusters);
+    p.bn = bn;
+    p.idesc = umma_idesc_i8(2 * BM, bn);
+    const int stage_bytes = p.ksub * (BM * BK + (bn / 2) * BK);
+    const int stages = (kSmemBytes - 1024 - kTailBytes - kStagingBytes) / stage_bytes;
+    p.stages = stages > kMaxStages ? kMaxStages : stages;
+    p.tiles_m = (int)((M + 2 * BM - 1) / (2 * BM));
+    p.tiles_n = (int)((N + bn - 1) / bn);
+    p.num_tiles = p.tiles_m * p.tiles_n;
+    if (p.num_tiles > kStaticMaxTiles) return -205;
+    int splits = clusters / p.num_tiles;
+    if (splits > p.k_iters) splits = p.k_iters;
+    if (splits > 16) splits = 16;
+    const int kps = (p.k_iters + splits - 1) / splits;
+    splits = (p.k_iters + kps - 1) / kps;
+    p.whole_tiles = p.num_tiles, p.splits = 0, p.kps = p.k_iters, p.num_items = p.num_tiles;
+    if (splits >= 2) {
+        int* scratch = nullptr;
+        if (int rc = static_scratch_ptr(dev, &scratch)) return rc;
+        const size_t used = kStaticCounterBytes + (size_t)p.num_tiles * kCountersPerSlot * 32 * 32 * sizeof(int);
+        const cudaError_t e = cudaMemsetAsync(scratch, 0, used, st);
+        if (e != cudaSuccess) return (int)e;
+        p.scratch = scratch;
+        p.partials = scratch + kStaticCounterBytes / sizeof(int);
+        p.whole_tiles = 0, p.splits = splits, p.kps = kps, p.num_items = p.num_tiles * splits;
+    }
+    CUtensorMap ta, tw, td;
+    if (!make_operand_tmap(&ta, A, M, K, BM) || !make_operand_tmap(&tw, W, N, K, bn / 2)) return -203;
+    if (p.tma_store) {
+        if (!make_output_tmap(&td, D, M, N, esz)) return -203;
+    } else {
+        td = ta;
+    }
+    const int grid = 2 * (p.num_items < clusters ? p.num_items : clusters);
+    if (out_dt == DT_F32) return launch_pair<float, EPI_PLAIN>(ta, tw, td, p, grid, st);
+    if (out_dt == DT_F16) return launch_pair<half, EPI_PLAIN>(ta, tw, td, p, grid, st);
+    return launch_pair<bf16, EPI_PLAIN>(ta, tw, td, p, grid, st);
+}
+
 #ifdef GEMM_PROFILE
 GPU_API int gpu_kernels_prof(unsigned long long* out, int clear) {
     cudaError_t e = cudaMemcpyFromSymbol(out, g_prof, sizeof(g_prof));

@@ -70,6 +70,17 @@ int gpu_int8_gemm_residual(const int8_t* A, const int8_t* W, const float* xs, co
 int gpu_int8_gemm_act(const int8_t* A, const int8_t* W, const float* xs, const float* ws, const void* bias, void* D,
                       int64_t M, int64_t N, int64_t K, int out_dt, int act, void* stream);
 
+/* No counterpart in the reference. gpu_int8_gemm for hosts that must not allocate device memory once they run (an
+ * engine that manages the card inside a fixed budget of its own, a latency-critical thread): small-output, long-K
+ * problems (at most 16 tiles of 256 x 256 outputs) are cut along K, and the scratch the slices meet in is a
+ * 4,259,840-byte array inside the loaded module instead of an allocation. Returns -205 when the problem needs more than
+ * the array holds (use gpu_int8_gemm then); other codes as gpu_int8_gemm. Makes no cudaMalloc / cudaFree or other
+ * allocating call. The first call on each device looks up the array's device address: issue it before any stream
+ * capture. The array is shared by every call and keeps the previous call's contents; each call clears what it uses on
+ * `stream`, so calls must not overlap on the GPU (serialise streams that use it). */
+int gpu_int8_gemm_noalloc(const int8_t* A, const int8_t* W, const float* xs, const float* ws, const void* bias, void* D,
+                          int64_t M, int64_t N, int64_t K, int out_dt, void* stream);
+
 /* New, for tests: the raw int32 accumulators D[m,n] = sum_k A[m,k] * W[n,k] that the fused forms never expose. */
 int gpu_int8_gemm_acc_i32(const int8_t* A, const int8_t* W, int32_t* D, int64_t M, int64_t N, int64_t K, void* stream);
 
