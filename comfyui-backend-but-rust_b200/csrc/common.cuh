@@ -241,6 +241,12 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// The same arrival with the default (CTA-scope) release: for hand-offs whose data the consumer reads through the async
+// proxy after the producer's own fence.proxy.async, where the cluster-scope release (measured at about a thousand
+// cycles per arrival on B200) buys nothing.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 // 2-D tiled TMA load issued by one CTA of a pair: data lands in this CTA's shared memory, the byte count is
 // credited to an mbarrier that may live in the peer CTA (shared::cluster address). No multicast.
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap, int x, int y, uint32_t bar_cluster_addr) {

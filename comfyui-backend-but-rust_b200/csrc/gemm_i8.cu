@@ -24,6 +24,7 @@
 #include <cmath>
 #include <cstdlib>
 #include <cuda.h>
+#include <cuda_fp8.h>
 #include <mutex>
 #include <type_traits>
 
@@ -147,17 +148,17 @@ template <> __device__ __forceinline__ void load8<half>(const half* p, float (&y
 // to the output type for the last step; the store rounds).
 //   t0 = float(acc) * xs;  v = out(fma(t0, ws, bias));  RESID: fma(v, rscale, resid);  ACT: act(v)
 // `vs`, when set, points at this warp's staged per-column vectors for these 8 columns in shared memory
-// (ws at vs[0..], bias at vs[128..], rscale at vs[256..], all as f32, zero beyond N).
-template <typename OutT, int EPI>
+// (ws at vs[0..], bias at vs[VS..], rscale at vs[2 VS..], all as f32, zero beyond N; VS = columns a warp stages).
+template <typename OutT, int EPI, int VS = 128>
 __device__ __forceinline__ void epilogue8(const GemmParams& p, const uint32_t* r, int row, int col, float xs_r, bool vec,
                                           float (&y)[8], const float* vs = nullptr) {
     float w8[8], b8[8], rs8[8], rr[8];
     const OutT* rsd = reinterpret_cast<const OutT*>(p.resid) + (int64_t)row * p.N + col;
     if (vs) {
         load8<float>(vs, w8);            // every lane reads the same words: broadcasts
-        load8<float>(vs + 128, b8);
+        load8<float>(vs + VS, b8);
         if (EPI == EPI_RESID) {
-            load8<float>(vs + 256, rs8);
+            load8<float>(vs + 2 * VS, rs8);
             if (vec) load8<OutT>(rsd, rr);
             else {
 #pragma unroll
@@ -241,13 +242,13 @@ __device__ __forceinline__ void chunk_direct(const GemmParams& p, const uint32_t
 // (2-byte outputs) or 128-byte (4-byte outputs) swizzle expects: row r at r * pitch, its 16-byte piece j at
 // piece j ^ f(r). Eight consecutive lanes then hit eight different bank groups.
 // 2-byte outputs: the chunk's 32 values of this lane's row, computed and packed (no shared-memory traffic yet)
-template <typename OutT, int EPI>
+template <typename OutT, int EPI, int VS = 128>
 __device__ __forceinline__ void chunk_compute16(const GemmParams& p, const uint32_t (&r)[32], int row, int col0, float xs_r,
                                                 const float* vs, uint4 (&pk)[4]) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         float y[8];
-        epilogue8<OutT, EPI>(p, r + 8 * j, row, col0 + 8 * j, xs_r, p.vec_ok && col0 + 8 * j + 8 <= p.N, y, vs + 8 * j);
+        epilogue8<OutT, EPI, VS>(p, r + 8 * j, row, col0 + 8 * j, xs_r, p.vec_ok && col0 + 8 * j + 8 <= p.N, y, vs + 8 * j);
         if constexpr (sizeof(OutT) == 2) pk[j] = pack8<OutT>(y);
     }
 }
@@ -804,7 +805,28 @@ int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const f
     return rc;
 }
 
+#include "gemm_w6.inl"
+
 }  // namespace
+
+// New: the W6A8 linear without the decoded copy. The reference expands the packed weight to int8 in a scratch buffer
+// (gpu_w6_decode, csrc/h3.cu:11-46) and then calls gpu_int8_gemm on it (src/h3.rs:1208-1216); these read the packed rows
+// [N, 3K/4] and the e4m3 group scales [N, K/32] directly and expand them in shared memory. Same results as that pair of
+// calls, bit for bit. ws = the per-channel scale (s_channel). K must be a multiple of 128, G must be 32 (-206 otherwise).
+GPU_API int gpu_w6a8_gemm(const int8_t* A, const uint8_t* Wq6, const uint8_t* s_rel, const float* xs, const float* ws,
+                          const void* bias, void* D, int64_t M, int64_t N, int64_t K, int G, int out_dt, void* stream) {
+    return run_w6_gemm(EPI_PLAIN, A, Wq6, s_rel, xs, ws, bias, nullptr, nullptr, D, M, N, K, G, out_dt, (cudaStream_t)stream);
+}
+GPU_API int gpu_w6a8_gemm_residual(const int8_t* A, const uint8_t* Wq6, const uint8_t* s_rel, const float* xs,
+                                   const float* ws, const void* bias, const void* rscale, const void* resid, void* D,
+                                   int64_t M, int64_t N, int64_t K, int G, int out_dt, void* stream) {
+    return run_w6_gemm(EPI_RESID, A, Wq6, s_rel, xs, ws, bias, rscale, resid, D, M, N, K, G, out_dt, (cudaStream_t)stream);
+}
+// For tests: the raw int32 accumulators of the fused-unpack GEMM.
+GPU_API int gpu_w6a8_gemm_acc_i32(const int8_t* A, const uint8_t* Wq6, const uint8_t* s_rel, int32_t* D, int64_t M,
+                                  int64_t N, int64_t K, int G, void* stream) {
+    return run_w6_gemm(EPI_ACC, A, Wq6, s_rel, nullptr, nullptr, nullptr, nullptr, nullptr, D, M, N, K, G, 0, (cudaStream_t)stream);
+}
 
 // D[M,N] = (A[M,K] . W[N,K]^T) * xs[m] * ws[n] + bias[n]; replaces the reference's csrc/gemm.cu:123-129.
 GPU_API int gpu_int8_gemm(const int8_t* A, const int8_t* W, const float* xs, const float* ws, const void* bias, void* D,

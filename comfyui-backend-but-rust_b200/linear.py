@@ -170,6 +170,31 @@ def int8_gemm_acc_i32(A, W):
     return D
 
 
+def w6a8_gemm(A, packed, s_rel, xs, s_channel, bias=None, *, out_dtype=torch.bfloat16, rscale=None, resid=None, out=None,
+              G: int = 32):
+    """gpu_w6a8_gemm / gpu_w6a8_gemm_residual: the W6A8 linear from the packed weight [N, 3K/4] and e4m3 scales [N, K/G]."""
+    _cuda(A)
+    M, K = A.shape
+    N = packed.shape[0]
+    D = out if out is not None else torch.empty((M, N), dtype=out_dtype, device=A.device)
+    lib = _lib()
+    if resid is not None:
+        ok(lib.gpu_w6a8_gemm_residual(_ptr(A), _ptr(packed), _ptr(s_rel), _ptr(xs), _ptr(s_channel), _ptr(bias), _ptr(rscale),
+                                      _ptr(resid), _ptr(D), M, N, K, G, _DT[D.dtype], _stream()), "gpu_w6a8_gemm_residual")
+    else:
+        ok(lib.gpu_w6a8_gemm(_ptr(A), _ptr(packed), _ptr(s_rel), _ptr(xs), _ptr(s_channel), _ptr(bias), _ptr(D), M, N, K, G,
+                             _DT[D.dtype], _stream()), "gpu_w6a8_gemm")
+    return D
+
+
+def w6a8_gemm_acc_i32(A, packed, s_rel, G: int = 32):
+    M, K = A.shape
+    N = packed.shape[0]
+    D = torch.empty((M, N), dtype=torch.int32, device=A.device)
+    ok(_lib().gpu_w6a8_gemm_acc_i32(_ptr(A), _ptr(packed), _ptr(s_rel), _ptr(D), M, N, K, G, _stream()), "gpu_w6a8_gemm_acc_i32")
+    return D
+
+
 def kernel_status() -> int:
     """Device status word (0 = every kernel completed its waits); synchronises the device and clears the word."""
     import ctypes as C

@@ -84,6 +84,20 @@ int gpu_int8_gemm_noalloc(const int8_t* A, const int8_t* W, const float* xs, con
 /* New, for tests: the raw int32 accumulators D[m,n] = sum_k A[m,k] * W[n,k] that the fused forms never expose. */
 int gpu_int8_gemm_acc_i32(const int8_t* A, const int8_t* W, int32_t* D, int64_t M, int64_t N, int64_t K, void* stream);
 
+/* New: the W6A8 linear straight from the packed weight. The reference expands Wq6 to int8 in a scratch buffer with
+ * gpu_w6_decode (csrc/h3.cu:11-46) and calls gpu_int8_gemm on that copy (src/h3.rs:1208-1216); these take the packed rows
+ * Wq6 [N, 3K/4] (nibble plane, then 2-bit plane) and the e4m3 group scales s_rel [N, K/G] and expand them in shared
+ * memory on the way to the tensor cores. Results equal gpu_w6_decode followed by gpu_int8_gemm[_residual] bit for bit;
+ * ws is the per-output-channel scale (s_channel). K % 128 == 0, Wq6 16-byte and s_rel 4-byte aligned (-202), G == 32
+ * (-206). gpu_w6a8_gemm_acc_i32 (for tests) returns the raw int32 accumulators. */
+int gpu_w6a8_gemm(const int8_t* A, const uint8_t* Wq6, const uint8_t* s_rel, const float* xs, const float* ws,
+                  const void* bias, void* D, int64_t M, int64_t N, int64_t K, int G, int out_dt, void* stream);
+int gpu_w6a8_gemm_residual(const int8_t* A, const uint8_t* Wq6, const uint8_t* s_rel, const float* xs, const float* ws,
+                           const void* bias, const void* rscale, const void* resid, void* D, int64_t M, int64_t N,
+                           int64_t K, int G, int out_dt, void* stream);
+int gpu_w6a8_gemm_acc_i32(const int8_t* A, const uint8_t* Wq6, const uint8_t* s_rel, int32_t* D, int64_t M, int64_t N,
+                          int64_t K, int G, void* stream);
+
 /* New, for tensor-parallel linears whose K columns are split across devices (the reference is single-device):
  * two-pass quantization around a max-reduction of the row maxima between the devices. Pass 1 writes the local row
  * maxima (after prologue and rotation) to amax [M]; pass 2 quantizes with the given maxima. Same argument meaning
