@@ -22,7 +22,8 @@
 #define W6P_LAP(slot, cond)
 #endif
 constexpr int kW6EpiWarps = 4;
-constexpr int kW6UnpackWarps = 8;
+constexpr int kW6Groups = 3;                     // unpack groups of four warps, taking K boxes in turn
+constexpr int kW6UnpackWarps = 4 * kW6Groups;
 constexpr int kW6Threads = 32 * (2 + kW6EpiWarps + kW6UnpackWarps);
 constexpr int kW6StagingPerWarp = 6144;   // output chunk (2 KB, or 4 KB for 4-byte outputs) + 3 KB of staged vectors
 constexpr int kW6StagingBytes = kW6EpiWarps * kW6StagingPerWarp;
@@ -45,7 +46,9 @@ struct W6Extra {
 __device__ __forceinline__ void w6_group(const uint4 l, uint32_t ha, uint32_t hb, uint32_t sb, uint32_t (&o)[8]) {
     const uint32_t lw[4] = {l.x, l.y, l.z, l.w};
     const uint32_t hv[2] = {ha, hb};
-    if (sb == 0x38u) {
+    // The three forms are chosen per warp, not per lane: lanes hold different rows with different scales, and a branch that
+    // splits the warp costs the sum of its sides. The general form is right for every scale, the clamped one too.
+    if (__all_sync(0xffffffffu, sb == 0x38u)) {
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const uint32_t h = hv[w >> 1] >> (16 * (w & 1));
@@ -58,7 +61,7 @@ __device__ __forceinline__ void w6_group(const uint4 l, uint32_t ha, uint32_t hb
     }
     const __half2 s2 = __half2half2(__half(__nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)sb, __NV_E4M3)));
     const __half2 magic = __float2half2_rn(1536.f);
-    const bool clamp = (sb & 0x7fu) >= 0x48u;              // |s| >= 4 (or NaN): 32 * |s| can pass 127
+    const bool clamp = __any_sync(0xffffffffu, (sb & 0x7fu) >= 0x48u);   // some |s| >= 4 (or NaN): 32 * |s| can pass 127
     const __half2 c2 = __hmul2(__float2half2_rn(-1056.f), s2);
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
@@ -146,7 +149,7 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             mbar_init(bar_pfull + 8 * i, 1);
         }
         for (int i = 0; i < SB; ++i) {
-            mbar_init(bar_bfull + 8 * i, kW6UnpackWarps);   // the four warps of one group in each CTA
+            mbar_init(bar_bfull + 8 * i, 2 * 4);   // the four warps of one group in each CTA
             mbar_init(bar_bempty + 8 * i, 1);
         }
         for (int i = 0; i < 2; ++i) {
@@ -203,7 +206,11 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             uint32_t tphase = 0;
             bool ok = true;
             for (int t = cluster_id; t < p.num_tiles && ok; t += nclusters) {
-                if (!mbar_wait(bar_tempty + 8 * buf, tphase ^ 1u, abort_s, ST_TIMEOUT_TMEM_EMPTY)) break;
+                {
+                    W6P_BEGIN();
+                    if (!mbar_wait(bar_tempty + 8 * buf, tphase ^ 1u, abort_s, ST_TIMEOUT_TMEM_EMPTY)) break;
+                    W6P_LAP(7, true);
+                }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * 256;
                 for (int kb = 0; kb < p.k_iters; ++kb) {
@@ -232,17 +239,17 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             }
         }
     } else if (warp >= 2 + kW6EpiWarps) {
-        // ---------------- unpack warps: two groups of four warps take alternate K boxes; one thread per weight row ----------------
+        // ---------------- unpack warps: groups of four warps take K boxes in turn; one thread per weight row ----------------
         // Every barrier operation and the proxy fence cost a warp on the order of a hundred cycles whatever the amount of
-        // data, so a group pays them once per 128 elements of its rows, and the two groups overlap each other's waits.
-        const int uw = warp - (2 + kW6EpiWarps);                 // 0..7
+        // data, so a group pays them once per 128 elements of its rows, and the groups overlap one another's waits.
+        const int uw = warp - (2 + kW6EpiWarps);
         const int grp = uw >> 2;
         const int r = 32 * (uw & 3) + lane;                      // row of the half tile
         const bool has_row = r < rows_w;
         const uint32_t bfull_leader = mapa_shared(bar_bfull, 0);
         const int sw_lo = (r >> 1) & 3, sw_hi = (r >> 2) & 1, sw_out = r & 7;
         const bool wide = (x6.srel_pitch & 15) == 0 && ((uintptr_t)x6.s_rel & 15) == 0;   // scale rows readable 16 bytes at a time
-        int sa = 0, sb = 0, step = 0;
+        int sa = 0, sb = 0, turn = 0;           // turn: which group takes the current K box
         uint32_t pa = 0, pb = 0;
         bool ok = true;
         for (int t = cluster_id; t < p.num_tiles && ok; t += nclusters) {
@@ -265,12 +272,12 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 return v;
             };
             sc_next = fetch(0);
-            for (int kb = 0; kb < p.k_iters; ++kb, ++step) {
+            for (int kb = 0; kb < p.k_iters; ++kb) {
                 if ((kb & 3) == 0) {
                     sc_cur = sc_next;
                     if (kb + 4 < p.k_iters) sc_next = fetch((kb >> 2) + 1);
                 }
-                if ((step & 1) == grp) {
+                if (turn == grp) {
                     const int q = kb & 3;
                     const uint32_t sr = q == 0 ? sc_cur.x : q == 1 ? sc_cur.y : q == 2 ? sc_cur.z : sc_cur.w;
                     W6P_BEGIN();
@@ -280,11 +287,11 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                     W6P_LAP(3, uw == 0 && lane == 0);
                     if (!__all_sync(0xffffffffu, mbar_try_wait(bar_bempty + 8 * sb, pb ^ 1u)) &&
                         !mbar_wait_warp(bar_bempty + 8 * sb, pb ^ 1u, abort_s, ST_TIMEOUT_UNPACK)) { ok = false; break; }
-                    W6P_LAP(5, uw == 0 && lane == 0);
-                    if (has_row) {
-                        const uint8_t* lo = sm + (sLo - base) + sa * lo_bytes + r * 64;
-                        const uint8_t* hi = sm + (sHi - base) + sa * hi_bytes + r * 32;
-                        uint8_t* out = sm + (sB - base) + sb * b_bytes + r * 128;
+                    {
+                        const int rr = has_row ? r : 0;    // lanes beyond the tile's rows redo row 0 (warp votes below) and store nothing
+                        const uint8_t* lo = sm + (sLo - base) + sa * lo_bytes + rr * 64;
+                        const uint8_t* hi = sm + (sHi - base) + sa * hi_bytes + rr * 32;
+                        uint8_t* out = sm + (sB - base) + sb * b_bytes + rr * 128;
                         const uint4 h0 = *reinterpret_cast<const uint4*>(hi + ((0 ^ sw_hi) << 4));
                         const uint4 h1 = *reinterpret_cast<const uint4*>(hi + ((1 ^ sw_hi) << 4));
                         const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
@@ -293,16 +300,18 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                             const uint4 l = *reinterpret_cast<const uint4*>(lo + ((c ^ sw_lo) << 4));
                             uint32_t o[8];
                             w6_group(l, hw[2 * c], hw[2 * c + 1], (sr >> (8 * c)) & 0xffu, o);
-                            *reinterpret_cast<uint4*>(out + (((2 * c) ^ sw_out) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-                            *reinterpret_cast<uint4*>(out + (((2 * c + 1) ^ sw_out) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+                            if (has_row) {
+                                *reinterpret_cast<uint4*>(out + (((2 * c) ^ sw_out) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                                *reinterpret_cast<uint4*>(out + (((2 * c + 1) ^ sw_out) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+                            }
                         }
                     }
                     W6P_LAP(6, uw == 0 && lane == 0);
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_remote(bfull_leader + 8 * sb);
-                    W6P_LAP(7, uw == 0 && lane == 0);
                 }
+                if (++turn == kW6Groups) turn = 0;
                 if (++sa == SA) { sa = 0; pa ^= 1u; }
                 if (++sb == SB) { sb = 0; pb ^= 1u; }
             }
@@ -345,6 +354,7 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 __syncwarp();
             }
             if (!mbar_wait_warp_relaxed(bar_tfull + 8 * buf, tphase, abort_s, ST_TIMEOUT_TMEM_FULL)) break;
+            W6P_BEGIN();
             tc_fence_after();
             const uint32_t taddr = tmem_base + buf * 256 + ((uint32_t)(quad * 32) << 16);
             uint32_t ra[32];
@@ -379,6 +389,7 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa_shared(bar_tempty + 8 * buf, 0));
+            W6P_LAP(5, threadIdx.x == 64);
             buf ^= 1;
             if (buf == 0) tphase ^= 1u;
         }
