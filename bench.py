@@ -37,13 +37,25 @@ WORKLOAD = "convrot_int8_mmdit_mlp_pair_M4352_K3072_N12288"
 INT8_NOMINAL_TOPS = 4500.0
 
 
+# --mode kernel: one kernel of the step alone, on the step's own buffers (what profiles/ summarises)
+KERNELS = {
+    "quant_rot": lambda b, I: I.quant_rows(b.h, 0, 1, q=b.a2, scales=b.xs2),             # M=4352 K=12288, PLAIN + R256
+    "quant_gelu": lambda b, I: I.quant_rows(b.h, 11, 1, q=b.a2, scales=b.xs2),           # the same with the GELU-tanh prologue
+    "quant_in": lambda b, I: I.quant_rows(b.x, 0, 1, q=b.a1, scales=b.xs1),              # M=4352 K=3072
+    "gemm_up": lambda b, I: I.int8_gemm(b.a1, b.w1, b.xs1, b.s1, b.b1, out=b.h),         # M=4352 K=3072 N=12288
+    "gemm_down": lambda b, I: I.int8_gemm(b.a2, b.w2, b.xs2, b.s2, b.b2, rscale=b.ones, resid=b.x, out=b.out),
+}
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
-    ap.add_argument("--mode", default="replicas", choices=["replicas", "tp"])
+    ap.add_argument("--mode", default="replicas", choices=["replicas", "tp", "kernel"])
+    ap.add_argument("--kernel", default="gemm_up", choices=sorted(KERNELS),
+                    help="--mode kernel: the one kernel to launch --steps times (the command ncu captures are taken from)")
     ap.add_argument("--cpu-rows", type=int, default=4352, help="rows of the batch the CPU baseline computes")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
@@ -281,6 +293,13 @@ def main():
     # token-sharded replicas: every rank owns one batch of the block (weights replicated), no data-path collective
     up, down, x, w1, w2, b1, b2 = host_inputs(wl, rank)
     blk = Block(impl, torch, dev, up, down, x, w1, w2, b1, b2, fused)
+    if args.mode == "kernel":
+        blk.step()                                   # fills every buffer the single kernels read
+        fn = KERNELS[args.kernel]
+        k_ms = time_steps(torch, lambda: fn(blk, impl), args.steps, args.warmup) / args.steps
+        print(json.dumps({"kernel": args.kernel, "us_per_launch": k_ms * 1e3, "launches": args.steps,
+                          "kernel_status": pkg.linear.kernel_status()}), flush=True)
+        return
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()

@@ -67,7 +67,19 @@ struct QuantArgs {
     int lut;            // table index of the prologue (read through L1), or -1
     const float* amax_in;   // when set: row maxima to quantize with (rows whose columns are split across devices)
     float* amax_out;        // when set: write each row's maximum here and stop (first pass of the same)
+    // normalising prologues
+    const float* norm_w;    // RMS / LAYERNORM weight [K] (nullable), LN_AFFINE weight
+    const float* norm_b;    // LN_AFFINE bias [K]
+    float eps;
+    const void* mod_scale;  // [K] in the activation dtype (nullable except ADALN)
+    const void* mod_shift;
 };
+
+template <int PRO> __host__ __device__ constexpr bool is_ln() { return PRO == PRO_LAYERNORM || PRO == PRO_LN_MOD || PRO == PRO_LN_AFFINE; }
+template <int PRO> __host__ __device__ constexpr bool is_norm() { return PRO == PRO_RMS || PRO == PRO_ADALN || is_ln<PRO>(); }
+// floats of shared memory a row needs for the sums of a normalising prologue: one partial per thread of the
+// reference's block (ceil(K / 1024) warps), 32 warp sums, the total
+__host__ __device__ inline int norm_words(int K) { return (((K >> 8) + 3) >> 2) * 32 + 33; }
 
 constexpr int kGroupWords = 304;   // 256 elements + 4 words of padding per 32, rounded so that groups sit 16 banks apart
 
@@ -155,6 +167,37 @@ __device__ __forceinline__ uint32_t quant2(float2 v, float st, float rcp, bool f
     return (uint32_t)(qx & 0xff) | ((uint32_t)(qy & 0xff) << 8);
 }
 
+// 8 consecutive per-column values as floats
+__device__ __forceinline__ void load8v(const float* p, float (&v)[8]) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+}
+__device__ __forceinline__ void load8v(const bf16* p, float (&v)[8]) {
+    const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[2 * i] = __uint_as_float(w[i] << 16), v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+}
+
+// The reference's soft-capped gated activation (csrc/common.cuh:73-91), operation for operation.
+__device__ __forceinline__ float stable_tanh_f(float x) {
+    const float t = expm1f(__fmul_rn(-2.f, fabsf(x)));
+    return copysignf(__fdiv_rn(-t, __fadd_rn(t, 2.f)), x);
+}
+__device__ __forceinline__ float situ_f(float hidden, float gate) {
+    const float a = __fdiv_rn(__fmul_rn(4.f, stable_tanh_f(__fdiv_rn(gate, 4.f))), __fadd_rn(1.f, expf(-gate)));
+    return __fmul_rn(a, __fmul_rn(25.f, stable_tanh_f(__fdiv_rn(hidden, 25.f))));
+}
+__device__ __forceinline__ float tanh_approx_f(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float situ_fast_f(float hidden, float gate) {
+    return __fmul_rn(__fdividef(__fmul_rn(4.f, tanh_approx_f(__fmul_rn(gate, 0.25f))), __fadd_rn(1.f, __expf(-gate))),
+                     __fmul_rn(25.f, tanh_approx_f(__fmul_rn(hidden, 0.04f))));
+}
+
 template <typename T, int PRO, int MAXT>
 __global__ void __launch_bounds__(MAXT) quant_rows_kernel(const QuantArgs p) {
     extern __shared__ __align__(16) uint8_t smem[];
@@ -163,6 +206,8 @@ __global__ void __launch_bounds__(MAXT) quant_rows_kernel(const QuantArgs p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     float* tbuf = reinterpret_cast<float*>(after_lut) + (warp * 4 + (lane >> 3)) * kGroupWords;   // this group's buffer
     unsigned* amax_s = reinterpret_cast<unsigned*>(after_lut + (size_t)nwarps * 4 * kGroupWords * 4);   // [3][rows]
+
+    float* norm_s = reinterpret_cast<float*>(amax_s + 3 * p.rows_per_cta);   // [rows][norm_words(K)], normalising prologues only
 
     for (int i = threadIdx.x; i < 3 * p.rows_per_cta; i += blockDim.x) amax_s[i] = 0u;
     __syncthreads();
@@ -198,6 +243,100 @@ __global__ void __launch_bounds__(MAXT) quant_rows_kernel(const QuantArgs p) {
             for (int i = 0; i < 32; ++i) {
                 if (sizeof(T) == 2 && p.lut >= 0) v[i] = lut_f(lut, v[i]);
                 else v[i] = rnd<T>(PRO == PRO_SILU ? silu_f(v[i]) : PRO == PRO_GELU ? gelu_f(v[i]) : gelu_tanh_f(v[i]));
+            }
+        } else if (PRO == PRO_SITU || PRO == PRO_SITU_FAST) {
+            float u[32];   // the gate half of the row; the product is not rounded here (csrc/kernels.cu:107-112)
+            load32<T>(x + p.up_offset, u);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = PRO == PRO_SITU ? situ_f(v[i], u[i]) : situ_fast_f(v[i], u[i]);
+        }
+
+        if constexpr (is_norm<PRO>()) {
+            // Row statistics in the reference's order of additions (csrc/kernels.cu:113-147, csrc/common.cuh:30-55), so
+            // that the sums, and everything after them, come out bit for bit: there a block of nwr = ceil(K / 1024)
+            // warps holds the row, warp w the groups w, w + nwr, ..., lane l elements 8 l .. 8 l + 7 of each; a thread
+            // adds its elements in that order, then a xor-shuffle tree runs over the lanes and another over the warps.
+            // Here a thread holds four such 8-runs of one group, so the running sums pass from group to group through
+            // shared memory, one round per group of a reference warp.
+            const int ngroups = p.K >> 8, nwr = (ngroups + 3) >> 2, words = nwr * 32 + 33;
+            const int nrounds = (ngroups + nwr - 1) / nwr;
+            float* part = norm_s + rloc * words;
+            const int rgi = grp / nwr, rw = grp - rgi * nwr;
+            auto row_sum = [&](bool squares) -> float {
+                for (int round = 0; round < nrounds; ++round) {
+                    if (rgi == round) {
+#pragma unroll
+                        for (int sub = 0; sub < 4; ++sub) {
+                            float* slot = part + rw * 32 + 4 * t8 + sub;
+                            float ss = round ? *slot : 0.f;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const float e = v[8 * sub + j];
+                                ss = squares ? __fmaf_rn(e, e, ss) : __fadd_rn(ss, e);
+                            }
+                            *slot = ss;
+                        }
+                    }
+                    __syncthreads();
+                }
+                for (int pi = warp; pi < p.rows_per_cta * nwr; pi += nwarps) {
+                    const int row = pi / nwr, ww = pi - row * nwr;
+                    float* pr = norm_s + row * words;
+                    float t = pr[ww * 32 + lane];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) t = __fadd_rn(t, __shfl_xor_sync(0xffffffffu, t, o));
+                    if (lane == 0) pr[nwr * 32 + ww] = t;
+                }
+                __syncthreads();
+                for (int row = warp; row < p.rows_per_cta; row += nwarps) {
+                    float* pr = norm_s + row * words;
+                    float t = lane < nwr ? pr[nwr * 32 + lane] : 0.f;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) t = __fadd_rn(t, __shfl_xor_sync(0xffffffffu, t, o));
+                    if (lane == 0) pr[nwr * 32 + 32] = t;
+                }
+                __syncthreads();
+                return part[nwr * 32 + 32];
+            };
+            if constexpr (is_ln<PRO>()) {
+                const float mean = __fdiv_rn(row_sum(false), (float)p.K);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __fsub_rn(v[i], mean);
+            }
+            const float rstd = rsqrtf(__fadd_rn(__fdiv_rn(row_sum(true), (float)p.K), p.eps));
+            const T* ms_p = reinterpret_cast<const T*>(p.mod_scale);
+            const T* sh_p = reinterpret_cast<const T*>(p.mod_shift);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                float ms[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, sh[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, nw[8], nb[8];
+                if (ms_p) load8v(ms_p + col + 8 * c, ms), load8v(sh_p + col + 8 * c, sh);
+                const bool has_w = p.norm_w != nullptr;
+                if (has_w) load8v(p.norm_w + col + 8 * c, nw);
+                if (PRO == PRO_LN_AFFINE) load8v(p.norm_b + col + 8 * c, nb);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    float n = __fmul_rn(v[8 * c + j], rstd);
+                    if (PRO == PRO_ADALN) {          // one rounding
+                        n = rnd<T>(__fmaf_rn(n, __fadd_rn(1.f, ms[j]), sh[j]));
+                    } else if (PRO == PRO_LN_MOD) {  // one rounding after the norm, one after the multiply-add
+                        n = rnd<T>(__fmaf_rn(rnd<T>(n), rnd<T>(__fadd_rn(1.f, ms[j])), sh[j]));
+                    } else if (PRO == PRO_LN_AFFINE) {
+                        n = rnd<T>(__fmaf_rn(n, nw[j], nb[j]));
+                    } else {                          // RMS, LAYERNORM: every step rounded
+                        if (has_w) n = __fmul_rn(n, nw[j]);
+                        n = rnd<T>(n);
+                        if (ms_p) {
+                            const float a = rnd<T>(__fadd_rn(1.f, ms[j]));
+                            // f32 rows: nothing rounds between the product and the sum, and whether they fuse into one
+                            // multiply-add is the compiler's choice. In the reference as nvcc 12.9 builds it, LAYERNORM
+                            // fuses everywhere and RMS only in the last of its four unrolled group iterations (found by
+                            // comparing outputs); that build is what these results are pinned to.
+                            if (sizeof(T) == 4 && (PRO == PRO_LAYERNORM || rgi == 3)) n = __fmaf_rn(a, n, sh[j]);
+                            else n = rnd<T>(__fadd_rn(rnd<T>(__fmul_rn(a, n)), sh[j]));
+                        }
+                    }
+                    v[8 * c + j] = n;
+                }
             }
         }
 
@@ -365,7 +504,8 @@ int launch_quant(QuantArgs& p, cudaStream_t st) {
     p.rows_per_cta = rows;
     p.nblocks = (p.M + rows - 1) / rows;
     const int threads = rows * p.tpr;
-    const size_t smem = (size_t)(threads / 32) * 4 * kGroupWords * 4 + 3 * rows * 4;
+    const size_t smem = (size_t)(threads / 32) * 4 * kGroupWords * 4 + 3 * rows * 4 +
+                        (is_norm<PRO>() ? (size_t)rows * norm_words(p.K) * 4 : 0);
     const int grid = p.nblocks;
     if (threads > 512) return launch_cfg<T, PRO, 1024>(p, threads, smem, grid, st);
     return launch_cfg<T, PRO, 512>(p, threads, smem, grid, st);
@@ -380,7 +520,14 @@ int dispatch_prologue(int prologue, QuantArgs& p, cudaStream_t st) {
         case PRO_SILU: return launch_quant<T, PRO_SILU>(p, st);
         case PRO_GELU: return launch_quant<T, PRO_GELU>(p, st);
         case PRO_GELU_TANH: return launch_quant<T, PRO_GELU_TANH>(p, st);
-        // the normalising prologues (RMS, LAYERNORM, ADALN, SITU, LN_MOD, LN_AFFINE...) are not built yet
+        case PRO_SITU: return launch_quant<T, PRO_SITU>(p, st);
+        case PRO_SITU_FAST: return launch_quant<T, PRO_SITU_FAST>(p, st);
+        case PRO_RMS: return launch_quant<T, PRO_RMS>(p, st);
+        case PRO_LAYERNORM: return launch_quant<T, PRO_LAYERNORM>(p, st);
+        case PRO_LN_MOD: return launch_quant<T, PRO_LN_MOD>(p, st);
+        case PRO_ADALN: return p.mod_scale && p.mod_shift ? launch_quant<T, PRO_ADALN>(p, st) : -3;
+        // LN_AFFINE needs the bias that only gpu_quant_rows_b carries (the reference reads a null pointer there)
+        case PRO_LN_AFFINE: return p.norm_w && p.norm_b ? launch_quant<T, PRO_LN_AFFINE>(p, st) : -3;
         default: return -3;
     }
 }
@@ -392,22 +539,35 @@ int dispatch_prologue(int prologue, QuantArgs& p, cudaStream_t st) {
 GPU_API int gpu_quant_rows(int dtype, int prologue, const void* x, int64_t x_stride, const void* g, int64_t g_stride,
                            int64_t up_offset, const float* norm_w, float eps, const void* mod_scale, const void* mod_shift,
                            int8_t* q, float* scales, int M, int K, int rotate, void* stream) {
-    (void)norm_w, (void)eps, (void)mod_scale, (void)mod_shift;
     if ((K % 256) != 0) return -1;
-    QuantArgs p{x, x_stride, g, g_stride, up_offset, q, scales, nullptr, M, K, rotate, 0, 0, 0, -1, nullptr, nullptr};
+    QuantArgs p{x, x_stride, g, g_stride, up_offset, q, scales, nullptr, M, K, rotate, 0, 0, 0, -1, nullptr, nullptr,
+                norm_w, nullptr, eps, mod_scale, mod_shift};
     if (dtype == DT_BF16) return dispatch_prologue<bf16>(prologue, p, (cudaStream_t)stream);
     if (dtype == DT_F32) return dispatch_prologue<float>(prologue, p, (cudaStream_t)stream);
     return -4;
 }
 
+// gpu_quant_rows with a LayerNorm bias (csrc/kernels.cu:301-314): bf16 only (-4), prologues LN_MOD and LN_AFFINE (-3).
+GPU_API int gpu_quant_rows_b(int dtype, int prologue, const void* x, int64_t x_stride, const float* norm_w, const float* norm_b,
+                             float eps, const void* mod_scale, const void* mod_shift, int8_t* q, float* scales, int M, int K,
+                             int rotate, void* stream) {
+    if ((K % 256) != 0) return -1;
+    if (dtype != DT_BF16) return -4;
+    if (prologue != PRO_LN_MOD && prologue != PRO_LN_AFFINE) return -3;
+    QuantArgs p{x, x_stride, nullptr, 0, 0, q, scales, nullptr, M, K, rotate, 0, 0, 0, -1, nullptr, nullptr,
+                norm_w, norm_b, eps, mod_scale, mod_shift};
+    return dispatch_prologue<bf16>(prologue, p, (cudaStream_t)stream);
+}
+
 // Prologue + rotation, fp32 rows out (the weight-only int8 path's activation side; csrc/kernels.cu:316-327).
 GPU_API int gpu_rotate_rows_f32(int prologue, const float* x, int64_t x_stride, int64_t up_offset, const float* norm_w,
                                 float eps, float* out, int M, int K, void* stream) {
-    (void)norm_w, (void)eps;
     if ((K % 256) != 0) return -1;
-    QuantArgs p{x, x_stride, nullptr, 0, up_offset, nullptr, nullptr, out, M, K, 1, 0, 0, 0, -1, nullptr, nullptr};
+    QuantArgs p{x, x_stride, nullptr, 0, up_offset, nullptr, nullptr, out, M, K, 1, 0, 0, 0, -1, nullptr, nullptr,
+                norm_w, nullptr, eps, nullptr, nullptr};
     switch (prologue) {
         case PRO_PLAIN: return launch_quant<float, PRO_PLAIN>(p, (cudaStream_t)stream);
+        case PRO_RMS: return launch_quant<float, PRO_RMS>(p, (cudaStream_t)stream);
         case PRO_SWIGLU: return launch_quant<float, PRO_SWIGLU>(p, (cudaStream_t)stream);
         default: return -3;
     }

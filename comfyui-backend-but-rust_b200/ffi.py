@@ -24,6 +24,7 @@ i32, i64, u64, f32 = C.c_int, C.c_int64, C.c_uint64, C.c_float
 # name -> argument types (all return int unless noted), in the order of include/gpu_kernels.h
 SIGNATURES = {
     "gpu_quant_rows": [i32, i32, P, i64, P, i64, i64, P, f32, P, P, P, P, i32, i32, i32, P],
+    "gpu_quant_rows_b": [i32, i32, P, i64, P, P, f32, P, P, P, P, i32, i32, i32, P],
     "gpu_rotate_rows_f32": [i32, P, i64, i64, P, f32, P, i32, i32, P],
     "gpu_sd_quant_rows": [P, i64, P, P, i32, i32, i32, P],
     "gpu_int8_gemm": [P, P, P, P, P, P, i64, i64, i64, i32, P],

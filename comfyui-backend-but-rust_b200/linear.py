@@ -39,15 +39,24 @@ def _cuda(t: torch.Tensor) -> torch.Tensor:
 
 def quant_rows(x: torch.Tensor, prologue: int = ffi.PRO_PLAIN, rotate: int = 0, *, K: Optional[int] = None,
                g: Optional[torch.Tensor] = None, up_offset: int = 0, q: Optional[torch.Tensor] = None,
-               scales: Optional[torch.Tensor] = None):
-    """gpu_quant_rows: x [M, >=K] bf16/f32 -> (q int8 [M, K], scales f32 [M])."""
+               scales: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None,
+               norm_b: Optional[torch.Tensor] = None, eps: float = 0.0, mod_scale: Optional[torch.Tensor] = None,
+               mod_shift: Optional[torch.Tensor] = None):
+    """gpu_quant_rows (gpu_quant_rows_b when a LayerNorm bias is given): x [M, >=K] bf16/f32 -> (q int8 [M, K],
+    scales f32 [M]). norm_w / norm_b f32 [K]; mod_scale / mod_shift [K] in x's dtype."""
     _cuda(x)
     M = x.shape[0]
     K = K if K is not None else x.shape[1]
     q = q if q is not None else torch.empty((M, K), dtype=torch.int8, device=x.device)
     scales = scales if scales is not None else torch.empty((M,), dtype=torch.float32, device=x.device)
+    if norm_b is not None:
+        ok(_lib().gpu_quant_rows_b(_DT[x.dtype], prologue, _ptr(x), x.stride(0), _ptr(norm_w), _ptr(norm_b), eps,
+                                   _ptr(mod_scale), _ptr(mod_shift), _ptr(q), _ptr(scales), M, K, rotate, _stream()),
+           "gpu_quant_rows_b")
+        return q, scales
     ok(_lib().gpu_quant_rows(_DT[x.dtype], prologue, _ptr(x), x.stride(0), _ptr(g), g.stride(0) if g is not None else 0,
-                             up_offset, 0, 0.0, 0, 0, _ptr(q), _ptr(scales), M, K, rotate, _stream()), "gpu_quant_rows")
+                             up_offset, _ptr(norm_w), eps, _ptr(mod_scale), _ptr(mod_shift), _ptr(q), _ptr(scales), M, K,
+                             rotate, _stream()), "gpu_quant_rows")
     return q, scales
 
 
@@ -86,12 +95,13 @@ def int8_epilogue(acc, xs, ws, bias=None, *, out_dtype=torch.bfloat16, act: int 
     return D
 
 
-def rotate_rows_f32(x: torch.Tensor, prologue: int = ffi.PRO_PLAIN, *, K: Optional[int] = None, up_offset: int = 0):
+def rotate_rows_f32(x: torch.Tensor, prologue: int = ffi.PRO_PLAIN, *, K: Optional[int] = None, up_offset: int = 0,
+                    norm_w: Optional[torch.Tensor] = None, eps: float = 0.0):
     _cuda(x)
     M = x.shape[0]
     K = K if K is not None else x.shape[1]
     out = torch.empty((M, K), dtype=torch.float32, device=x.device)
-    ok(_lib().gpu_rotate_rows_f32(prologue, _ptr(x), x.stride(0), up_offset, 0, 0.0, _ptr(out), M, K, _stream()),
+    ok(_lib().gpu_rotate_rows_f32(prologue, _ptr(x), x.stride(0), up_offset, _ptr(norm_w), eps, _ptr(out), M, K, _stream()),
        "gpu_rotate_rows_f32")
     return out
 

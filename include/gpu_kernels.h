@@ -39,6 +39,13 @@ int gpu_quant_rows(int dtype, int prologue, const void* x, int64_t x_stride, con
                    int64_t up_offset, const float* norm_w, float eps, const void* mod_scale, const void* mod_shift,
                    int8_t* q, float* scales, int M, int K, int rotate, void* stream);
 
+/* gpu_quant_rows for the LayerNorm prologues that carry a bias: LN_AFFINE (norm_w, norm_b [K] f32) and LN_MOD
+ * (mod_scale, mod_shift [K] bf16). bf16 input only (-4), other prologues -3.
+ * Replaces csrc/kernels.cu:301-314 (src/ffi.rs:143). */
+int gpu_quant_rows_b(int dtype, int prologue, const void* x, int64_t x_stride, const float* norm_w, const float* norm_b,
+                     float eps, const void* mod_scale, const void* mod_shift, int8_t* q, float* scales, int M, int K,
+                     int rotate, void* stream);
+
 /* Prologue + rotation, rotated rows written as f32 [M, K] (weight-only int8 layers' activation side).
  * Replaces csrc/kernels.cu:316-327 (src/ffi.rs:35). */
 int gpu_rotate_rows_f32(int prologue, const float* x, int64_t x_stride, int64_t up_offset, const float* norm_w, float eps,

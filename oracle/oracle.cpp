@@ -72,6 +72,14 @@ inline float e4m3_to_f(uint8_t v) {
 inline float silu_f(float x) { return x / (1.f + expf(-x)); }
 inline float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
 inline float gelu_f(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+// csrc/common.cuh:73-81: tanh through expm1 (accurate near zero) and the soft-capped gated activation built on it
+inline float stable_tanh(float x) {
+    const float t = expm1f(-2.f * fabsf(x));
+    return copysignf(-t / (t + 2.f), x);
+}
+inline float situ_f(float hidden, float gate) {
+    return 4.f * stable_tanh(gate / 4.f) / (1.f + expf(-gate)) * (25.f * stable_tanh(hidden / 25.f));
+}
 inline float gelu_tanh_f(float x, int contract) {
     const float k0 = 0.7978845608028654f, k1 = 0.044715f;
     // nvcc contracts x + k1*x*x*x into an fma in the reference build; `contract` restates that.
@@ -109,7 +117,7 @@ inline int8_t to_i8(float t, float lo) {  // (int8_t)fminf(127, fmaxf(lo, nearby
 }
 
 enum { PRO_PLAIN = 0, PRO_RMS = 1, PRO_GATE = 2, PRO_SWIGLU = 3, PRO_LAYERNORM = 4, PRO_SILU = 5, PRO_GELU = 6,
-       PRO_ADALN = 7, PRO_GELU_TANH = 11 };  // src/ffi.rs:15-29
+       PRO_ADALN = 7, PRO_SITU = 8, PRO_LN_MOD = 9, PRO_LN_AFFINE = 10, PRO_GELU_TANH = 11, PRO_SITU_FAST = 13 };  // src/ffi.rs:15-29
 
 }  // namespace
 
@@ -120,7 +128,9 @@ ORC_API void orc_fht_rows(float* x, int64_t M, int K, int group) {
 }
 
 // Activation quantizer: csrc/kernels.cu:76-259 (quant_rows_kernel) behind gpu_quant_rows (:271-298).
-// dtype bf16 or f32; prologues PLAIN, RMS, GATE, SWIGLU, LAYERNORM, SILU, GELU, ADALN, GELU_TANH.
+// dtype bf16 or f32; prologues PLAIN, RMS, GATE, SWIGLU, LAYERNORM, SILU, GELU, ADALN, SITU, LN_MOD, LN_AFFINE (with
+// norm_b: the gpu_quant_rows_b entry point, kernels.cu:301-314), GELU_TANH. SITU_FAST (hardware tanh and exp
+// approximations on the GPU, about 2^-11 relative) is restated with the exact SITU expression.
 // The block-wide sums of the norm prologues run in the reference's order: each lane's own elements in
 // group order, a shuffle tree over the warp's 32 lanes, then a shuffle tree over the warps
 // (csrc/common.cuh:30-52).
@@ -128,7 +138,7 @@ ORC_API void orc_fht_rows(float* x, int64_t M, int K, int group) {
 ORC_API int orc_quant_rows(int dtype, int prologue, const void* x, int64_t x_stride, const void* g, int64_t g_stride,
                            int64_t up_offset, const float* norm_w, float eps, const void* mod_scale,
                            const void* mod_shift, int8_t* q, float* scales, int M, int K, int rotate, float* out_f,
-                           int contract) {
+                           int contract, const float* norm_b) {
     if (K % 256) return -1;
     const int ngroups = K / 256;
     const int nwarps = (ngroups + 3) / 4;
@@ -136,7 +146,8 @@ ORC_API int orc_quant_rows(int dtype, int prologue, const void* x, int64_t x_str
     if (dtype != DT_BF16 && dtype != DT_F32) return -4;
     switch (prologue) {
         case PRO_PLAIN: case PRO_RMS: case PRO_GATE: case PRO_SWIGLU: case PRO_LAYERNORM: case PRO_SILU:
-        case PRO_GELU: case PRO_ADALN: case PRO_GELU_TANH: break;
+        case PRO_GELU: case PRO_ADALN: case PRO_GELU_TANH: case PRO_SITU: case PRO_SITU_FAST: case PRO_LN_MOD: break;
+        case PRO_LN_AFFINE: if (!norm_w || !norm_b) return -3; break;
         default: return -3;
     }
     const float fmax_t = dtype == DT_BF16 ? 3.38953139e38f : 3.402823466e+38f;  // kernels.cu:49-51
@@ -175,13 +186,15 @@ ORC_API int orc_quant_rows(int dtype, int prologue, const void* x, int64_t x_str
                 switch (prologue) {
                     case PRO_GATE: v[k] = rnd(a * rnd(sigmoid_f(ld_t(dtype, g, (int64_t)m * g_stride + k)))); break;
                     case PRO_SWIGLU: v[k] = rnd(rnd(silu_f(a)) * ld_t(dtype, x, xo + up_offset + k)); break;
+                    case PRO_SITU: case PRO_SITU_FAST: v[k] = situ_f(a, ld_t(dtype, x, xo + up_offset + k)); break;  // not rounded here
                     case PRO_SILU: v[k] = rnd(silu_f(a)); break;
                     case PRO_GELU: v[k] = rnd(gelu_f(a)); break;
                     case PRO_GELU_TANH: v[k] = rnd(gelu_tanh_f(a, contract)); break;
                     default: v[k] = a;
                 }
             }
-            if (prologue == PRO_RMS || prologue == PRO_LAYERNORM || prologue == PRO_ADALN) {
+            const bool ln = prologue == PRO_LAYERNORM || prologue == PRO_LN_MOD || prologue == PRO_LN_AFFINE;
+            if (prologue == PRO_RMS || ln || prologue == PRO_ADALN) {
                 auto thread_partials = [&](auto f) {
                     for (int w = 0; w < nwarps; ++w)
                         for (int l = 0; l < 32; ++l) {
@@ -194,7 +207,7 @@ ORC_API int orc_quant_rows(int dtype, int prologue, const void* x, int64_t x_str
                             part[w * 32 + l] = ss;
                         }
                 };
-                if (prologue == PRO_LAYERNORM) {
+                if (ln) {
                     thread_partials([](float ss, float e) { return ss + e; });
                     const float mean = block_sum(part) / (float)K;
                     for (int k = 0; k < K; ++k) v[k] -= mean;
@@ -211,12 +224,22 @@ ORC_API int orc_quant_rows(int dtype, int prologue, const void* x, int64_t x_str
                         v[k] = rnd(contract ? fmaf(n, 1.f + ms, sh) : n * (1.f + ms) + sh);
                         continue;
                     }
+                    if (prologue == PRO_LN_MOD) {   // kernels.cu:40: one rounding after the norm, one after the addcmul
+                        const float ms = mod_scale ? ld_t(dtype, mod_scale, k) : 0.f, sh = mod_scale ? ld_t(dtype, mod_shift, k) : 0.f;
+                        v[k] = rnd(fmaf(rnd(n), rnd(1.f + ms), sh));
+                        continue;
+                    }
+                    if (prologue == PRO_LN_AFFINE) {   // kernels.cu:41
+                        v[k] = rnd(fmaf(n, norm_w[k], norm_b[k]));
+                        continue;
+                    }
                     if (norm_w) n *= norm_w[k];
                     n = rnd(n);
                     if (mod_scale) {
                         const float a = rnd(1.f + ld_t(dtype, mod_scale, k));
-                        n = rnd(a * n);
-                        n = rnd(n + ld_t(dtype, mod_shift, k));
+                        // f32 rows: rnd is the identity and nvcc fuses a * n + shift in the reference build
+                        if (dtype == DT_F32 && contract) n = fmaf(a, n, ld_t(dtype, mod_shift, k));
+                        else n = rnd(rnd(a * n) + ld_t(dtype, mod_shift, k));
                     }
                     v[k] = n;
                 }

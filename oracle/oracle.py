@@ -19,7 +19,9 @@ _LIB_PATH = os.path.join(_HERE, "liboracle.so")
 
 DT_F32, DT_F16, DT_BF16 = 0, 1, 2
 PRO_PLAIN, PRO_RMS, PRO_GATE, PRO_SWIGLU, PRO_LAYERNORM, PRO_SILU, PRO_GELU, PRO_ADALN = range(8)
+PRO_SITU, PRO_LN_MOD, PRO_LN_AFFINE = 8, 9, 10
 PRO_GELU_TANH = 11
+PRO_SITU_FAST = 13
 _DT = {torch.float32: DT_F32, torch.float16: DT_F16, torch.bfloat16: DT_BF16}
 _TORCH = {v: k for k, v in _DT.items()}
 
@@ -77,7 +79,7 @@ def fht_rows(x: torch.Tensor, group: int = 256) -> torch.Tensor:
 
 
 def quant_rows(x, prologue=PRO_PLAIN, rotate=0, *, K=None, x_stride=None, g=None, g_stride=0, up_offset=0,
-               norm_w=None, eps=0.0, mod_scale=None, mod_shift=None, out_f=False, contract=1):
+               norm_w=None, eps=0.0, mod_scale=None, mod_shift=None, out_f=False, contract=1, norm_b=None):
     """gpu_quant_rows on host cores. Returns (q int8 [M,K], scales f32 [M]) or the rotated f32 rows."""
     _chk(x, torch.bfloat16, torch.float32)
     M = x.shape[0]
@@ -89,7 +91,7 @@ def quant_rows(x, prologue=PRO_PLAIN, rotate=0, *, K=None, x_stride=None, g=None
     rc = lib().orc_quant_rows(C.c_int(_DT[x.dtype]), C.c_int(prologue), _p(x), C.c_int64(x_stride), _p(g),
                               C.c_int64(g_stride), C.c_int64(up_offset), _p(norm_w), C.c_float(eps), _p(mod_scale),
                               _p(mod_shift), _p(q), _p(s), C.c_int(M), C.c_int(K), C.c_int(rotate), _p(o),
-                              C.c_int(contract))
+                              C.c_int(contract), _p(norm_b))
     if rc:
         raise RuntimeError(f"orc_quant_rows failed with code {rc}")
     return o if out_f else (q, s)

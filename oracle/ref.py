@@ -39,17 +39,35 @@ def _st():
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def quant_rows(x, prologue=0, rotate=0, *, K=None, g=None, up_offset=0, q=None, scales=None):
+def quant_rows(x, prologue=0, rotate=0, *, K=None, g=None, up_offset=0, q=None, scales=None, norm_w=None, norm_b=None,
+               eps=0.0, mod_scale=None, mod_shift=None):
+    """The reference's gpu_quant_rows (gpu_quant_rows_b when norm_b is given), csrc/kernels.cu:271-314."""
     M = x.shape[0]
     K = K if K is not None else x.shape[1]
     q = q if q is not None else torch.empty((M, K), dtype=torch.int8, device=x.device)
     s = scales if scales is not None else torch.empty((M,), dtype=torch.float32, device=x.device)
-    rc = lib().gpu_quant_rows(C.c_int(_DT[x.dtype]), C.c_int(prologue), _p(x), C.c_int64(x.stride(0)), _p(g),
-                              C.c_int64(g.stride(0) if g is not None else 0), C.c_int64(up_offset), _p(None),
-                              C.c_float(0.0), _p(None), _p(None), _p(q), _p(s), C.c_int(M), C.c_int(K), C.c_int(rotate),
-                              _st())
+    if norm_b is not None:
+        rc = lib().gpu_quant_rows_b(C.c_int(_DT[x.dtype]), C.c_int(prologue), _p(x), C.c_int64(x.stride(0)), _p(norm_w),
+                                    _p(norm_b), C.c_float(eps), _p(mod_scale), _p(mod_shift), _p(q), _p(s), C.c_int(M),
+                                    C.c_int(K), C.c_int(rotate), _st())
+    else:
+        rc = lib().gpu_quant_rows(C.c_int(_DT[x.dtype]), C.c_int(prologue), _p(x), C.c_int64(x.stride(0)), _p(g),
+                                  C.c_int64(g.stride(0) if g is not None else 0), C.c_int64(up_offset), _p(norm_w),
+                                  C.c_float(eps), _p(mod_scale), _p(mod_shift), _p(q), _p(s), C.c_int(M), C.c_int(K),
+                                  C.c_int(rotate), _st())
     assert rc == 0, rc
     return q, s
+
+
+def rotate_rows_f32(x, prologue=0, *, K=None, up_offset=0, norm_w=None, eps=0.0):
+    """The reference's gpu_rotate_rows_f32 (csrc/kernels.cu:316-327): f32 rows in, rotated f32 rows out."""
+    M = x.shape[0]
+    K = K if K is not None else x.shape[1]
+    out = torch.empty((M, K), dtype=torch.float32, device=x.device)
+    rc = lib().gpu_rotate_rows_f32(C.c_int(prologue), _p(x), C.c_int64(x.stride(0)), C.c_int64(up_offset), _p(norm_w),
+                                   C.c_float(eps), _p(out), C.c_int(M), C.c_int(K), _st())
+    assert rc == 0, rc
+    return out
 
 
 def sd_quant_rows(x, rotate=0):

@@ -22,7 +22,25 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 
 BITS = {torch.bfloat16: torch.int16, torch.float16: torch.int16}
-PRO = {"plain": 0, "gate": 2, "swiglu": 3, "silu": 5, "gelu": 6, "gelu_tanh": 11}
+PRO = {"plain": 0, "rms": 1, "gate": 2, "swiglu": 3, "layernorm": 4, "silu": 5, "gelu": 6, "adaln": 7, "situ": 8, "ln_mod": 9,
+       "ln_affine": 10, "gelu_tanh": 11}
+EPS = 1e-6
+
+
+def norm_cases(I: dict, mv) -> dict:
+    """name -> (prologue, K, keyword arguments) of the normalising / SITU quantizer cases; rows are x_bf16[:, :K]."""
+    w, b, ms, sh = mv(I["norm_w_f32"]), mv(I["norm_b_f32"]), mv(I["mod_scale_bf16"]), mv(I["mod_shift_bf16"])
+    c = lambda t, K: t[:K].contiguous()
+    return {
+        "quant_rms_w": ("rms", 768, dict(norm_w=c(w, 768), eps=EPS)),
+        "quant_rms_w_mod_k1536": ("rms", 1536, dict(norm_w=w, mod_scale=ms, mod_shift=sh, eps=EPS)),
+        "quant_layernorm_w_mod": ("layernorm", 768, dict(norm_w=c(w, 768), mod_scale=c(ms, 768), mod_shift=c(sh, 768), eps=EPS)),
+        "quant_layernorm_k1536": ("layernorm", 1536, dict(eps=EPS)),
+        "quant_adaln": ("adaln", 768, dict(mod_scale=c(ms, 768), mod_shift=c(sh, 768), eps=EPS)),
+        "quant_ln_mod_k1536": ("ln_mod", 1536, dict(mod_scale=ms, mod_shift=sh, eps=EPS)),
+        "quant_ln_affine": ("ln_affine", 768, dict(norm_w=c(w, 768), norm_b=c(b, 768), eps=EPS)),
+        "quant_situ": ("situ", 768, dict(up_offset=768)),
+    }
 
 
 def to_np(t: torch.Tensor) -> np.ndarray:
@@ -60,6 +78,11 @@ def make_inputs() -> dict:
         d[f"bias_{name}"] = (torch.randn(88, generator=g) * 0.5).to(dt)
         d[f"rscale_{name}"] = torch.randn(88, generator=g).to(dt)
         d[f"resid_{name}"] = torch.randn(72, 88, generator=g).to(dt)
+    # per-column vectors of the normalising prologues (drawn last: everything above keeps its values)
+    d["norm_w_f32"] = torch.randn(1536, generator=g) * 0.2 + 1.0
+    d["norm_b_f32"] = torch.randn(1536, generator=g) * 0.1
+    d["mod_scale_bf16"] = (torch.randn(1536, generator=g) * 0.3).bfloat16()
+    d["mod_shift_bf16"] = (torch.randn(1536, generator=g) * 0.5).bfloat16()
     return d
 
 
@@ -102,6 +125,10 @@ def run_cases(I: dict, B, dev: str) -> dict:
     out["quant_gate_q"], out["quant_gate_s"] = q, s
     q, s = B.quant_rows(mv(I["x_f32"]), PRO["plain"], 1)
     out["quant_f32_q"], out["quant_f32_s"] = q, s
+    for name, (pro, K, kw) in norm_cases(I, mv).items():
+        rows = x if (K == 1536 or pro == "situ") else x[:, :768].contiguous()
+        q, s = B.quant_rows(rows, PRO[pro], 1, K=K, **kw)
+        out[f"{name}_q"], out[f"{name}_s"] = q, s
     for rot in (0, 64):
         q, s = B.sd_quant_rows(mv(I["sd_x640"]), rot)
         out[f"sd640_rot{rot}_q"], out[f"sd640_rot{rot}_s"] = q, s
@@ -128,8 +155,8 @@ class OracleBackend:
         from oracle import oracle as O
         self.O = O
 
-    def quant_rows(self, x, pro, rot, K=None, up_offset=0, g=None):
-        return self.O.quant_rows(x, pro, rot, K=K, up_offset=up_offset, g=g, g_stride=g.stride(0) if g is not None else 0)
+    def quant_rows(self, x, pro, rot, K=None, up_offset=0, g=None, **norm):
+        return self.O.quant_rows(x, pro, rot, K=K, up_offset=up_offset, g=g, g_stride=g.stride(0) if g is not None else 0, **norm)
 
     def sd_quant_rows(self, x, rot):
         return self.O.sd_quant_rows(x, rot)

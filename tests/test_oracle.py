@@ -54,7 +54,7 @@ def test_error_codes(oracle):
     with pytest.raises(RuntimeError, match="-1"):
         oracle.quant_rows(x)                       # K % 256
     with pytest.raises(RuntimeError, match="-3"):
-        oracle.quant_rows(torch.zeros(2, 256).bfloat16(), prologue=9)
+        oracle.quant_rows(torch.zeros(2, 256).bfloat16(), prologue=12)   # LN_AFFINE_SILU: not reachable through gpu_quant_rows
     with pytest.raises(RuntimeError, match="-1"):
         oracle.sd_quant_rows(torch.zeros(2, 100).half(), rotate=64)
 
@@ -108,7 +108,9 @@ def test_oracle_reproduces_its_golden_file(oracle, golden_inputs, golden_oracle)
 
 
 # prologues that call expf/tanhf/erff: the host libm may differ from CUDA's in the last ulp, which can move a code by one
-_LIBM = ("quant_silu", "quant_gelu", "quant_gelu_tanh", "quant_swiglu", "quant_gate")
+# normalising prologues: rsqrt.approx on the GPU against 1/sqrtf here (2 ulp), with the same effect
+_LIBM = ("quant_silu", "quant_gelu", "quant_gelu_tanh", "quant_swiglu", "quant_gate", "quant_rms", "quant_layernorm",
+         "quant_adaln", "quant_ln_", "quant_situ")
 
 
 def test_oracle_matches_the_reference_run_on_b200(golden_oracle, golden_reference):
@@ -121,7 +123,7 @@ def test_oracle_matches_the_reference_run_on_b200(golden_oracle, golden_referenc
         if k.startswith(_LIBM):
             if k.endswith("_q"):
                 d = np.abs(r.astype(np.int32) - o.astype(np.int32))
-                assert d.max() <= 1 and (d != 0).mean() <= 1e-3, (k, int(d.max()), float((d != 0).mean()))
+                assert d.max() <= 1 and (d != 0).mean() <= 2e-3, (k, int(d.max()), float((d != 0).mean()))
             else:
                 assert np.allclose(r, o, rtol=2e-2), k      # a scale moves with the row maximum's bf16 step
         else:

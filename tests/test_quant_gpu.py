@@ -125,7 +125,7 @@ def test_full_size_properties(pkg, dev):
 def test_errors(pkg, dev):
     x = torch.zeros(4, 512, device=dev, dtype=torch.bfloat16)
     with pytest.raises(pkg.GpuKernelError, match="-3"):
-        pkg.linear.quant_rows(x, 9, 0)          # LN_MOD needs gpu_quant_rows_b
+        pkg.linear.quant_rows(x, 12, 0)         # LN_AFFINE_SILU: no quantizing entry point takes it
     with pytest.raises(pkg.GpuKernelError, match="-2"):
         pkg.linear.quant_rows(torch.zeros(1, 33024, device=dev, dtype=torch.bfloat16), 0, 0)
     q, s = pkg.linear.quant_rows(torch.zeros(0, 512, device=dev, dtype=torch.bfloat16), 0, 0)
