@@ -90,7 +90,49 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return warp_max(t);
 }
 
+// block_sum of the reference (csrc/common.cuh:42-55): xor-shuffle tree over each warp, then over the warp sums
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+    __syncthreads();
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    float t = lane < nw ? red[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t = __fadd_rn(t, __shfl_xor_sync(0xffffffffu, t, o));
+    return t;
+}
+
 // ---- fp16 row quantizer ---------------------------------------------------------------------------------
+// rotation, row maximum, scale and codes of a row held in (padded) shared memory as fp32
+__device__ void sd_quant_tail(float* row, float* red, int8_t* __restrict__ qr, float* __restrict__ scale_out, int K, int rotate,
+                              int vec) {
+    if (rotate) rotate_row_smem(row, K, rotate);
+    float mx = 0.f;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) mx = fmaxf(mx, fabsf(rnd<half>(row[pad(k)])));
+    mx = block_max(mx, red);
+    const float scale = __fdiv_rn(fmaxf(mx, 1e-30f), 127.f);
+    if (threadIdx.x == 0) *scale_out = scale;
+    const float sh = rnd<half>(scale);
+    const float st = sh > 0.f ? sh : scale;  // a scale below half's range divides in float
+    if (vec) {
+        for (int c = threadIdx.x; c < K / 8; c += blockDim.x) {
+            const float* s = row + pad(c * 8);
+            uint32_t w[2] = {0u, 0u};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int qi = clamp_rint_i8(rnd<half>(__fdiv_rn(rnd<half>(s[j]), st)), -128.f);
+                w[j >> 2] |= (uint32_t)(qi & 0xff) << (8 * (j & 3));
+            }
+            reinterpret_cast<uint2*>(qr)[c] = make_uint2(w[0], w[1]);
+        }
+    } else {
+        for (int k = threadIdx.x; k < K; k += blockDim.x)
+            qr[k] = (int8_t)clamp_rint_i8(rnd<half>(__fdiv_rn(rnd<half>(row[pad(k)]), st)), -128.f);
+    }
+}
+
 __global__ void __launch_bounds__(256) sd_quant_rows_kernel(const half* __restrict__ x, int64_t x_stride,
                                                             int8_t* __restrict__ q, float* __restrict__ scales, int K,
                                                             int rotate, int vec) {
@@ -113,30 +155,52 @@ __global__ void __launch_bounds__(256) sd_quant_rows_kernel(const half* __restri
         for (int k = threadIdx.x; k < K; k += blockDim.x) row[pad(k)] = __half2float(r[k]);
     }
     __syncthreads();
-    if (rotate) rotate_row_smem(row, K, rotate);
-    float mx = 0.f;
-    for (int k = threadIdx.x; k < K; k += blockDim.x) mx = fmaxf(mx, fabsf(rnd<half>(row[pad(k)])));
-    mx = block_max(mx, red);
-    const float scale = __fdiv_rn(fmaxf(mx, 1e-30f), 127.f);
-    if (threadIdx.x == 0) scales[m] = scale;
-    const float sh = rnd<half>(scale);
-    const float st = sh > 0.f ? sh : scale;  // a scale below half's range divides in float
-    int8_t* qr = q + m * (int64_t)K;
-    if (vec) {
-        for (int c = threadIdx.x; c < K / 8; c += blockDim.x) {
-            const float* s = row + pad(c * 8);
-            uint32_t w[2] = {0u, 0u};
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int qi = clamp_rint_i8(rnd<half>(__fdiv_rn(rnd<half>(s[j]), st)), -128.f);
-                w[j >> 2] |= (uint32_t)(qi & 0xff) << (8 * (j & 3));
-            }
-            reinterpret_cast<uint2*>(qr)[c] = make_uint2(w[0], w[1]);
+    sd_quant_tail(row, red, q + m * (int64_t)K, scales + m, K, rotate, vec);
+}
+
+// The same quantizer over a row that another of the reference's kernels would have written in half first
+// (csrc/sd.cu:611-724): the row is computed as that kernel computes it, rounded to half, then quantized as above.
+// 256 threads, each adding elements t, t + 256, ... and then the block tree: the reference's order of additions.
+enum { SDQ_LN = 1, SDQ_GEGLU = 2, SDQ_UNPAD = 3 };
+struct SdSrc {
+    const half* x;
+    int64_t x_stride;   // LN: elements between rows
+    const float* w;     // LN weight and bias
+    const float* b;
+    float eps;
+    int heads, d, dp;   // UNPAD: heads of d values stored dp wide
+};
+template <int MODE>
+__global__ void __launch_bounds__(256) sd_quant_src_kernel(const SdSrc p, int8_t* __restrict__ q, float* __restrict__ scales,
+                                                           int K, int rotate, int vec) {
+    extern __shared__ float row[];
+    __shared__ float red[33];
+    const int64_t m = blockIdx.x;
+    if (MODE == SDQ_LN) {            // sd_layer_norm_kernel, csrc/sd.cu:312-328
+        const half* r = p.x + m * p.x_stride;
+        float s = 0.f;
+        for (int k = threadIdx.x; k < K; k += blockDim.x) s = __fadd_rn(s, __half2float(r[k]));
+        const float mean = __fdiv_rn(block_sum(s, red), (float)K);
+        float ss = 0.f;
+        for (int k = threadIdx.x; k < K; k += blockDim.x) {
+            const float d = __fsub_rn(__half2float(r[k]), mean);
+            ss = __fmaf_rn(d, d, ss);
         }
-    } else {
+        const float rstd = rsqrtf(__fadd_rn(__fdiv_rn(block_sum(ss, red), (float)K), p.eps));
         for (int k = threadIdx.x; k < K; k += blockDim.x)
-            qr[k] = (int8_t)clamp_rint_i8(rnd<half>(__fdiv_rn(rnd<half>(row[pad(k)]), st)), -128.f);
+            row[pad(k)] = rnd<half>(__fmaf_rn(__fmul_rn(__fsub_rn(__half2float(r[k]), mean), rstd), p.w[k], p.b[k]));
+    } else if (MODE == SDQ_GEGLU) {  // sd_geglu_kernel: [M, 2K], value then gate
+        const half* r = p.x + m * 2 * (int64_t)K;
+        for (int k = threadIdx.x; k < K; k += blockDim.x) {
+            const float g = rnd<half>(gelu_f(__half2float(r[K + k])));
+            row[pad(k)] = rnd<half>(__fmul_rn(__half2float(r[k]), g));
+        }
+    } else {                         // sd_unpad_heads
+        const half* r = p.x + m * (int64_t)p.heads * p.dp;
+        for (int k = threadIdx.x; k < K; k += blockDim.x) row[pad(k)] = __half2float(r[(k / p.d) * p.dp + k % p.d]);
     }
+    __syncthreads();
+    sd_quant_tail(row, red, q + m * (int64_t)K, scales + m, K, rotate, vec);
 }
 
 // ---- ConvRot weight requant / dequant -------------------------------------------------------------------
@@ -280,6 +344,39 @@ GPU_API int gpu_sd_quant_rows(const void* x, int64_t x_stride, int8_t* q, float*
                                                                                      rotate, vec);
     KCHECK();
     return 0;
+}
+
+namespace {
+template <int MODE>
+int launch_sd_src(const SdSrc& p, int8_t* q, float* scales, int M, int K, int rotate, cudaStream_t st) {
+    if ((rotate != 0 && rotate != 64 && rotate != 256) || (rotate && K % rotate)) return -1;
+    if (M <= 0 || K <= 0) return 0;
+    const size_t smem = (size_t)padded_words(K) * sizeof(float);
+    if (int rc = set_smem((const void*)sd_quant_src_kernel<MODE>, smem)) return rc;
+    const int vec = (K % 8 == 0) && (((uintptr_t)q & 7) == 0);
+    sd_quant_src_kernel<MODE><<<M, 256, smem, st>>>(p, q, scales, K, rotate, vec);
+    KCHECK();
+    return 0;
+}
+}  // namespace
+
+// LayerNorm of half rows (f32 weight and bias) fused into the quantizer: gpu_sd_layer_norm then gpu_sd_quant_rows,
+// without the half intermediate in memory. csrc/sd.cu:690-696.
+GPU_API int gpu_sd_ln_quant_rows(const void* x, int64_t x_stride, const float* w, const float* b, float eps, int8_t* q,
+                                 float* scales, int M, int K, int rotate, void* stream) {
+    SdSrc p{(const half*)x, x_stride, w, b, eps, 0, 0, 0};
+    return launch_sd_src<SDQ_LN>(p, q, scales, M, K, rotate, (cudaStream_t)stream);
+}
+// GEGLU of in [M, 2 I] (value then gate) fused into the quantizer of the [M, I] result. csrc/sd.cu:697-702.
+GPU_API int gpu_sd_geglu_quant_rows(const void* in, int8_t* q, float* scales, int M, int I, int rotate, void* stream) {
+    SdSrc p{(const half*)in, 0, nullptr, nullptr, 0.f, 0, 0, 0};
+    return launch_sd_src<SDQ_GEGLU>(p, q, scales, M, I, rotate, (cudaStream_t)stream);
+}
+// Head un-padding of src [M, H, dp] fused into the quantizer of the [M, H * d] result. csrc/sd.cu:703-708.
+GPU_API int gpu_sd_unpad_quant_rows(const void* src, int8_t* q, float* scales, int M, int H, int d, int dp, int rotate,
+                                    void* stream) {
+    SdSrc p{(const half*)src, 0, nullptr, nullptr, 0.f, H, d, dp};
+    return launch_sd_src<SDQ_UNPAD>(p, q, scales, M, H * d, rotate, (cudaStream_t)stream);
 }
 
 // x [N, K] f32 or bf16 in its original basis -> rotated q [N, K] int8 and row scales s [N].

@@ -116,6 +116,37 @@ def sd_quant_rows(x: torch.Tensor, rotate: int = 0):
     return q, s
 
 
+def sd_ln_quant_rows(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float, rotate: int = 0):
+    """gpu_sd_ln_quant_rows: LayerNorm (f32 weight, bias) of half rows, then the fp16 quantizer."""
+    _cuda(x)
+    M, K = x.shape
+    q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    s = torch.empty((M,), dtype=torch.float32, device=x.device)
+    ok(_lib().gpu_sd_ln_quant_rows(_ptr(x), x.stride(0), _ptr(w), _ptr(b), eps, _ptr(q), _ptr(s), M, K, rotate, _stream()),
+       "gpu_sd_ln_quant_rows")
+    return q, s
+
+
+def sd_geglu_quant_rows(x: torch.Tensor, rotate: int = 0):
+    """gpu_sd_geglu_quant_rows: x [M, 2 I] half (value, gate) -> codes of value * gelu(gate) [M, I]."""
+    _cuda(x)
+    M, I = x.shape[0], x.shape[1] // 2
+    q = torch.empty((M, I), dtype=torch.int8, device=x.device)
+    s = torch.empty((M,), dtype=torch.float32, device=x.device)
+    ok(_lib().gpu_sd_geglu_quant_rows(_ptr(x), _ptr(q), _ptr(s), M, I, rotate, _stream()), "gpu_sd_geglu_quant_rows")
+    return q, s
+
+
+def sd_unpad_quant_rows(x: torch.Tensor, d: int, rotate: int = 0):
+    """gpu_sd_unpad_quant_rows: x [M, H, dp] half -> codes of the first d values of every head, [M, H * d]."""
+    _cuda(x)
+    M, H, dp = x.shape
+    q = torch.empty((M, H * d), dtype=torch.int8, device=x.device)
+    s = torch.empty((M,), dtype=torch.float32, device=x.device)
+    ok(_lib().gpu_sd_unpad_quant_rows(_ptr(x), _ptr(q), _ptr(s), M, H, d, dp, rotate, _stream()), "gpu_sd_unpad_quant_rows")
+    return q, s
+
+
 def convrot_requant(x: torch.Tensor, seed: int = 0):
     _cuda(x)
     N, K = x.shape

@@ -282,6 +282,78 @@ ORC_API int orc_sd_quant_rows(const void* x, int64_t x_stride, int8_t* q, float*
     return 0;
 }
 
+// The fp16 quantizer over a row another kernel would have produced (csrc/sd.cu:611-708): mode 1 LayerNorm with f32
+// weight and bias (sd_layer_norm_kernel's sums: 256 threads, thread t adds elements t, t + 256, ..., then the block
+// tree of csrc/common.cuh:42-55), 2 GEGLU of [M, 2K] (value, gate), 3 head un-padding of [M, heads, dp] to heads * d.
+ORC_API int orc_sd_src_quant_rows(int mode, const void* x, int64_t x_stride, const float* w, const float* b, float eps, int heads,
+                                  int d, int dp, int8_t* q, float* scales, int M, int K, int rotate) {
+    if ((rotate != 0 && rotate != 64 && rotate != 256) || (rotate && K % rotate)) return -1;
+    if (mode < 1 || mode > 3) return -3;
+    const uint16_t* xh = (const uint16_t*)x;
+    auto block_sum256 = [](const float* part) {   // part[256] per-thread sums
+        float wsum[8];
+        for (int wi = 0; wi < 8; ++wi) {
+            float t[32];
+            for (int l = 0; l < 32; ++l) t[l] = part[wi * 32 + l];
+            for (int o = 16; o > 0; o >>= 1) {
+                float n[32];
+                for (int l = 0; l < 32; ++l) n[l] = t[l] + t[l ^ o];
+                std::memcpy(t, n, sizeof(t));
+            }
+            wsum[wi] = t[0];
+        }
+        float t[32];
+        for (int l = 0; l < 32; ++l) t[l] = l < 8 ? wsum[l] : 0.f;
+        for (int o = 16; o > 0; o >>= 1) {
+            float n[32];
+            for (int l = 0; l < 32; ++l) n[l] = t[l] + t[l ^ o];
+            std::memcpy(t, n, sizeof(t));
+        }
+        return t[0];
+    };
+#pragma omp parallel
+    {
+        std::vector<float> row(K);
+#pragma omp for schedule(static)
+        for (int m = 0; m < M; ++m) {
+            if (mode == 1) {
+                const uint16_t* r = xh + (int64_t)m * x_stride;
+                float part[256];
+                for (int t = 0; t < 256; ++t) {
+                    float sacc = 0.f;
+                    for (int k = t; k < K; k += 256) sacc += h2f(r[k]);
+                    part[t] = sacc;
+                }
+                const float mean = block_sum256(part) / (float)K;
+                for (int t = 0; t < 256; ++t) {
+                    float ss = 0.f;
+                    for (int k = t; k < K; k += 256) {
+                        const float dd = h2f(r[k]) - mean;
+                        ss = fmaf(dd, dd, ss);           // nvcc fuses ss += d * d
+                    }
+                    part[t] = ss;
+                }
+                const float rstd = 1.0f / sqrtf(block_sum256(part) / (float)K + eps);   // rsqrtf on the GPU (<= 2 ulp apart)
+                for (int k = 0; k < K; ++k) row[k] = rnd_h(fmaf((h2f(r[k]) - mean) * rstd, w[k], b[k]));
+            } else if (mode == 2) {
+                const uint16_t* r = xh + (int64_t)m * 2 * K;
+                for (int k = 0; k < K; ++k) row[k] = rnd_h(h2f(r[k]) * rnd_h(gelu_f(h2f(r[K + k]))));
+            } else {
+                const uint16_t* r = xh + (int64_t)m * heads * dp;
+                for (int k = 0; k < K; ++k) row[k] = h2f(r[(k / d) * dp + k % d]);
+            }
+            if (rotate) fht_rows(row.data(), K, rotate);
+            float mx = 0.f;
+            for (int k = 0; k < K; ++k) mx = fmaxf(mx, fabsf(rnd_h(row[k])));
+            const float scale = fmaxf(mx, 1e-30f) / 127.f;
+            scales[m] = scale;
+            const float st = rnd_h(scale) > 0.f ? rnd_h(scale) : scale;
+            for (int k = 0; k < K; ++k) q[(int64_t)m * K + k] = to_i8(rnd_h(rnd_h(row[k]) / st), -128.f);
+        }
+    }
+    return 0;
+}
+
 namespace {
 inline uint32_t pcg_hash(uint32_t x) {  // csrc/kernels.cu:1356-1360
     const uint32_t state = x * 747796405u + 2891336453u;

@@ -108,6 +108,22 @@ def sd_quant_rows(x, rotate=0):
     return q, s
 
 
+def sd_src_quant_rows(mode, x, rotate=0, *, w=None, b=None, eps=0.0, d=0):
+    """gpu_sd_{ln,geglu,unpad}_quant_rows on host cores; mode 'ln' (x [M,K] half), 'geglu' (x [M,2K]), 'unpad' (x [M,H,dp])."""
+    _chk(x, torch.float16)
+    M = x.shape[0]
+    code = {"ln": 1, "geglu": 2, "unpad": 3}[mode]
+    K = x.shape[1] if code == 1 else x.shape[1] // 2 if code == 2 else x.shape[1] * d
+    heads, dp = (x.shape[1], x.shape[2]) if code == 3 else (0, 0)
+    q = torch.empty((M, K), dtype=torch.int8)
+    s = torch.empty((M,), dtype=torch.float32)
+    rc = lib().orc_sd_src_quant_rows(C.c_int(code), _p(x), C.c_int64(x.stride(0)), _p(w), _p(b), C.c_float(eps), C.c_int(heads),
+                                     C.c_int(d), C.c_int(dp), _p(q), _p(s), C.c_int(M), C.c_int(K), C.c_int(rotate))
+    if rc:
+        raise RuntimeError(f"orc_sd_src_quant_rows failed with code {rc}")
+    return q, s
+
+
 def convrot_requant(x, seed=0):
     _chk(x, torch.float32, torch.bfloat16)
     N, K = x.shape

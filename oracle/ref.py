@@ -79,6 +79,24 @@ def sd_quant_rows(x, rotate=0):
     return q, s
 
 
+def sd_src_quant_rows(mode, x, rotate=0, *, w=None, b=None, eps=0.0, d=0):
+    """The reference's fused-source SD quantizers (csrc/sd.cu:690-708); mode 'ln', 'geglu' or 'unpad'."""
+    M = x.shape[0]
+    K = {"ln": lambda: x.shape[1], "geglu": lambda: x.shape[1] // 2, "unpad": lambda: x.shape[1] * d}[mode]()
+    q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    s = torch.empty((M,), dtype=torch.float32, device=x.device)
+    if mode == "ln":
+        rc = lib().gpu_sd_ln_quant_rows(_p(x), C.c_int64(x.stride(0)), _p(w), _p(b), C.c_float(eps), _p(q), _p(s), C.c_int(M),
+                                        C.c_int(K), C.c_int(rotate), _st())
+    elif mode == "geglu":
+        rc = lib().gpu_sd_geglu_quant_rows(_p(x), _p(q), _p(s), C.c_int(M), C.c_int(K), C.c_int(rotate), _st())
+    else:
+        rc = lib().gpu_sd_unpad_quant_rows(_p(x), _p(q), _p(s), C.c_int(M), C.c_int(x.shape[1]), C.c_int(d), C.c_int(x.shape[2]),
+                                           C.c_int(rotate), _st())
+    assert rc == 0, rc
+    return q, s
+
+
 def convrot_requant(x, seed=0):
     N, K = x.shape
     q = torch.empty((N, K), dtype=torch.int8, device=x.device)

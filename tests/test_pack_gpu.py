@@ -112,3 +112,56 @@ def test_quantize_at_load_full_size_round_trip(pkg, dev):
     assert bool((err <= 0.5001 * s[:, None] + 1e-7).all())
     q2, s2 = pkg.linear.convrot_requant(back, 0)
     assert float((q2 != q).float().mean()) < 1e-4 and torch.allclose(s2, s, rtol=1e-5)
+
+
+# ---- fp16 quantizer with a fused source stage (gpu_sd_{ln,geglu,unpad}_quant_rows) -------------------------------------
+def _sd_src_case(mode, M, K, seed):
+    g = torch.Generator().manual_seed(seed)
+    if mode == "ln":
+        x = (torch.randn(M, K, generator=g) * 2.0 + 0.5).half()
+        return x, dict(w=torch.randn(K, generator=g) * 0.2 + 1.0, b=torch.randn(K, generator=g) * 0.1, eps=1e-5)
+    if mode == "geglu":
+        return (torch.randn(M, 2 * K, generator=g) * 1.5).half(), {}
+    d = 64
+    return torch.randn(M, K // d, d + 8, generator=g).half(), dict(d=d)
+
+
+def _sd_src_run(L, mode, x, rotate, kw):
+    if mode == "ln":
+        return L.sd_ln_quant_rows(x, kw["w"], kw["b"], kw["eps"], rotate)
+    if mode == "geglu":
+        return L.sd_geglu_quant_rows(x, rotate)
+    return L.sd_unpad_quant_rows(x, kw["d"], rotate)
+
+
+@pytest.mark.parametrize("mode", ["ln", "geglu", "unpad"])
+@pytest.mark.parametrize("M,K,rotate", [(9, 320, 64), (40, 640, 0), (33, 1280, 256), (12, 2560, 64), (3, 5120, 256)])
+def test_sd_fused_source_quantizers(pkg, oracle, dev, mode, M, K, rotate):
+    """Bit-exact against the reference's kernels where they are built; against the oracle exactly for the gather, within
+    one step on a small fraction of codes where erff (GEGLU) or rsqrt (LayerNorm) differ between host and GPU."""
+    x, kw = _sd_src_case(mode, M, K, 11 + K + M)
+    dkw = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in kw.items()}
+    q, s = _sd_src_run(pkg.linear, mode, x.to(dev), rotate, dkw)
+    qo, so = oracle.sd_src_quant_rows(mode, x, rotate, **kw)
+    if mode == "unpad":
+        assert_bits_equal(q, qo, "codes"), assert_bits_equal(s, so, "scales")
+    else:
+        dlt = (q.cpu().int() - qo.int()).abs()
+        assert int(dlt.max()) <= 1 and float((dlt != 0).float().mean()) <= 2e-3
+        assert torch.allclose(s.cpu(), so, rtol=2e-3)
+    from oracle import ref as R
+    if R.available():
+        qr, sr = R.sd_src_quant_rows(mode, x.to(dev), rotate, **dkw)
+        assert_bits_equal(s, sr, "scales vs the reference kernel")
+        assert_bits_equal(q, qr, "codes vs the reference kernel")
+
+
+def test_sd_geglu_equals_the_two_kernel_flow(pkg, dev):
+    """The fused form against value * gelu(gate) materialised in half and quantized by gpu_sd_quant_rows (full-size row)."""
+    g = torch.Generator().manual_seed(3)
+    x = (torch.randn(512, 2 * 5120, generator=g) * 1.5).half().to(dev)
+    q, s = pkg.linear.sd_geglu_quant_rows(x, 64)
+    val = (x[:, :5120].float() * torch.nn.functional.gelu(x[:, 5120:].float()).half().float()).half()
+    q2, s2 = pkg.linear.sd_quant_rows(val, 64)
+    dlt = (q.int() - q2.int()).abs()      # torch's erf against CUDA's erff: last-ulp differences of the gate
+    assert int(dlt.max()) <= 1 and float((dlt != 0).float().mean()) <= 2e-3
