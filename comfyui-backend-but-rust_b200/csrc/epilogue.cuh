@@ -32,5 +32,7 @@ struct SkinnyParams {
     int M, N, K;
     int act;
 };
+// quant_rows.cu: table of bf16(act(x)) over all bf16 x for Act code `act`, built on first use (on `st`)
+int act_lut_ptr(int act, cudaStream_t st, const uint16_t** out);
 bool skinny_gemm_applies(int64_t M, int64_t N, int64_t K);
 int launch_skinny_gemm(int epi, const SkinnyParams& p, int out_dt, int sms, cudaStream_t st);

@@ -78,6 +78,8 @@ struct GemmParams {
     int* scratch;        // counters [split tiles][2][4][8], zero between launches
     int* partials;       // [split tiles][2][4][8][32 values][32 lanes] int32 sums, zero between launches
     uint32_t idesc;      // instruction descriptor for M = 256, N = bn
+    const uint16_t* act_lut;   // EPI_ACT with bf16 outputs: bf16(act(x)) for every bf16 x (a tanhf or erff per element
+                               // made the epilogue, not the tensor core, the limit: 836 against 2740 TOPS), or null
 #ifdef GEMM_PROFILE
     int dbg;             // debug build: bit 0 skips the TMA loads, bit 1 skips the MMAs
 #endif
@@ -195,7 +197,12 @@ __device__ __forceinline__ void epilogue8(const GemmParams& p, const uint32_t* r
         const float t0 = __fmul_rn(__int2float_rn((int)r[e]), xs_r);
         float v = rnd<OutT>(__fmaf_rn(t0, w8[e], b8[e]));
         if (EPI == EPI_RESID) v = __fmaf_rn(v, rs8[e], rr[e]);
-        else if (EPI == EPI_ACT) v = p.act == ACT_GELU_TANH ? gelu_tanh_f(v) : p.act == ACT_SILU ? silu_f(v) : gelu_f(v);
+        else if (EPI == EPI_ACT) {
+            if (std::is_same<OutT, bf16>::value && p.act_lut)
+                v = __uint_as_float((uint32_t)__ldg(p.act_lut + (__float_as_uint(v) >> 16)) << 16);
+            else
+                v = p.act == ACT_GELU_TANH ? gelu_tanh_f(v) : p.act == ACT_SILU ? silu_f(v) : gelu_f(v);
+        }
         y[e] = v;
     }
 }
@@ -741,6 +748,10 @@ int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const f
     p.xs = xs, p.ws = ws, p.bias = bias, p.rscale = rscale, p.resid = resid, p.D = D;
     p.M = (int)M, p.N = (int)N, p.K = (int)K;
     p.act = act;
+    p.act_lut = nullptr;
+    if (epi == EPI_ACT && out_dt == DT_BF16 && M * N >= (1 << 20)) {
+        if (int rc = act_lut_ptr(act, st, &p.act_lut)) return rc;
+    }
 #ifdef GEMM_PROFILE
     p.dbg = env_int("GEMM_DBG", 0);
 #endif

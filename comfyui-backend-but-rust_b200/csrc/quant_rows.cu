@@ -463,6 +463,32 @@ int ensure_lut(int which, cudaStream_t st) {
     return 0;
 }
 
+}  // namespace
+
+// Device address of the bf16 -> bf16 table of a GEMM-epilogue activation (epilogue.cuh's Act codes), built on first use
+// like the quantizer's own: the epilogue's out(act(out(v))) on bf16 outputs is a function of 16 bits.
+int act_lut_ptr(int act, cudaStream_t st, const uint16_t** out) {
+    const int which = act == 1 ? LUT_GELU_TANH : act == 2 ? LUT_SILU : act == 3 ? LUT_GELU : -1;
+    if (which < 0) return -204;
+    if (int rc = ensure_lut(which, st)) return rc;
+    static const uint16_t* base[64];
+    static std::mutex mu;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lk(mu);
+    const uint16_t*& b = base[dev & 63];
+    if (!b) {
+        void* addr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&addr, g_act_lut);
+        if (e != cudaSuccess) return (int)e;
+        b = reinterpret_cast<const uint16_t*>(addr);
+    }
+    *out = b + (size_t)which * 65536;
+    return 0;
+}
+
+namespace {
+
 template <typename T, int PRO, int MAXT>
 int launch_cfg(QuantArgs& p, int threads, size_t smem, int grid, cudaStream_t st) {
     auto kern = quant_rows_kernel<T, PRO, MAXT>;

@@ -83,20 +83,21 @@ def shard_pair(w1q, s1, b1, w2q, s2, b2, rank: int, world: int, hidden_of=None) 
     """Slices already-quantized weights. w1q [N1, K1], w2q [N2, K2] with K2 == N1 (or K2 == N1 / 3 for a QKV whose V
     third feeds the second linear: pass hidden_of = (offset, length) of that part inside N1)."""
     n1 = w1q.shape[0]
-    assert n1 % world == 0
     off, length = hidden_of if hidden_of else (0, n1)
-    assert length == w2q.shape[1] and length % (256 * world) == 0, "K slices must hold whole 256-wide rotation groups"
-    step = length // world
+    groups = length // 256
+    assert length == w2q.shape[1] and length % 256 == 0 and groups >= world, "K slices must hold whole 256-wide rotation groups"
+    # whole rotation groups per rank, as even as they divide (3072 hidden columns over 8 ranks: 1 or 2 groups each)
+    c0, c1 = 256 * (rank * groups // world), 256 * ((rank + 1) * groups // world)
     if hidden_of:   # QKV: keep q, k, v rows of this rank's heads together: [q_r | k_r | v_r]
-        parts = [slice(p * length + rank * step, p * length + (rank + 1) * step) for p in range(n1 // length)]
+        parts = [slice(p * length + c0, p * length + c1) for p in range(n1 // length)]
         idx = torch.cat([torch.arange(s.start, s.stop) for s in parts]).to(w1q.device)
         w1 = w1q.index_select(0, idx).contiguous()
         s1r = s1.index_select(0, idx).contiguous()
         b1r = b1.index_select(0, idx).contiguous() if b1 is not None else None
     else:
-        sl = slice(rank * step, (rank + 1) * step)
+        sl = slice(c0, c1)
         w1, s1r, b1r = w1q[sl].contiguous(), s1[sl].contiguous(), (b1[sl].contiguous() if b1 is not None else None)
-    w2 = w2q[:, rank * step:(rank + 1) * step].contiguous()
+    w2 = w2q[:, c0:c1].contiguous()
     return PairWeights(w1, s1r, b1r, w2, s2, b2)
 
 
@@ -159,7 +160,7 @@ def bench_main(args, rank, world, local, metric, unit):
     blocks = int(os.environ.get("BENCH_TP_BLOCKS", "60"))
     exact = os.environ.get("BENCH_TP_EXACT", "0") == "1"
     M, F, MLP = 16896, 3072, 12288
-    assert M % world == 0 and F % (256 * world) == 0
+    assert M % world == 0 and F // 256 >= world
     g = torch.Generator(device=dev).manual_seed(1234)          # same seed on every rank: identical full weights, then sliced
 
     def qweight(n, k):

@@ -97,6 +97,19 @@ def test_activation_epilogue_equals_the_reference_prologue_flow(pkg, ref, dev, a
     assert_bits_equal(s, s_ref, "scales")
 
 
+@pytest.mark.parametrize("act", [1, 2, 3])
+def test_tabulated_activation_epilogue_equals_the_computed_one(pkg, dev, act):
+    """Outputs of 2^20 elements and more take the activation from the bf16 -> bf16 table; smaller ones compute it. The same
+    rows must come out of both (row blocks of the large problem, run as problems of their own)."""
+    g, A, W, xs, ws = _operands(1536, 1024, 512, 77)
+    bias = (torch.randn(1024, generator=g) * 0.5).bfloat16().to(dev)
+    A, W, xs, ws = A.to(dev), W.to(dev), (xs * 0.3).to(dev), ws.to(dev)
+    big = pkg.linear.int8_gemm(A, W, xs, ws, bias, act=act)                      # 1.5 M outputs: table
+    for r0 in (0, 512, 1024):
+        part = pkg.linear.int8_gemm(A[r0:r0 + 512].contiguous(), W, xs[r0:r0 + 512].contiguous(), ws, bias, act=act)   # computed
+        assert_bits_equal(big[r0:r0 + 512], part, f"rows {r0}..")
+
+
 def test_golden_vectors(pkg, dev, golden_inputs, golden_reference):
     I = {k: v.to(dev) for k, v in golden_inputs.items()}
     for name, dt in (("bf16", torch.bfloat16), ("f16", torch.float16), ("f32", torch.float32)):

@@ -15,7 +15,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def _weights():
     g = torch.Generator().manual_seed(5)
-    F, H = 512, 1024
+    F, H = 512, 768          # three rotation groups of hidden columns: ranks take one and two
     w1 = torch.randn(H, F, generator=g) * 0.02
     w2 = torch.randn(F, H, generator=g) * 0.02
     b1 = (torch.randn(H, generator=g) * 0.01).bfloat16()
