@@ -98,6 +98,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// The same with a suspend-time hint: the thread may stay suspended in hardware for up to `ns` nanoseconds (it is
+// woken when the phase completes), instead of returning after the short system default and spinning in software.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait built on it, for roles that can afford a wake-up latency: a handful of instructions per poll and a
+// poll only every few microseconds, so that many waiting warps do not take issue slots from the working ones.
+__device__ __forceinline__ bool mbar_wait_suspended(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code);
 // Non-blocking test of an mbarrier phase.
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -131,6 +147,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
                 *abort_flag = code;
                 return false;
             }
+        }
+    }
+}
+
+__device__ __forceinline__ bool mbar_wait_suspended(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    uint64_t t0 = 0;
+    for (;;) {
+        if (mbar_try_wait_hint(bar, parity, 4000u)) return true;
+        if (*abort_flag) return false;
+        const uint64_t now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > kWaitLimitNs) {
+            *abort_flag = code;
+            return false;
         }
     }
 }

@@ -92,10 +92,10 @@ __device__ __forceinline__ void w6_group(const uint4 l, uint32_t ha, uint32_t hb
 // reads after the TMA writes.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
     int ok = 1;
-    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, code) ? 1 : 0;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait_suspended(bar, parity, abort_flag, code) ? 1 : 0;
     ok = __shfl_sync(0xffffffffu, ok, 0);
     if (!ok) return false;
-    return mbar_try_wait(bar, parity) || mbar_wait(bar, parity, abort_flag, code);
+    return mbar_try_wait(bar, parity) || mbar_wait_suspended(bar, parity, abort_flag, code);
 }
 
 constexpr int kW6BStages = 4;    // ring of expanded W tiles: only has to span unpack -> MMA
@@ -183,7 +183,7 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 const int row_a = tm * (2 * BM) + (int)rank * BM;
                 const int row_w = tn * BN + (int)rank * rows_w;
                 for (int kb = 0; kb < p.k_iters; ++kb) {
-                    if (!mbar_wait(bar_aempty + 8 * sa, pa ^ 1u, abort_s, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+                    if (!mbar_wait_suspended(bar_aempty + 8 * sa, pa ^ 1u, abort_s, ST_TIMEOUT_EMPTY)) { ok = false; break; }
                     mbar_arrive_expect_tx(bar_pfull + 8 * sa, lo_bytes + hi_bytes);
                     tma_load_2d(sLo + sa * lo_bytes, &tmap_lo, kb * 64, row_w, bar_pfull + 8 * sa);
                     tma_load_2d(sHi + sa * hi_bytes, &tmap_hi, kb * 32, row_w, bar_pfull + 8 * sa);

@@ -320,6 +320,92 @@ __global__ void __launch_bounds__(256) w6_decode_kernel(const uint8_t* __restric
     *reinterpret_cast<uint4*>(out + n * (int64_t)K + c * 16) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+// ---- W6A8 packer: bf16 weight -> R256 -> 6-bit codes + e4m3 group scales + f32 channel scale -----------------------
+// The algorithm of the reference's gpu_w6_requant (csrc/vendor/w6a8_requant.cu:59-154), per row:
+//   rotate, round to bf16; per group of 32: step gs = amax / 31, refined by two least-squares rounds
+//   (q = clamp(rint(w / gs), +-31); gs = sum(w q) / sum(q q)); channel scale sc = max |q gs| / 127;
+//   s_rel = e4m3(gs / sc); every element t = w / sc takes one of the 63 levels clamp(rint((i - 31) s_rel), +-127) that
+//   bracket it, drawn with probability proportional to the distance (hash-keyed uniform), and is stored as i + 1.
+// One thread per group (the sums are sequential over the group's 32 values, as there); maxima are order-free.
+__device__ __forceinline__ float w6_level(int i, float s) {
+    return fminf(127.f, fmaxf(-127.f, nearbyintf(__fmul_rn((float)(i - 31), s))));
+}
+__device__ __forceinline__ int w6_first_level_not_below(float t, float s, float inv_s) {
+    int i = __float2int_rn(__fmul_rn(__fsub_rn(ceilf(t), 0.5f), inv_s)) + 31;
+    i = min(max(i, 0), 63);
+    while (i > 0 && w6_level(i - 1, s) >= t) --i;
+    while (i < 63 && w6_level(i, s) < t) ++i;
+    return i;
+}
+__global__ void __launch_bounds__(256) w6_requant_kernel(const bf16* __restrict__ w, uint8_t* __restrict__ packed,
+                                                         uint8_t* __restrict__ s_rel, float* __restrict__ s_channel, int K,
+                                                         uint64_t seed) {
+    extern __shared__ float row[];            // padded row, then K / 32 group steps
+    __shared__ float red[32];
+    float* gstep = row + padded_words(K);
+    const int64_t n = blockIdx.x;
+    const bf16* r = w + n * (int64_t)K;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) row[pad(k)] = __bfloat162float(r[k]);
+    __syncthreads();
+    rotate_row_smem(row, K, 256);
+    for (int k = threadIdx.x; k < K; k += blockDim.x) row[pad(k)] = rnd<bf16>(row[pad(k)]);   // the rotated weight lives in bf16
+    __syncthreads();
+    const int groups = K / 32;
+    float amax_row = 0.f;
+    for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+        float v[32];
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = row[pad(g * 32 + i)], amax = fmaxf(amax, fabsf(v[i]));
+        float gs = fmaxf(__fdiv_rn(amax, 31.f), 1e-8f);
+        float inv = __fdiv_rn(1.f, gs);
+#pragma unroll 1
+        for (int it = 0; it < 2; ++it) {
+            float num = 0.f, den = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const float q = fminf(31.f, fmaxf(-31.f, nearbyintf(__fmul_rn(v[i], inv))));
+                num = __fmaf_rn(v[i], q, num);
+                den = __fmaf_rn(q, q, den);
+            }
+            gs = fmaxf(__fdiv_rn(num, fmaxf(den, 1e-8f)), 1e-8f);
+            inv = __fdiv_rn(1.f, gs);
+        }
+        gstep[g] = gs;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            amax_row = fmaxf(amax_row, fabsf(__fmul_rn(fminf(31.f, fmaxf(-31.f, nearbyintf(__fmul_rn(v[i], inv)))), gs)));
+    }
+    amax_row = block_max(amax_row, red);
+    const float sc = fmaxf(__fdiv_rn(amax_row, 127.f), 1e-8f);
+    const float inv_sc = __fdiv_rn(1.f, sc);
+    if (threadIdx.x == 0) s_channel[n] = sc;
+    uint8_t* prow = packed + n * (int64_t)(K / 4 * 3);
+    const uint32_t key = (uint32_t)seed ^ (uint32_t)(seed >> 32);
+    for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+        const uint8_t sb = (uint8_t)__nv_cvt_float_to_fp8(__fdiv_rn(gstep[g], sc), __NV_SATFINITE, __NV_E4M3);
+        s_rel[n * groups + g] = sb;
+        const float s = e4m3_to_f(sb);
+        const float inv_s = __fdiv_rn(1.f, fmaxf(s, 1e-30f));
+        uint32_t lo[4] = {0u, 0u, 0u, 0u}, hi[2] = {0u, 0u};
+#pragma unroll 4
+        for (int i = 0; i < 32; ++i) {
+            const float t = __fmul_rn(row[pad(g * 32 + i)], inv_sc);
+            const int pos = w6_first_level_not_below(t, s, inv_s);
+            const int l = min(max(pos - 1, 0), 61);
+            const float level_lo = w6_level(l, s);
+            const uint32_t h = pcg_hash((uint32_t)(n * (int64_t)K + g * 32 + i) ^ key);
+            const float u = __fmul_rn((float)(h >> 8), 1.0f / 16777216.0f);
+            const float thr = __fmaf_rn(u, __fsub_rn(w6_level(l + 1, s), level_lo), level_lo);
+            const uint32_t code = (uint32_t)min(l + (t > thr ? 1 : 0), 62) + 1u;
+            lo[i >> 3] |= (code & 15u) << (4 * (i & 7));
+            hi[i >> 4] |= ((code >> 4) & 3u) << (2 * (i & 15));
+        }
+        *reinterpret_cast<uint4*>(prow + g * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        *reinterpret_cast<uint2*>(prow + K / 2 + g * 8) = make_uint2(hi[0], hi[1]);
+    }
+}
+
 int set_smem(const void* fn, size_t bytes) {
     if (bytes <= 48 * 1024) return 0;
     const cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
@@ -446,6 +532,20 @@ GPU_API int gpu_w6_decode(const void* q, const void* s_rel, void* out, int64_t N
     if (n <= 0) return 0;
     w6_decode_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const uint8_t*)q, (const uint8_t*)s_rel,
                                                                                  (int8_t*)out, N, K, G);
+    KCHECK();
+    return 0;
+}
+
+// bf16 weight [N, K] -> W6A8 storage: packed [N, 3K/4], s_rel e4m3 [N, K/32], s_channel f32 [N]; stochastic rounding keyed
+// by `seed` and the element index. Replaces csrc/vendor/w6a8_requant.cu:246-257 (src/ffi.rs:132). -1: K % 256.
+GPU_API int gpu_w6_requant(const void* weight, void* packed, void* s_rel, void* s_channel, int64_t N, int K, uint64_t seed,
+                           void* stream) {
+    if (K % 256) return -1;
+    if (N <= 0) return 0;
+    const size_t smem = (size_t)(padded_words(K) + K / 32) * sizeof(float);
+    if (int rc = set_smem((const void*)w6_requant_kernel, smem)) return rc;
+    w6_requant_kernel<<<(unsigned)N, 256, smem, (cudaStream_t)stream>>>((const bf16*)weight, (uint8_t*)packed, (uint8_t*)s_rel,
+                                                                       (float*)s_channel, K, seed);
     KCHECK();
     return 0;
 }

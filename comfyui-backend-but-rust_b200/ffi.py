@@ -42,6 +42,7 @@ SIGNATURES = {
     "gpu_quant_rows_scaled": [i32, i32, P, i64, P, i64, i64, P, P, P, i32, i32, i32, P],
     "gpu_int8_epilogue": [P, P, P, P, P, P, P, i64, i64, i32, i32, P],
     "gpu_w6_decode": [P, P, P, i64, i32, i32, P],
+    "gpu_w6_requant": [P, P, P, P, i64, i32, u64, P],
     "gpu_convrot_requant": [i32, P, P, P, i64, i32, u64, P],
     "gpu_convrot_dequant": [i32, P, P, P, i64, i32, P],
     "gpu_dequant_i8": [P, P, P, i64, i64, P],

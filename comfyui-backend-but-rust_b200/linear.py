@@ -184,6 +184,17 @@ def w6_decode(packed: torch.Tensor, s_rel: torch.Tensor, K: int, G: int = 32):
     return out
 
 
+def w6_requant(w: torch.Tensor, seed: int = 1):
+    """gpu_w6_requant: bf16 [N, K] -> (packed u8 [N, 3K/4], s_rel u8 [N, K/32], s_channel f32 [N])."""
+    _cuda(w)
+    N, K = w.shape
+    packed = torch.empty((N, K * 3 // 4), dtype=torch.uint8, device=w.device)
+    s_rel = torch.empty((N, K // 32), dtype=torch.uint8, device=w.device)
+    s_ch = torch.empty((N,), dtype=torch.float32, device=w.device)
+    ok(_lib().gpu_w6_requant(_ptr(w), _ptr(packed), _ptr(s_rel), _ptr(s_ch), N, K, seed, _stream()), "gpu_w6_requant")
+    return packed, s_rel, s_ch
+
+
 def int8_gemm(A, W, xs, ws, bias=None, *, out_dtype=torch.bfloat16, act: int = 0, rscale=None, resid=None, out=None):
     """gpu_int8_gemm / gpu_int8_gemm_act / gpu_int8_gemm_residual, chosen by the arguments given."""
     _cuda(A)

@@ -137,6 +137,12 @@ int gpu_int8_epilogue(const int32_t* acc, const float* xs, const float* ws, cons
  * Replaces csrc/h3.cu:40-46 (src/ffi.rs:121). */
 int gpu_w6_decode(const void* q, const void* s_rel, void* out, int64_t N, int K, int G, void* stream);
 
+/* The W6A8 packer: bf16 weight [N, K] -> R256 -> packed [N, 3K/4] (nibble plane, then 2-bit plane), s_rel e4m3 [N, K/32],
+ * s_channel f32 [N]; group steps by two least-squares rounds, levels drawn by stochastic rounding keyed by seed and
+ * element index. -1: K % 256. Replaces csrc/vendor/w6a8_requant.cu:246-257 (src/ffi.rs:132). */
+int gpu_w6_requant(const void* weight, void* packed, void* s_rel, void* s_channel, int64_t N, int K, uint64_t seed,
+                   void* stream);
+
 /* ---- kernel 4: quantize-at-load weight packers and their inverses ------------------------------------- */
 
 /* x [N, K] f32 or bf16 -> R256 -> q int8 [N, K] + s f32 [N]; seed 0 rounds to nearest even, any other seed rounds

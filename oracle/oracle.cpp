@@ -355,6 +355,91 @@ ORC_API int orc_sd_src_quant_rows(int mode, const void* x, int64_t x_stride, con
 }
 
 namespace {
+// float -> fp8 e4m3 bits, round to nearest even, saturating to +-448 (what __nv_cvt_float_to_fp8(x, __NV_SATFINITE,
+// __NV_E4M3) returns); NaN -> 0x7f.
+inline uint8_t f_to_e4m3(float x) {
+    if (std::isnan(x)) return 0x7f;
+    const uint8_t sign = std::signbit(x) ? 0x80 : 0;
+    const float a = fabsf(x);
+    if (a >= 448.f) return sign | 0x7e;
+    if (a < 0.015625f) return sign | (uint8_t)nearbyintf(a * 512.f);   // denormals: steps of 2^-9 (8 rounds up into the normals)
+    int e;
+    const float m = frexpf(a, &e);                  // a = m 2^e, m in [0.5, 1)
+    int q = (int)nearbyintf(m * 16.f);              // 4 significant bits: 8..16
+    int ex = e - 1;
+    if (q == 16) q = 8, ++ex;
+    const int bits = ((ex + 7) << 3) | (q - 8);
+    return sign | (uint8_t)(bits > 0x7e ? 0x7e : bits);
+}
+inline float w6_level(int i, float s) { return fminf(127.f, fmaxf(-127.f, nearbyintf((float)(i - 31) * s))); }
+inline uint32_t pcg_hash(uint32_t x);
+}  // namespace
+
+// W6A8 packer, csrc/vendor/w6a8_requant.cu:59-154 and :228-257 (gpu_w6_requant: bf16 input, G = 32, always stochastic).
+// packed [N, 3K/4], s_rel [N, K/32] e4m3 bits, s_channel [N].
+ORC_API int orc_w6_requant(const void* w, uint8_t* packed, uint8_t* s_rel, float* s_channel, int64_t N, int K, uint64_t seed) {
+    if (K % 256) return -1;
+    const int groups = K / 32;
+    const uint32_t key = (uint32_t)seed ^ (uint32_t)(seed >> 32);
+#pragma omp parallel
+    {
+        std::vector<float> row(K), gstep(groups);
+#pragma omp for schedule(static)
+        for (int64_t n = 0; n < N; ++n) {
+            for (int k = 0; k < K; ++k) row[k] = ld_t(DT_BF16, w, n * K + k);
+            fht_rows(row.data(), K, 256);
+            for (int k = 0; k < K; ++k) row[k] = rnd_bf(row[k]);
+            float amax_row = 0.f;
+            for (int g = 0; g < groups; ++g) {
+                const float* v = row.data() + g * 32;
+                float amax = 0.f;
+                for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+                float gs = fmaxf(amax / 31.f, 1e-8f), inv = 1.f / gs;
+                for (int it = 0; it < 2; ++it) {
+                    float num = 0.f, den = 0.f;
+                    for (int i = 0; i < 32; ++i) {
+                        const float q = fminf(31.f, fmaxf(-31.f, nearbyintf(v[i] * inv)));
+                        num = fmaf(v[i], q, num);       // nvcc fuses num += w * q and den += q * q
+                        den = fmaf(q, q, den);
+                    }
+                    gs = fmaxf(num / fmaxf(den, 1e-8f), 1e-8f);
+                    inv = 1.f / gs;
+                }
+                gstep[g] = gs;
+                for (int i = 0; i < 32; ++i)
+                    amax_row = fmaxf(amax_row, fabsf(fminf(31.f, fmaxf(-31.f, nearbyintf(v[i] * inv))) * gs));
+            }
+            const float sc = fmaxf(amax_row / 127.f, 1e-8f), inv_sc = 1.f / sc;
+            s_channel[n] = sc;
+            uint8_t* prow = packed + n * (int64_t)(K / 4 * 3);
+            std::memset(prow, 0, (size_t)K / 4 * 3);
+            for (int g = 0; g < groups; ++g) {
+                const uint8_t sb = f_to_e4m3(gstep[g] / sc);
+                s_rel[n * groups + g] = sb;
+                const float s = e4m3_to_f(sb), inv_s = 1.f / fmaxf(s, 1e-30f);
+                for (int i = 0; i < 32; ++i) {
+                    const int e = g * 32 + i;
+                    const float t = row[e] * inv_sc;
+                    int pos = (int)nearbyintf((ceilf(t) - 0.5f) * inv_s) + 31;
+                    pos = std::min(std::max(pos, 0), 63);
+                    while (pos > 0 && w6_level(pos - 1, s) >= t) --pos;
+                    while (pos < 63 && w6_level(pos, s) < t) ++pos;
+                    const int l = std::min(std::max(pos - 1, 0), 61);
+                    const float level_lo = w6_level(l, s);
+                    const uint32_t h = pcg_hash((uint32_t)(n * (int64_t)K + e) ^ key);
+                    const float u = (float)(h >> 8) * (1.0f / 16777216.0f);
+                    const float thr = fmaf(u, w6_level(l + 1, s) - level_lo, level_lo);   // fused in the reference build
+                    const uint32_t code = (uint32_t)std::min(l + (t > thr ? 1 : 0), 62) + 1u;
+                    prow[e >> 1] |= (uint8_t)((code & 15u) << (4 * (e & 1)));
+                    prow[K / 2 + (e >> 2)] |= (uint8_t)(((code >> 4) & 3u) << (2 * (e & 3)));
+                }
+            }
+        }
+    }
+    return 0;
+}
+
+namespace {
 inline uint32_t pcg_hash(uint32_t x) {  // csrc/kernels.cu:1356-1360
     const uint32_t state = x * 747796405u + 2891336453u;
     const uint32_t word = ((state >> ((state >> 28u) + 4u)) ^ state) * 277803737u;

@@ -176,6 +176,19 @@ def w6_decode(packed, s_rel, K, G=32):
     return out
 
 
+def w6_requant(w: torch.Tensor, seed: int = 1):
+    """gpu_w6_requant on host cores: bf16 [N, K] -> (packed u8 [N, 3K/4], s_rel u8 [N, K/32], s_channel f32 [N])."""
+    _chk(w, torch.bfloat16)
+    N, K = w.shape
+    packed = torch.empty((N, K * 3 // 4), dtype=torch.uint8)
+    s_rel = torch.empty((N, K // 32), dtype=torch.uint8)
+    s_ch = torch.empty((N,), dtype=torch.float32)
+    rc = lib().orc_w6_requant(_p(w), _p(packed), _p(s_rel), _p(s_ch), C.c_int64(N), C.c_int(K), C.c_uint64(seed))
+    if rc:
+        raise RuntimeError(f"orc_w6_requant failed with code {rc}")
+    return packed, s_rel, s_ch
+
+
 def w6_pack_codes(codes: torch.Tensor) -> torch.Tensor:
     """6-bit codes u8 [N,K] (1..63) -> the reference's two-plane row layout u8 [N, 3K/4]
     (nibble plane then 2-bit plane; csrc/vendor/w6a8_requant.cu:128-151)."""

@@ -141,6 +141,7 @@ def run_cases(I: dict, B, dev: str) -> dict:
             if seed == 0:
                 out[f"dequant_{name}"] = B.convrot_dequant(q, s, I[name].dtype)
     out["w6_decode"] = B.w6_decode(mv(w6_pack_codes(I["w6_codes"])), mv(I["w6_srel"]), 512)
+    out["w6_requant_packed"], out["w6_requant_srel"], out["w6_requant_schannel"] = B.w6_requant(mv(I["w_bf16"]), 3)
     A, W, xs, ws = mv(I["A"]), mv(I["W"]), mv(I["xs"]), mv(I["ws"])
     for name, dt in DTYPES.items():
         b, rs, rr = mv(I[f"bias_{name}"]), mv(I[f"rscale_{name}"]), mv(I[f"resid_{name}"])
@@ -169,6 +170,9 @@ class OracleBackend:
 
     def w6_decode(self, p, s, K):
         return self.O.w6_decode(p, s, K)
+
+    def w6_requant(self, w, seed):
+        return self.O.w6_requant(w, seed)
 
     def int8_gemm(self, A, W, xs, ws, bias, out_dtype, rscale=None, resid=None):
         # both multiply-adds of the epilogue fused: the form the reference binary has (contract = 3)

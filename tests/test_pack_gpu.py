@@ -165,3 +165,39 @@ def test_sd_geglu_equals_the_two_kernel_flow(pkg, dev):
     q2, s2 = pkg.linear.sd_quant_rows(val, 64)
     dlt = (q.int() - q2.int()).abs()      # torch's erf against CUDA's erff: last-ulp differences of the gate
     assert int(dlt.max()) <= 1 and float((dlt != 0).float().mean()) <= 2e-3
+
+
+# ---- W6A8 packer (gpu_w6_requant) ------------------------------------------------------------------------------------
+@pytest.mark.parametrize("N,K,seed", [(3, 256, 1), (20, 768, 3), (9, 5120, 0xDEADBEEF12345), (5, 13824, 7)])
+def test_w6_requant_bit_exact(pkg, oracle, dev, N, K, seed):
+    """Packed codes, e4m3 group scales and channel scales against the CPU oracle and, where built, the reference's kernel
+    (every step is IEEE arithmetic in a fixed order, so all three agree bit for bit); decoding gives back the weight."""
+    g = torch.Generator().manual_seed(N + K)
+    w = (torch.randn(N, K, generator=g) * 0.02)
+    w[:, ::97] *= 6.0                                        # a few outliers per row
+    w = w.bfloat16()
+    packed, s_rel, s_ch = pkg.linear.w6_requant(w.to(dev), seed)
+    po, so, co = oracle.w6_requant(w, seed)
+    assert_bits_equal(s_ch, co, "s_channel"), assert_bits_equal(s_rel, so, "s_rel"), assert_bits_equal(packed, po, "packed")
+    from oracle import ref as R
+    if R.available():
+        pr, sr, cr = R.w6_requant(w.to(dev), seed)
+        assert_bits_equal(s_ch, cr, "s_channel vs reference"), assert_bits_equal(s_rel, sr, "s_rel vs reference")
+        assert_bits_equal(packed, pr, "packed vs reference")
+    # round trip: decode to int8, undo the rotation, compare with the weight (6-bit steps: a few per cent of the row maximum)
+    w8 = pkg.linear.w6_decode(packed, s_rel, K)
+    back = pkg.linear.convrot_dequant(w8, s_ch, torch.float32).cpu()
+    err = (back - w.float()).abs().amax(1) / w.float().abs().amax(1)
+    assert float(err.max()) < 0.08, float(err.max())
+
+
+def test_w6_requant_feeds_the_fused_gemm(pkg, dev):
+    """Packer -> fused W6A8 GEMM equals packer -> decode -> int8 GEMM."""
+    g = torch.Generator().manual_seed(4)
+    w = (torch.randn(384, 1024, generator=g) * 0.02).bfloat16().to(dev)
+    packed, s_rel, s_ch = pkg.linear.w6_requant(w, 11)
+    A = torch.randint(-128, 128, (200, 1024), generator=g, dtype=torch.int8).to(dev)
+    xs = (torch.rand(200, generator=g) * 0.05 + 1e-3).to(dev)
+    got = pkg.linear.w6a8_gemm(A, packed, s_rel, xs, s_ch, None)
+    want = pkg.linear.int8_gemm(A, pkg.linear.w6_decode(packed, s_rel, 1024), xs, s_ch, None)
+    assert_bits_equal(got, want, "fused vs decoded")
