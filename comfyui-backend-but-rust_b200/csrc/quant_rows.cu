@@ -443,6 +443,18 @@ int ensure_lut(int which, cudaStream_t st) {
     cudaGetDevice(&dev);
     LutState& s = g_lut_state[dev & 63];
     std::lock_guard<std::mutex> lk(s.mu);
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess) (void)cudaGetLastError();
+    if (cap != cudaStreamCaptureStatusNone) {
+        // While a graph is being captured neither event queries nor waits on outside events are allowed. A table
+        // requested first inside a capture is built by the captured graph itself, every replay (idempotent); one
+        // launched before is taken as complete: the warm-up call that launched it precedes the capture.
+        if (!s.launched[which]) {
+            build_lut_kernel<<<256, 256, 0, st>>>(which);
+            KCHECK();
+        }
+        return 0;
+    }
     if (!s.launched[which]) {
         build_lut_kernel<<<256, 256, 0, st>>>(which);
         KCHECK();
