@@ -56,7 +56,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
-    ap.add_argument("--mode", default="replicas", choices=["replicas", "tp", "kernel"])
+    ap.add_argument("--mode", default="replicas", choices=["replicas", "tp", "kernel", "shapes"])
     ap.add_argument("--kernel", default="gemm_up", choices=sorted(KERNELS),
                     help="--mode kernel: the one kernel to launch --steps times (the command ncu captures are taken from)")
     ap.add_argument("--cpu-rows", type=int, default=4352, help="rows of the batch the CPU baseline computes")
@@ -181,6 +181,54 @@ class RefImpl:
         return self.R.int8_gemm(A, W, xs, ws, bias, rscale=rscale, resid=resid, out=out)
 
 
+def run_shapes(torch, wl, impl, dev, tag):
+    """--mode shapes: every linear of the five benchmark configurations alone (GEMM with bias in the configuration's
+    activation dtype, and the quantizer that feeds it), one JSON line each. Operands smaller than the L2 are timed with
+    a 256 MB buffer written between launches."""
+    flush = torch.empty(64 * 1024 * 1024, device=dev)
+
+    def timed(fn, small, iters=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if not small:
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / iters * 1e3
+        tot = 0.0
+        for _ in range(iters):
+            flush.fill_(1.0)
+            e0.record(); fn(); e1.record()
+            torch.cuda.synchronize()
+            tot += e0.elapsed_time(e1)
+        return tot / iters * 1e3
+
+    for ci in range(5):
+        specs = wl.config(ci) + (wl.config(2, 6144) if ci == 2 else [])
+        for sp in specs:
+            M, K, N, dt = sp.M, sp.K, sp.N, sp.act_dtype
+            A = torch.randint(-128, 128, (M, K), dtype=torch.int8, device=dev)
+            W = torch.randint(-128, 128, (N, K), dtype=torch.int8, device=dev)
+            xs, ws = torch.rand(M, device=dev) * 0.01, torch.rand(N, device=dev) * 0.001
+            bias, D = torch.randn(N, device=dev).to(dt), torch.empty(M, N, dtype=dt, device=dev)
+            small = (M * K + N * K + M * N * D.element_size()) < 126e6
+            us = timed(lambda: impl.int8_gemm(A, W, xs, ws, bias, out=D), small)
+            line = {"impl": tag, "cfg": ci, "linear": sp.name, "M": M, "K": K, "N": N, "out": str(dt).split(".")[-1],
+                    "gemm_us": us, "tops": 2.0 * M * N * K / us / 1e6, "frac_of_4500": 2.0 * M * N * K / us / 1e6 / INT8_NOMINAL_TOPS,
+                    "gemm_gbs": (M * K + N * K + M * N * D.element_size()) / us / 1e3, "l2_flushed": small}
+            if K % 256 == 0 and dt == torch.bfloat16 and M > 1:
+                X = torch.randn(M, K, device=dev).to(dt)
+                Q, S = torch.empty(M, K, dtype=torch.int8, device=dev), torch.empty(M, device=dev)
+                qus = timed(lambda: impl.quant_rows(X, 0, 1 if sp.rotate else 0, q=Q, scales=S), small)
+                line.update(quant_us=qus, quant_gbs=3.0 * M * K / qus / 1e3)
+            print(json.dumps(line), flush=True)
+            del A, W, D
+
+
 def time_steps(torch, fn, steps: int, warmup: int, barrier=None):
     """W warm-up steps, then exactly `steps` timed with CUDA events on the current stream; returns milliseconds."""
     for _ in range(warmup):
@@ -294,6 +342,11 @@ def main():
         impl, fused = RefImpl(R), False
     else:
         impl, fused = pkg.linear, os.environ.get("BENCH_FUSED_GELU", "0") == "1"
+
+    if args.mode == "shapes":
+        if rank == 0:
+            run_shapes(torch, wl, impl, dev, args.impl)
+        return
 
     # token-sharded replicas: every rank owns one batch of the block (weights replicated), no data-path collective
     up, down, x, w1, w2, b1, b2 = host_inputs(wl, rank)
