@@ -104,7 +104,9 @@ constexpr int kW6BStages = 4;    // ring of expanded W tiles: only has to span u
 // the unpack warps. Barriers: afull (leader: A bytes of both CTAs), pfull (per CTA: its packed planes), aempty (per
 // CTA: MMAs have read A slot -> its packed slot is free too, the unpack that fed those MMAs being long done),
 // bfull (leader: 16 unpack-warp arrivals), bempty (per CTA: MMAs have read the expanded slot).
-template <typename OutT, int EPI>
+// MH = 256-row halves per tile (1 or 2). With MH = 2 an expanded W tile feeds two sets of MMAs (rows 0-255 and 256-511 of
+// the tile, two accumulators of bn <= 128 columns per buffer), so the unpack work per MMA halves.
+template <typename OutT, int EPI, int MH>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kW6Threads, 1)
 gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_lo,
                       const __grid_constant__ CUtensorMap tmap_hi, const __grid_constant__ CUtensorMap tmap_d,
@@ -117,7 +119,8 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const int SB = x6.sb;
     const int BN = p.bn;
     const int rows_w = BN / 2;                              // weight rows this CTA expands
-    const uint32_t a_bytes = BM * BK, b_bytes = (uint32_t)rows_w * BK, lo_bytes = (uint32_t)rows_w * 64, hi_bytes = (uint32_t)rows_w * 32;
+    constexpr uint32_t a_box = BM * BK;                    // one 128-row, 128-byte K box of A
+    const uint32_t a_bytes = MH * a_box, b_bytes = (uint32_t)rows_w * BK, lo_bytes = (uint32_t)rows_w * 64, hi_bytes = (uint32_t)rows_w * 32;
     uint8_t* staging = sm;
     const uint32_t sA = base + kW6StagingBytes;
     const uint32_t sB = sA + SA * a_bytes;
@@ -180,7 +183,7 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             for (int t = cluster_id; t < p.num_tiles && ok; t += nclusters) {
                 int tm, tn;
                 tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
-                const int row_a = tm * (2 * BM) + (int)rank * BM;
+                const int row_a = tm * (2 * BM * MH) + (int)rank * BM;
                 const int row_w = tn * BN + (int)rank * rows_w;
                 for (int kb = 0; kb < p.k_iters; ++kb) {
                     if (!mbar_wait_suspended(bar_aempty + 8 * sa, pa ^ 1u, abort_s, ST_TIMEOUT_EMPTY)) { ok = false; break; }
@@ -188,7 +191,10 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                     tma_load_2d(sLo + sa * lo_bytes, &tmap_lo, kb * 64, row_w, bar_pfull + 8 * sa);
                     tma_load_2d(sHi + sa * hi_bytes, &tmap_hi, kb * 32, row_w, bar_pfull + 8 * sa);
                     if (leader) mbar_arrive_expect_tx(bar_afull + 8 * sa, 2 * a_bytes);
-                    tma_load_2d_pair(sA + sa * a_bytes, &tmap_a, kb * BK, row_a, mapa_shared(bar_afull + 8 * sa, 0));
+#pragma unroll
+                    for (int h = 0; h < MH; ++h)
+                        tma_load_2d_pair(sA + sa * a_bytes + h * a_box, &tmap_a, kb * BK, row_a + h * 2 * BM,
+                                         mapa_shared(bar_afull + 8 * sa, 0));
                     if (++sa == SA) { sa = 0; pa ^= 1u; }
                 }
             }
@@ -220,10 +226,14 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                     if (!mbar_wait(bar_bfull + 8 * sb, pb, abort_s, ST_TIMEOUT_FULL)) { ok = false; break; }
                     W6P_LAP(1, true);
                     tc_fence_after();
-                    umma_i8_pair_lo(d_tmem, a_lo, b_lo, idesc, kb);
-                    umma_i8_pair_lo(d_tmem, a_lo + 2, b_lo + 2, idesc, 1);
-                    umma_i8_pair_lo(d_tmem, a_lo + 4, b_lo + 4, idesc, 1);
-                    umma_i8_pair_lo(d_tmem, a_lo + 6, b_lo + 6, idesc, 1);
+#pragma unroll
+                    for (int h = 0; h < MH; ++h) {
+                        const uint32_t dh = d_tmem + h * 128, ah = a_lo + h * (a_box >> 4);
+                        umma_i8_pair_lo(dh, ah, b_lo, idesc, kb);
+                        umma_i8_pair_lo(dh, ah + 2, b_lo + 2, idesc, 1);
+                        umma_i8_pair_lo(dh, ah + 4, b_lo + 4, idesc, 1);
+                        umma_i8_pair_lo(dh, ah + 6, b_lo + 6, idesc, 1);
+                    }
                     umma_commit_pair(bar_bempty + 8 * sb);
                     umma_commit_pair(bar_aempty + 8 * sa);
                     W6P_LAP(2, true);
@@ -244,7 +254,10 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         // data, so a group pays them once per 128 elements of its rows, and the groups overlap one another's waits.
         const int uw = warp - (2 + kW6EpiWarps);
         const int grp = uw >> 2;
-        const int r = 32 * (uw & 3) + lane;                      // row of the half tile
+        // up to 64 rows per CTA (bn <= 128): two threads per row, 64 elements each; else one thread per row
+        const bool two = rows_w <= 64;
+        const int r = two ? 32 * (uw & 1) + lane : 32 * (uw & 3) + lane;      // row of the half tile
+        const int hf = two ? (uw >> 1) & 1 : 0;                               // which 64 elements of the box
         const bool has_row = r < rows_w;
         const uint32_t bfull_leader = mapa_shared(bar_bfull, 0);
         const int sw_lo = (r >> 1) & 3, sw_hi = (r >> 2) & 1, sw_out = r & 7;
@@ -292,14 +305,16 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                         const uint8_t* lo = sm + (sLo - base) + sa * lo_bytes + rr * 64;
                         const uint8_t* hi = sm + (sHi - base) + sa * hi_bytes + rr * 32;
                         uint8_t* out = sm + (sB - base) + sb * b_bytes + rr * 128;
-                        const uint4 h0 = *reinterpret_cast<const uint4*>(hi + ((0 ^ sw_hi) << 4));
+                        const uint4 h0 = *reinterpret_cast<const uint4*>(hi + ((hf ^ sw_hi) << 4));
                         const uint4 h1 = *reinterpret_cast<const uint4*>(hi + ((1 ^ sw_hi) << 4));
                         const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {      // 32 elements = one scale group per 16-byte piece of nibbles
+                            if (two && (c >> 1) != hf) continue;             // the other thread of the row (the same for the whole warp)
+                            const int hi_w = two ? 2 * (c & 1) : 2 * c;
                             const uint4 l = *reinterpret_cast<const uint4*>(lo + ((c ^ sw_lo) << 4));
                             uint32_t o[8];
-                            w6_group(l, hw[2 * c], hw[2 * c + 1], (sr >> (8 * c)) & 0xffu, o);
+                            w6_group(l, hw[hi_w], hw[hi_w + 1], (sr >> (8 * c)) & 0xffu, o);
                             if (has_row) {
                                 *reinterpret_cast<uint4*>(out + (((2 * c) ^ sw_out) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
                                 *reinterpret_cast<uint4*>(out + (((2 * c + 1) ^ sw_out) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
@@ -332,11 +347,6 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             int tm, tn;
             tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
             const int n0 = tn * BN;
-            const int row0 = tm * (2 * BM) + (int)rank * BM + quad * 32;
-            const int row = row0 + lane;
-            const bool row_ok = row < p.M;
-            const int rrow = row_ok ? row : p.M - 1;
-            const float xs_r = EPI != EPI_ACC ? p.xs[rrow] : 0.f;
             const bool staged = kStageVec && p.tma_store;
             if (staged) {
                 // the tile's columns of ws / bias / rscale, fetched while the mainloop still runs
@@ -356,10 +366,16 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             if (!mbar_wait_warp_relaxed(bar_tfull + 8 * buf, tphase, abort_s, ST_TIMEOUT_TMEM_FULL)) break;
             W6P_BEGIN();
             tc_fence_after();
-            const uint32_t taddr = tmem_base + buf * 256 + ((uint32_t)(quad * 32) << 16);
             uint32_t ra[32];
 #pragma unroll 1
-            for (int c = 0; c < nchunks; ++c) {
+            for (int hc = 0; hc < MH * nchunks; ++hc) {
+                const int h = MH == 1 ? 0 : hc / nchunks, c = hc - h * nchunks;
+                const int row0 = tm * (2 * BM * MH) + h * 2 * BM + (int)rank * BM + quad * 32;
+                const int row = row0 + lane;
+                const bool row_ok = row < p.M;
+                const int rrow = row_ok ? row : p.M - 1;
+                const float xs_r = EPI != EPI_ACC ? p.xs[rrow] : 0.f;
+                const uint32_t taddr = tmem_base + buf * 256 + h * 128 + ((uint32_t)(quad * 32) << 16);
                 tmem_ld32(taddr + c * 32, ra);
                 tmem_ld_wait();
                 const int col0 = n0 + c * 32;
@@ -429,10 +445,10 @@ bool make_plane_tmap(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t col
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <typename OutT, int EPI>
-int launch_w6(const CUtensorMap& ta, const CUtensorMap& tlo, const CUtensorMap& thi, const CUtensorMap& td,
-              const GemmParams& p, const W6Extra& x6, int grid, cudaStream_t st) {
-    auto kern = gemm_w6a8_pair_kernel<OutT, EPI>;
+template <typename OutT, int EPI, int MH>
+int launch_w6_mh(const CUtensorMap& ta, const CUtensorMap& tlo, const CUtensorMap& thi, const CUtensorMap& td,
+                 const GemmParams& p, const W6Extra& x6, int grid, cudaStream_t st) {
+    auto kern = gemm_w6a8_pair_kernel<OutT, EPI, MH>;
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -445,6 +461,13 @@ int launch_w6(const CUtensorMap& ta, const CUtensorMap& tlo, const CUtensorMap& 
     kern<<<grid, kW6Threads, kSmemBytes, st>>>(ta, tlo, thi, td, p, x6);
     KCHECK();
     return 0;
+}
+
+template <typename OutT, int EPI>
+int launch_w6(const CUtensorMap& ta, const CUtensorMap& tlo, const CUtensorMap& thi, const CUtensorMap& td,
+              const GemmParams& p, const W6Extra& x6, int mh, int grid, cudaStream_t st) {
+    return mh == 2 ? launch_w6_mh<OutT, EPI, 2>(ta, tlo, thi, td, p, x6, grid, st)
+                   : launch_w6_mh<OutT, EPI, 1>(ta, tlo, thi, td, p, x6, grid, st);
 }
 
 int run_w6_gemm(int epi, const int8_t* A, const uint8_t* Wq6, const uint8_t* s_rel, const float* xs, const float* ws,
@@ -470,14 +493,18 @@ int run_w6_gemm(int epi, const int8_t* A, const uint8_t* Wq6, const uint8_t* s_r
     p.tma_store = !no_tma_store && al16(D) && ((N * esz) % 16 == 0);
     p.ksub = 1;
     p.k_iters = (int)(K / BK);
-    const int bn = choose_bn(M, N, p.k_iters, clusters);
+    // More than 256 rows: tiles of 512 rows x 128 columns, so that each expanded W tile serves two sets of MMAs and the
+    // unpack work per MMA halves; otherwise one 256-row half and the column width that fills the clusters best.
+    static const int mh_env = env_int("GPU_KERNELS_W6_MH", 0);
+    const int mh = mh_env ? (mh_env == 2 ? 2 : 1) : (M > 256 && N >= 128 ? 2 : 1);
+    const int bn = mh == 2 ? 128 : choose_bn(M, N, p.k_iters, clusters);
     p.bn = bn;
     p.idesc = umma_idesc_i8(2 * BM, bn);
-    const int stage_bytes = BM * BK + (bn / 2) * (64 + 32);          // A box + packed planes; the expanded ring is separate
+    const int stage_bytes = mh * BM * BK + (bn / 2) * (64 + 32);     // A boxes + packed planes; the expanded ring is separate
     const int sbs = kW6BStages;
     const int stages = (kSmemBytes - 1024 - 512 - kW6StagingBytes - sbs * (bn / 2) * BK) / stage_bytes;
     p.stages = stages > kMaxStages ? kMaxStages : stages;
-    p.tiles_m = (int)((M + 2 * BM - 1) / (2 * BM));
+    p.tiles_m = (int)((M + 2 * BM * mh - 1) / (2 * BM * mh));
     p.tiles_n = (int)((N + bn - 1) / bn);
     p.num_tiles = p.tiles_m * p.tiles_n;
     p.whole_tiles = p.num_tiles, p.num_items = p.num_tiles, p.kps = p.k_iters;
@@ -493,10 +520,10 @@ int run_w6_gemm(int epi, const int8_t* A, const uint8_t* Wq6, const uint8_t* s_r
     }
     W6Extra x6{s_rel, (int)(K / 32), sbs};
     const int grid = 2 * (p.num_tiles < clusters ? p.num_tiles : clusters);
-    if (epi == EPI_ACC) return launch_w6<float, EPI_ACC>(ta, tlo, thi, td, p, x6, grid, st);
+    if (epi == EPI_ACC) return launch_w6<float, EPI_ACC>(ta, tlo, thi, td, p, x6, mh, grid, st);
 #define W6_DISPATCH(T)                                                                                   \
-    (epi == EPI_RESID ? launch_w6<T, EPI_RESID>(ta, tlo, thi, td, p, x6, grid, st)                      \
-                      : launch_w6<T, EPI_PLAIN>(ta, tlo, thi, td, p, x6, grid, st))
+    (epi == EPI_RESID ? launch_w6<T, EPI_RESID>(ta, tlo, thi, td, p, x6, mh, grid, st)                      \
+                      : launch_w6<T, EPI_PLAIN>(ta, tlo, thi, td, p, x6, mh, grid, st))
     if (out_dt == DT_F32) return W6_DISPATCH(float);
     if (out_dt == DT_F16) return W6_DISPATCH(half);
     return W6_DISPATCH(bf16);

@@ -161,15 +161,45 @@ __global__ void __launch_bounds__(256) sd_quant_rows_kernel(const half* __restri
 // The same quantizer over a row that another of the reference's kernels would have written in half first
 // (csrc/sd.cu:611-724): the row is computed as that kernel computes it, rounded to half, then quantized as above.
 // 256 threads, each adding elements t, t + 256, ... and then the block tree: the reference's order of additions.
-enum { SDQ_LN = 1, SDQ_GEGLU = 2, SDQ_UNPAD = 3 };
+enum { SDQ_LN = 1, SDQ_GEGLU = 2, SDQ_UNPAD = 3, SDQ_GN = 4 };
 struct SdSrc {
     const half* x;
     int64_t x_stride;   // LN: elements between rows
-    const float* w;     // LN weight and bias
+    const float* w;     // LN, GN: weight and bias
     const float* b;
-    float eps;
+    float eps;          // LN, GN
     int heads, d, dp;   // UNPAD: heads of d values stored dp wide
+    const double* sums; // GN: per (image, group) sum and sum of squares
+    int groups;         // GN
+    int64_t P;          // GN: pixels per image
+    double cnt;         // GN: values per group, P * C / groups
 };
+
+// GroupNorm statistics of x [N, P, C] half: per (image, group) the sum and the sum of squares, accumulated in double
+// from per-block float sums as the reference's sd_group_sums_kernel forms them (csrc/sd.cu:209-233: 256 threads, thread
+// t takes values t, t + 256, ... of the block's pixel range, then the block tree), so the statistics come out the same.
+__global__ void __launch_bounds__(256) sd_group_sums_kernel(const half* __restrict__ x, double* __restrict__ sums, int64_t P,
+                                                            int C, int G, int splits) {
+    __shared__ float red[33];
+    const int ng = blockIdx.x, split = blockIdx.y;
+    const int n = ng / G, g = ng % G, per = C / G;
+    const int64_t base = (int64_t)n * P * C + g * per;
+    const int64_t p0 = P * split / splits, p1 = P * (split + 1) / splits;
+    const int64_t count = (p1 - p0) * per;
+    float s = 0.f, ss = 0.f;
+    for (int64_t i = threadIdx.x; i < count; i += blockDim.x) {
+        const float v = __half2float(x[base + (p0 + i / per) * C + (int)(i % per)]);
+        s = __fadd_rn(s, v);
+        ss = __fmaf_rn(v, v, ss);
+    }
+    s = block_sum(s, red);
+    __syncthreads();
+    ss = block_sum(ss, red);
+    if (threadIdx.x == 0) {
+        atomicAdd(&sums[ng * 2], (double)s);
+        atomicAdd(&sums[ng * 2 + 1], (double)ss);
+    }
+}
 template <int MODE>
 __global__ void __launch_bounds__(256) sd_quant_src_kernel(const SdSrc p, int8_t* __restrict__ q, float* __restrict__ scales,
                                                            int K, int rotate, int vec) {
@@ -195,9 +225,25 @@ __global__ void __launch_bounds__(256) sd_quant_src_kernel(const SdSrc p, int8_t
             const float g = rnd<half>(gelu_f(__half2float(r[K + k])));
             row[pad(k)] = rnd<half>(__fmul_rn(__half2float(r[k]), g));
         }
-    } else {                         // sd_unpad_heads
+    } else if (MODE == SDQ_UNPAD) {  // sd_unpad_heads
         const half* r = p.x + m * (int64_t)p.heads * p.dp;
         for (int k = threadIdx.x; k < K; k += blockDim.x) row[pad(k)] = __half2float(r[(k / p.d) * p.dp + k % p.d]);
+    } else {                         // sd_group_apply_kernel without SiLU: row m is a pixel of image m / P (csrc/sd.cu:198-205,244-255)
+        __shared__ float2 stat[256];
+        const int n = (int)(m / p.P);
+        for (int g = threadIdx.x; g < p.groups; g += blockDim.x) {
+            const double su = p.sums[(n * p.groups + g) * 2], sq = p.sums[(n * p.groups + g) * 2 + 1];
+            const double mean = su / p.cnt;
+            const double var = fmax(fma(-mean, mean, sq / p.cnt), 0.0);
+            stat[g] = make_float2((float)mean, (float)(1.0 / sqrt(var + (double)p.eps)));
+        }
+        __syncthreads();
+        const half* r = p.x + m * (int64_t)K;
+        const int per = K / p.groups;
+        for (int c = threadIdx.x; c < K; c += blockDim.x) {
+            const float2 st = stat[c / per];
+            row[pad(c)] = rnd<half>(__fmaf_rn(__fmul_rn(__fsub_rn(__half2float(r[c]), st.x), st.y), p.w[c], p.b[c]));
+        }
     }
     __syncthreads();
     sd_quant_tail(row, red, q + m * (int64_t)K, scales + m, K, rotate, vec);
@@ -450,19 +496,39 @@ int launch_sd_src(const SdSrc& p, int8_t* q, float* scales, int M, int K, int ro
 // without the half intermediate in memory. csrc/sd.cu:690-696.
 GPU_API int gpu_sd_ln_quant_rows(const void* x, int64_t x_stride, const float* w, const float* b, float eps, int8_t* q,
                                  float* scales, int M, int K, int rotate, void* stream) {
-    SdSrc p{(const half*)x, x_stride, w, b, eps, 0, 0, 0};
+    SdSrc p{(const half*)x, x_stride, w, b, eps, 0, 0, 0, nullptr, 0, 0, 0.0};
     return launch_sd_src<SDQ_LN>(p, q, scales, M, K, rotate, (cudaStream_t)stream);
 }
 // GEGLU of in [M, 2 I] (value then gate) fused into the quantizer of the [M, I] result. csrc/sd.cu:697-702.
 GPU_API int gpu_sd_geglu_quant_rows(const void* in, int8_t* q, float* scales, int M, int I, int rotate, void* stream) {
-    SdSrc p{(const half*)in, 0, nullptr, nullptr, 0.f, 0, 0, 0};
+    SdSrc p{(const half*)in, 0, nullptr, nullptr, 0.f, 0, 0, 0, nullptr, 0, 0, 0.0};
     return launch_sd_src<SDQ_GEGLU>(p, q, scales, M, I, rotate, (cudaStream_t)stream);
 }
 // Head un-padding of src [M, H, dp] fused into the quantizer of the [M, H * d] result. csrc/sd.cu:703-708.
 GPU_API int gpu_sd_unpad_quant_rows(const void* src, int8_t* q, float* scales, int M, int H, int d, int dp, int rotate,
                                     void* stream) {
-    SdSrc p{(const half*)src, 0, nullptr, nullptr, 0.f, H, d, dp};
+    SdSrc p{(const half*)src, 0, nullptr, nullptr, 0.f, H, d, dp, nullptr, 0, 0, 0.0};
     return launch_sd_src<SDQ_UNPAD>(p, q, scales, M, H * d, rotate, (cudaStream_t)stream);
+}
+
+// GroupNorm (no SiLU) of x [N, P, C] half fused into the quantizer of its [N * P, C] rows. `sums` is scratch of
+// N * G * 2 doubles + 16 bytes, as the reference's gpu_sd_group_norm takes it; it is cleared here and holds the groups'
+// sums afterwards (the reference overwrites the first half of each pair with (mean, rstd) as floats; nothing reads
+// them after the call). -1: C % G, G > 256 or a bad rotate. csrc/sd.cu:710-724.
+GPU_API int gpu_sd_group_norm_quant_rows(const void* x, const float* w, const float* b, void* sums, int N, int64_t P, int C,
+                                         int G, float eps, int8_t* q, float* scales, int rotate, void* stream) {
+    if (G <= 0 || C % G || G > 256) return -1;
+    if ((rotate != 0 && rotate != 64 && rotate != 256) || (rotate && C % rotate)) return -1;
+    if (N <= 0 || P <= 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    const cudaError_t e = cudaMemsetAsync(sums, 0, (size_t)N * G * 2 * sizeof(double) + 16, st);
+    if (e != cudaSuccess) return (int)e;
+    const int64_t want = P * (C / G) / 4096;
+    const int splits = want < 1 ? 1 : want > 64 ? 64 : (int)want;
+    sd_group_sums_kernel<<<dim3(N * G, splits), 256, 0, st>>>((const half*)x, (double*)sums, P, C, G, splits);
+    KCHECK();
+    SdSrc p{(const half*)x, 0, w, b, eps, 0, 0, 0, (const double*)sums, G, P, (double)P * (C / G)};
+    return launch_sd_src<SDQ_GN>(p, q, scales, (int)(N * P), C, rotate, st);
 }
 
 // x [N, K] f32 or bf16 in its original basis -> rotated q [N, K] int8 and row scales s [N].

@@ -30,6 +30,7 @@ SIGNATURES = {
     "gpu_sd_ln_quant_rows": [P, i64, P, P, f32, P, P, i32, i32, i32, P],
     "gpu_sd_geglu_quant_rows": [P, P, P, i32, i32, i32, P],
     "gpu_sd_unpad_quant_rows": [P, P, P, i32, i32, i32, i32, i32, P],
+    "gpu_sd_group_norm_quant_rows": [P, P, P, P, i32, i64, i32, i32, f32, P, P, i32, P],
     "gpu_int8_gemm": [P, P, P, P, P, P, i64, i64, i64, i32, P],
     "gpu_int8_gemm_residual": [P, P, P, P, P, P, P, P, i64, i64, i64, i32, P],
     "gpu_int8_gemm_act": [P, P, P, P, P, P, i64, i64, i64, i32, i32, P],

@@ -137,6 +137,18 @@ def sd_geglu_quant_rows(x: torch.Tensor, rotate: int = 0):
     return q, s
 
 
+def sd_group_norm_quant_rows(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, groups: int, eps: float, rotate: int = 0):
+    """gpu_sd_group_norm_quant_rows: x [N, P, C] half -> GroupNorm (f32 weight, bias; no SiLU) -> codes [N * P, C]."""
+    _cuda(x)
+    N, P, C = x.shape
+    q = torch.empty((N * P, C), dtype=torch.int8, device=x.device)
+    s = torch.empty((N * P,), dtype=torch.float32, device=x.device)
+    sums = torch.empty((N * groups * 2 + 2,), dtype=torch.float64, device=x.device)
+    ok(_lib().gpu_sd_group_norm_quant_rows(_ptr(x), _ptr(w), _ptr(b), _ptr(sums), N, P, C, groups, eps, _ptr(q), _ptr(s), rotate,
+                                           _stream()), "gpu_sd_group_norm_quant_rows")
+    return q, s
+
+
 def sd_unpad_quant_rows(x: torch.Tensor, d: int, rotate: int = 0):
     """gpu_sd_unpad_quant_rows: x [M, H, dp] half -> codes of the first d values of every head, [M, H * d]."""
     _cuda(x)

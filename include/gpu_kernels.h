@@ -58,13 +58,16 @@ int gpu_sd_quant_rows(const void* x, int64_t x_stride, int8_t* q, float* scales,
 /* gpu_sd_quant_rows over a row that another kernel of the reference would have written in half first, computed here
  * as that kernel computes it (same order of additions, same rounding to half) and quantized without the intermediate
  * in memory: LayerNorm with f32 weight and bias; GEGLU of in [M, 2I] (value, then gate); head un-padding of
- * src [M, H, dp] to [M, H*d]. Errors as gpu_sd_quant_rows. Replace csrc/sd.cu:690-708 (src/ffi.rs:247-252).
- * (gpu_sd_group_norm_quant_rows is not provided: it needs the reference's group-norm statistics kernel.) */
+ * src [M, H, dp] to [M, H*d]. Errors as gpu_sd_quant_rows. Replace csrc/sd.cu:690-724 (src/ffi.rs:247-253).
+ * gpu_sd_group_norm_quant_rows: GroupNorm (no SiLU) of x [N, P, C] with G groups, then the quantizer of its N*P rows of
+ * C values; sums = scratch of N*G*2 doubles + 16 bytes (cleared here). -1 also for C % G != 0 or G > 256. */
 int gpu_sd_ln_quant_rows(const void* x, int64_t x_stride, const float* w, const float* b, float eps, int8_t* q,
                          float* scales, int M, int K, int rotate, void* stream);
 int gpu_sd_geglu_quant_rows(const void* in, int8_t* q, float* scales, int M, int I, int rotate, void* stream);
 int gpu_sd_unpad_quant_rows(const void* src, int8_t* q, float* scales, int M, int H, int d, int dp, int rotate,
                             void* stream);
+int gpu_sd_group_norm_quant_rows(const void* x, const float* w, const float* b, void* sums, int N, int64_t P, int C, int G,
+                                 float eps, int8_t* q, float* scales, int rotate, void* stream);
 
 /* ---- kernels 2 + 3: int8 GEMM mainloop with the fused dequant epilogue -------------------------------- */
 

@@ -354,6 +354,80 @@ ORC_API int orc_sd_src_quant_rows(int mode, const void* x, int64_t x_stride, con
     return 0;
 }
 
+// GroupNorm (no SiLU) of x [N, P, C] half fused into the fp16 quantizer of its pixels' rows (csrc/sd.cu:198-233, :244-255,
+// :710-724). Group sums: per (group, split of the pixels) 256 per-thread float sums over values t, t + 256, ... and the
+// block tree, added in double; mean and 1/sqrt(var + eps) in double, then float.
+ORC_API int orc_sd_gn_quant_rows(const void* x, const float* w, const float* b, int N, int64_t P, int C, int G, float eps,
+                                 int8_t* q, float* scales, int rotate) {
+    if (G <= 0 || C % G) return -1;
+    if ((rotate != 0 && rotate != 64 && rotate != 256) || (rotate && C % rotate)) return -1;
+    const uint16_t* xh = (const uint16_t*)x;
+    const int per = C / G;
+    const int64_t want = P * per / 4096;
+    const int splits = want < 1 ? 1 : want > 64 ? 64 : (int)want;
+    const double cnt = (double)P * per;
+    auto tree256 = [](const float* part) {
+        float wsum[8];
+        for (int wi = 0; wi < 8; ++wi) {
+            float t[32];
+            for (int l = 0; l < 32; ++l) t[l] = part[wi * 32 + l];
+            for (int o = 16; o > 0; o >>= 1) { float n2[32]; for (int l = 0; l < 32; ++l) n2[l] = t[l] + t[l ^ o]; std::memcpy(t, n2, sizeof(t)); }
+            wsum[wi] = t[0];
+        }
+        float t[32];
+        for (int l = 0; l < 32; ++l) t[l] = l < 8 ? wsum[l] : 0.f;
+        for (int o = 16; o > 0; o >>= 1) { float n2[32]; for (int l = 0; l < 32; ++l) n2[l] = t[l] + t[l ^ o]; std::memcpy(t, n2, sizeof(t)); }
+        return t[0];
+    };
+    std::vector<float> mean_f((size_t)N * G), rstd_f((size_t)N * G);
+#pragma omp parallel for schedule(static)
+    for (int ng = 0; ng < N * G; ++ng) {
+        const int n = ng / G, g = ng % G;
+        const int64_t base = (int64_t)n * P * C + g * per;
+        double su = 0.0, sq = 0.0;
+        for (int split = 0; split < splits; ++split) {
+            const int64_t p0 = P * split / splits, p1 = P * (split + 1) / splits, count = (p1 - p0) * per;
+            float ps[256], pq[256];
+            for (int t = 0; t < 256; ++t) {
+                float s1 = 0.f, s2 = 0.f;
+                for (int64_t i = t; i < count; i += 256) {
+                    const float v = h2f(xh[base + (p0 + i / per) * C + (int)(i % per)]);
+                    s1 += v;
+                    s2 = fmaf(v, v, s2);
+                }
+                ps[t] = s1, pq[t] = s2;
+            }
+            su += (double)tree256(ps);
+            sq += (double)tree256(pq);
+        }
+        const double mean = su / cnt;
+        const double var = fmax(fma(-mean, mean, sq / cnt), 0.0);
+        mean_f[ng] = (float)mean;
+        rstd_f[ng] = (float)(1.0 / sqrt(var + (double)eps));
+    }
+    const int64_t M = (int64_t)N * P;
+#pragma omp parallel
+    {
+        std::vector<float> row(C);
+#pragma omp for schedule(static)
+        for (int64_t m = 0; m < M; ++m) {
+            const int n = (int)(m / P);
+            for (int c = 0; c < C; ++c) {
+                const int ng = n * G + c / per;
+                row[c] = rnd_h(fmaf((h2f(xh[m * C + c]) - mean_f[ng]) * rstd_f[ng], w[c], b[c]));
+            }
+            if (rotate) fht_rows(row.data(), C, rotate);
+            float mx = 0.f;
+            for (int c = 0; c < C; ++c) mx = fmaxf(mx, fabsf(rnd_h(row[c])));
+            const float scale = fmaxf(mx, 1e-30f) / 127.f;
+            scales[m] = scale;
+            const float st = rnd_h(scale) > 0.f ? rnd_h(scale) : scale;
+            for (int c = 0; c < C; ++c) q[m * C + c] = to_i8(rnd_h(rnd_h(row[c]) / st), -128.f);
+        }
+    }
+    return 0;
+}
+
 namespace {
 // float -> fp8 e4m3 bits, round to nearest even, saturating to +-448 (what __nv_cvt_float_to_fp8(x, __NV_SATFINITE,
 // __NV_E4M3) returns); NaN -> 0x7f.

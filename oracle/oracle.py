@@ -124,6 +124,19 @@ def sd_src_quant_rows(mode, x, rotate=0, *, w=None, b=None, eps=0.0, d=0):
     return q, s
 
 
+def sd_group_norm_quant_rows(x, w, b, groups, eps, rotate=0):
+    """gpu_sd_group_norm_quant_rows on host cores: x [N, P, C] half -> (codes [N * P, C], scales [N * P])."""
+    _chk(x, torch.float16)
+    N, P, Cc = x.shape
+    q = torch.empty((N * P, Cc), dtype=torch.int8)
+    s = torch.empty((N * P,), dtype=torch.float32)
+    rc = lib().orc_sd_gn_quant_rows(_p(x), _p(_chk(w, torch.float32)), _p(_chk(b, torch.float32)), C.c_int(N), C.c_int64(P),
+                                    C.c_int(Cc), C.c_int(groups), C.c_float(eps), _p(q), _p(s), C.c_int(rotate))
+    if rc:
+        raise RuntimeError(f"orc_sd_gn_quant_rows failed with code {rc}")
+    return q, s
+
+
 def convrot_requant(x, seed=0):
     _chk(x, torch.float32, torch.bfloat16)
     N, K = x.shape

@@ -97,6 +97,18 @@ def sd_src_quant_rows(mode, x, rotate=0, *, w=None, b=None, eps=0.0, d=0):
     return q, s
 
 
+def sd_group_norm_quant_rows(x, w, b, groups, eps, rotate=0):
+    """The reference's gpu_sd_group_norm_quant_rows (csrc/sd.cu:710-724); x [N, P, C] half."""
+    N, P, Cc = x.shape
+    q = torch.empty((N * P, Cc), dtype=torch.int8, device=x.device)
+    s = torch.empty((N * P,), dtype=torch.float32, device=x.device)
+    sums = torch.empty((N * groups * 2 + 2,), dtype=torch.float64, device=x.device)
+    rc = lib().gpu_sd_group_norm_quant_rows(_p(x), _p(w), _p(b), _p(sums), C.c_int(N), C.c_int64(P), C.c_int(Cc), C.c_int(groups),
+                                            C.c_float(eps), _p(q), _p(s), C.c_int(rotate), _st())
+    assert rc == 0, rc
+    return q, s
+
+
 def convrot_requant(x, seed=0):
     N, K = x.shape
     q = torch.empty((N, K), dtype=torch.int8, device=x.device)

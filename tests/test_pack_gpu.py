@@ -201,3 +201,20 @@ def test_w6_requant_feeds_the_fused_gemm(pkg, dev):
     got = pkg.linear.w6a8_gemm(A, packed, s_rel, xs, s_ch, None)
     want = pkg.linear.int8_gemm(A, pkg.linear.w6_decode(packed, s_rel, 1024), xs, s_ch, None)
     assert_bits_equal(got, want, "fused vs decoded")
+
+
+@pytest.mark.parametrize("N,P,C,G,rotate", [(1, 64, 320, 32, 64), (2, 1024, 640, 32, 64), (1, 4096, 320, 32, 0), (2, 256, 1280, 32, 256)])
+def test_sd_group_norm_quantizer(pkg, oracle, dev, N, P, C, G, rotate):
+    """GroupNorm fused into the fp16 quantizer: bit-exact against the reference's pair of kernels where built; against the
+    oracle the group statistics agree exactly (same float partial sums, double accumulation), so codes and scales do too."""
+    g = torch.Generator().manual_seed(N + P + C)
+    x = (torch.randn(N, P, C, generator=g) * 1.5 + 0.25).half()
+    w = torch.randn(C, generator=g) * 0.2 + 1.0
+    b = torch.randn(C, generator=g) * 0.1
+    q, s = pkg.linear.sd_group_norm_quant_rows(x.to(dev), w.to(dev), b.to(dev), G, 1e-5, rotate)
+    qo, so = oracle.sd_group_norm_quant_rows(x, w, b, G, 1e-5, rotate)
+    assert_bits_equal(s, so, "scales vs oracle"), assert_bits_equal(q, qo, "codes vs oracle")
+    from oracle import ref as R
+    if R.available():
+        qr, sr = R.sd_group_norm_quant_rows(x.to(dev), w.to(dev), b.to(dev), G, 1e-5, rotate)
+        assert_bits_equal(s, sr, "scales vs the reference kernels"), assert_bits_equal(q, qr, "codes vs the reference kernels")
