@@ -183,9 +183,11 @@ class RefImpl:
 
 def run_shapes(torch, wl, impl, dev, tag):
     """--mode shapes: every linear of the five benchmark configurations alone (GEMM with bias in the configuration's
-    activation dtype, and the quantizer that feeds it), one JSON line each. Operands smaller than the L2 are timed with
-    a 256 MB buffer written between launches."""
-    flush = torch.empty(64 * 1024 * 1024, device=dev)
+    activation dtype, and the quantizer that feeds it), one JSON line each. Operands smaller than the L2 are timed one
+    launch at a time with a 256 MB buffer read in between (a read leaves clean lines behind; after a written buffer the
+    timed kernel also pays for the write-back of the dirty lines it evicts)."""
+    flush = torch.zeros(64 * 1024 * 1024, device=dev)
+    sink = torch.zeros((), device=dev)
 
     def timed(fn, small, iters=20):
         for _ in range(3):
@@ -201,7 +203,7 @@ def run_shapes(torch, wl, impl, dev, tag):
             return e0.elapsed_time(e1) / iters * 1e3
         tot = 0.0
         for _ in range(iters):
-            flush.fill_(1.0)
+            sink.copy_(flush.sum())
             e0.record(); fn(); e1.record()
             torch.cuda.synchronize()
             tot += e0.elapsed_time(e1)
