@@ -176,6 +176,9 @@ class RefImpl:
     def quant_rows(self, x, pro, rot, q=None, scales=None):
         self.R.quant_rows(x, pro, rot, q=q, scales=scales)
 
+    def sd_quant_rows(self, x, rot):
+        return self.R.sd_quant_rows(x, rot)
+
     def int8_gemm(self, A, W, xs, ws, bias, act=0, rscale=None, resid=None, out=None):
         assert act == 0
         return self.R.int8_gemm(A, W, xs, ws, bias, rscale=rscale, resid=resid, out=out)
@@ -226,6 +229,10 @@ def run_shapes(torch, wl, impl, dev, tag):
                 X = torch.randn(M, K, device=dev).to(dt)
                 Q, S = torch.empty(M, K, dtype=torch.int8, device=dev), torch.empty(M, device=dev)
                 qus = timed(lambda: impl.quant_rows(X, 0, 1 if sp.rotate else 0, q=Q, scales=S), small)
+                line.update(quant_us=qus, quant_gbs=3.0 * M * K / qus / 1e3)
+            elif dt == torch.float16:
+                X = torch.randn(M, K, device=dev).half()
+                qus = timed(lambda: impl.sd_quant_rows(X, sp.rotate), small)
                 line.update(quant_us=qus, quant_gbs=3.0 * M * K / qus / 1e3)
             print(json.dumps(line), flush=True)
             del A, W, D

@@ -13,6 +13,7 @@
 // two register phases: each thread takes 16 consecutive elements (index bits 0-3: radix-4 stages 0 and 1), then 16
 // elements 16 apart (index bits 4-7: stages 2 and 3; groups of 64 have only stage 2), so a row is read and written
 // in shared memory twice whatever its length. Every butterfly adds in the reference's left-to-right order.
+#include <cstdlib>
 #include <cuda_fp8.h>
 
 #include "common.cuh"
@@ -156,6 +157,72 @@ __global__ void __launch_bounds__(256) sd_quant_rows_kernel(const half* __restri
     }
     __syncthreads();
     sd_quant_tail(row, red, q + m * (int64_t)K, scales + m, K, rotate, vec);
+}
+
+// The same quantizer for the run-time case (activations of every SD linear): rows in registers instead of shared memory.
+// A thread holds 16 consecutive values: stages 0 and 1 of the rotation are its own; stage 2 (and 3 for groups of 256)
+// pairs it with the three other lanes whose position differs in index bits 4-5 (6-7) through shuffles, each lane
+// computing its own output row of the H4 block with the reference's association ((+-x0 +- x1) +- x2) +- x3. Several rows
+// per CTA, row maximum through a shared-memory atomicMax. Bit-identical to the kernel above.
+template <int ROT>
+__global__ void __launch_bounds__(512) sd_quant_rows_reg_kernel(const half* __restrict__ x, int64_t x_stride,
+                                                                int8_t* __restrict__ q, float* __restrict__ scales, int M, int K,
+                                                                int tpr, int rows_per_cta) {
+    extern __shared__ unsigned amax_s[];     // [rows_per_cta]
+    for (int i = threadIdx.x; i < rows_per_cta; i += blockDim.x) amax_s[i] = 0u;
+    __syncthreads();
+    const int rloc = threadIdx.x / tpr, tin = threadIdx.x - rloc * tpr;
+    const int64_t m_raw = (int64_t)blockIdx.x * rows_per_cta + rloc;
+    const bool live = m_raw < M;
+    const int64_t m = live ? m_raw : M - 1;      // idle rows recompute the last row and store nothing
+    const half* r = x + m * x_stride + tin * 16;
+    float v[16];
+    {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(r)), b = __ldg(reinterpret_cast<const uint4*>(r) + 1);
+        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            v[2 * i] = f.x, v[2 * i + 1] = f.y;
+        }
+    }
+    if (ROT) {
+#pragma unroll
+        for (int i = 0; i < 16; i += 4) h4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h4(v[i], v[i + 4], v[i + 8], v[i + 12]);
+        const int lane = threadIdx.x & 31;
+#pragma unroll
+        for (int st = 0; st < (ROT == 256 ? 2 : 1); ++st) {
+            const int sh = st ? 4 : 1;                    // lane distance between the block's four inputs
+            const int pos = (tin / sh) & 3;               // this lane's row of the H4 block
+            const int base = lane - pos * sh;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float x0 = __shfl_sync(0xffffffffu, v[i], base), x1 = __shfl_sync(0xffffffffu, v[i], base + sh);
+                const float x2 = __shfl_sync(0xffffffffu, v[i], base + 2 * sh), x3 = __shfl_sync(0xffffffffu, v[i], base + 3 * sh);
+                const float a = pos == 3 ? -x0 : x0, b = pos == 2 ? -x1 : x1, c = pos == 1 ? -x2 : x2, d = pos == 0 ? -x3 : x3;
+                v[i] = __fmul_rn(0.5f, __fadd_rn(__fadd_rn(__fadd_rn(a, b), c), d));
+            }
+        }
+    }
+    float mx = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = rnd<half>(v[i]), mx = fmaxf(mx, fabsf(v[i]));
+    atomicMax(amax_s + rloc, __float_as_uint(mx));       // non-negative floats order as integers
+    __syncthreads();
+    mx = __uint_as_float(amax_s[rloc]);
+    const float scale = __fdiv_rn(fmaxf(mx, 1e-30f), 127.f);
+    if (live && tin == 0) scales[m] = scale;
+    const float sh16 = rnd<half>(scale);
+    const float st = sh16 > 0.f ? sh16 : scale;
+    uint32_t o[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int qi = clamp_rint_i8(rnd<half>(__fdiv_rn(v[i], st)), -128.f);
+        o[i >> 2] |= (uint32_t)(qi & 0xff) << (8 * (i & 3));
+    }
+    if (live) *reinterpret_cast<uint4*>(q + m * (int64_t)K + tin * 16) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
 // The same quantizer over a row that another of the reference's kernels would have written in half first
@@ -469,6 +536,25 @@ GPU_API int gpu_sd_quant_rows(const void* x, int64_t x_stride, int8_t* q, float*
                               void* stream) {
     if ((rotate != 0 && rotate != 64 && rotate != 256) || (rotate && K % rotate)) return -1;
     if (M <= 0 || K <= 0) return 0;
+    // register kernel: whole 16-value pieces per thread, rotation groups inside a warp, aligned rows
+    static const bool no_reg = [] { const char* e = getenv("GPU_KERNELS_SD_SMEM"); return e && e[0] == '1'; }();
+    const int tpr = K / 16;
+    if (!no_reg && K % 16 == 0 && tpr <= 512 && x_stride % 8 == 0 && (((uintptr_t)x & 15) == 0) && (((uintptr_t)q & 15) == 0)) {
+        const int gcd32 = tpr % 32 == 0 ? 32 : tpr % 16 == 0 ? 16 : tpr % 8 == 0 ? 8 : tpr % 4 == 0 ? 4 : tpr % 2 == 0 ? 2 : 1;
+        const int r0 = 32 / gcd32;                       // rows that make the CTA a whole number of warps
+        int rows = r0 * (256 / (tpr * r0) > 0 ? 256 / (tpr * r0) : 1);
+        if (rows * tpr <= 512) {
+            const int grid = (M + rows - 1) / rows, threads = rows * tpr;
+            const size_t sm = (size_t)rows * sizeof(unsigned);
+            cudaStream_t st = (cudaStream_t)stream;
+            const half* xh = (const half*)x;
+            if (rotate == 0) sd_quant_rows_reg_kernel<0><<<grid, threads, sm, st>>>(xh, x_stride, q, scales, M, K, tpr, rows);
+            else if (rotate == 64) sd_quant_rows_reg_kernel<64><<<grid, threads, sm, st>>>(xh, x_stride, q, scales, M, K, tpr, rows);
+            else sd_quant_rows_reg_kernel<256><<<grid, threads, sm, st>>>(xh, x_stride, q, scales, M, K, tpr, rows);
+            KCHECK();
+            return 0;
+        }
+    }
     const size_t smem = (size_t)padded_words(K) * sizeof(float);
     if (int rc = set_smem((const void*)sd_quant_rows_kernel, smem)) return rc;
     const int vec = (K % 8 == 0) && (x_stride % 8 == 0) && (((uintptr_t)x & 15) == 0) && (((uintptr_t)q & 7) == 0);
