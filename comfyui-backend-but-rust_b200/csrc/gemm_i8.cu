@@ -708,19 +708,21 @@ int* split_workspace(int dev, cudaStream_t st, size_t need) {
     return nullptr;
 }
 
-// Column-tile width: the candidate whose rounds x (width + fixed per-tile cost) is smallest, so that a shape
-// leaving the last round nearly empty at 256 takes a narrower tile instead.
+// Column-tile width: the candidate whose rounds x (width + fixed per-tile cost) is smallest, so that a shape leaving
+// the last round nearly empty at 256 takes a narrower tile instead; narrower tiles read A from L2 once more per column
+// tile, and on large shapes the L2 -> SM path, not the tensor core, is what the kernel waits for (up-projection: 113 us
+// at 256 against 118 at 224 and 124 at 192, although 224 has the smaller product), hence the mild penalty on width lost.
 int choose_bn(int64_t M, int64_t N, int64_t k_iters, int clusters) {
     static const int forced = env_int("GPU_KERNELS_BN", 0);
     if (forced >= 32 && forced <= 256 && forced % 32 == 0) return forced;
+    (void)k_iters;
     const int64_t tm = (M + 2 * BM - 1) / (2 * BM);
     int best = 256;
     double best_cost = 1e30;
     for (int bn = 256; bn >= 64; bn -= 32) {
         const int64_t tiles = tm * ((N + bn - 1) / bn);
-        const int64_t full = tiles / clusters, rem = tiles % clusters;
-        const double tail = rem ? 1.0 : 0.0;
-        const double cost = ((double)full + tail) * (bn + 32);
+        const int64_t rounds = (tiles + clusters - 1) / clusters;
+        const double cost = (double)rounds * (bn + 32) * (1.0 + 0.4 * (256 - bn) / 256.0);
         if (cost < best_cost) best_cost = cost, best = bn;
     }
     return best;
