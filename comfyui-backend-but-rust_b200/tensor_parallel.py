@@ -181,11 +181,27 @@ def bench_main(args, rank, world, local, metric, unit):
     rows = M // world
     x = torch.randn(rows, F, generator=torch.Generator(device=dev).manual_seed(99 + rank), device=dev).bfloat16()
 
+    # Micro-batches (BENCH_TP_MICRO, default 1 = off): the rank's rows split into independent parts, each on its own stream
+    # and walked through the stack block by block in turn, so that the collectives of one part could overlap the kernels of
+    # the other. Measured on two GPUs it does not pay: the persistent GEMM holds every SM, NCCL's kernels wait for it, and
+    # the halved GEMMs are less efficient (fast mode 105 against 99.6 ms per stack, exact 141 against 125).
+    micro = int(os.environ.get("BENCH_TP_MICRO", "1"))
+    assert rows % micro == 0
+    parts = [x[i * (rows // micro):(i + 1) * (rows // micro)].contiguous() for i in range(micro)]
+    streams = [torch.cuda.Stream(dev) for _ in range(micro)]
+
     def step():
-        h = x
+        cur = torch.cuda.current_stream()
+        hs = list(parts)
+        for s in streams:
+            s.wait_stream(cur)
         for b in stack:
-            h = b.forward(h)
-        return h
+            for i, s in enumerate(streams):
+                with torch.cuda.stream(s):
+                    hs[i] = b.forward(hs[i])
+        for s in streams:
+            cur.wait_stream(s)
+        return hs
 
     for _ in range(max(1, args.warmup)):
         step()
@@ -211,6 +227,7 @@ def bench_main(args, rank, world, local, metric, unit):
                           "vs_baseline": None, "dtype": "int8", "data": "synthetic",
                           "config": {"workload": f"mmdit_linear_stack_{blocks}blocks_M16896_hidden3072", "parallelism": f"tp{world}",
                                      "mode": "exact (int32 reduce-scatter)" if exact else "fast (bf16 reduce-scatter)",
+                                     "micro_batches": micro,
                                      "dit_block_gemm_ms": ms / args.steps / blocks},
                           "gpu_launches": args.steps * blocks * (10 if exact else 8), "kernel_status": ops.kernel_status()}), flush=True)
     if world > 1:
