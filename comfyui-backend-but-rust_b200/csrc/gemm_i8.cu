@@ -380,10 +380,18 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         continue;
                     }
 #endif
-                    if (leader) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * stage_bytes);
+#ifdef GEMM_PROFILE
+                    const bool skip_a = (p.dbg & 4) && (cluster_id & 1);   // experiment: half the clusters do not load A (wrong results)
+                    const bool skip_b = (p.dbg & 8) && (cluster_id & 1);
+#else
+                    constexpr bool skip_a = false, skip_b = false;
+#endif
+                    if (leader) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * KS * ((skip_a ? 0 : a_bytes) + (skip_b ? 0 : b_bytes)));
                     const uint32_t full = mapa_shared(bar_full + 8 * stage, 0);
                     for (int ks = 0; ks < KS; ++ks) {
+                        if (!skip_a)
                         tma_load_2d_pair(sA + (stage * KS + ks) * a_bytes, &tmap_a, (kb * KS + ks) * BK, row_a, full);
+                        if (!skip_b)
                         tma_load_2d_pair(sB + (stage * KS + ks) * b_bytes, &tmap_w, (kb * KS + ks) * BK, row_w, full);
                     }
                     if (++stage == S) { stage = 0; phase ^= 1u; }
