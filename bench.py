@@ -312,8 +312,8 @@ def run_reference_cpu(args, rank):
 
 
 # DRAM bytes (read + write) of one launch of the dominant kernel, from the ncu capture summarised in
-# profiles/gemm_i8_pair_mlp_up.md (same shape, full size: 99.7 MB read + 75.7 MB written).
-GEMM_UP_DRAM_BYTES_PER_LAUNCH = 175.4e6
+# profiles/gemm_i8_pair_mlp_up.md (same shape, full size: 100.6 MB read + 76.0 MB written).
+GEMM_UP_DRAM_BYTES_PER_LAUNCH = 176.6e6
 
 
 def main():

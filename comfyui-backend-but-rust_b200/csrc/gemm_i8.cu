@@ -30,6 +30,7 @@
 
 #include "common.cuh"
 #include "epilogue.cuh"
+#include "w6_decode.cuh"
 
 __device__ int g_kernel_status = 0;
 #ifdef GEMM_PROFILE

@@ -17,6 +17,7 @@
 #include <cuda_fp8.h>
 
 #include "common.cuh"
+#include "w6_decode.cuh"
 
 namespace {
 
@@ -519,6 +520,31 @@ __global__ void __launch_bounds__(256) w6_requant_kernel(const bf16* __restrict_
     }
 }
 
+// The same with 32 codes (one whole scale group when G is a multiple of 32) per thread and the permute-table decode of
+// w6_decode.cuh: 16 + 8 bytes in, 32 bytes out per thread. The decode form is voted per warp, so every lane takes part
+// (lanes past the end redo the last piece and store nothing).
+__global__ void __launch_bounds__(256) w6_decode32_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ s_rel,
+                                                          int8_t* __restrict__ out, int64_t N, int K, int G) {
+    const int64_t per = K / 32;
+    const int64_t total = N * per;
+    const int64_t i_raw = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool live = i_raw < total;
+    const int64_t i = live ? i_raw : total - 1;
+    const int64_t n = i / per;
+    const int c = (int)(i - n * per);
+    const uint8_t* row = q + n * (int64_t)(K / 4 * 3);
+    const uint4 lo = __ldg(reinterpret_cast<const uint4*>(row + c * 16));
+    const uint2 hi = __ldg(reinterpret_cast<const uint2*>(row + K / 2 + c * 8));
+    const uint32_t sb = s_rel[n * (K / G) + c * 32 / G];
+    uint32_t o[8];
+    w6_group(lo, hi.x, hi.y, sb, o);
+    if (live) {
+        uint4* d = reinterpret_cast<uint4*>(out + n * (int64_t)K + c * 32);
+        d[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        d[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+}
+
 int set_smem(const void* fn, size_t bytes) {
     if (bytes <= 48 * 1024) return 0;
     const cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
@@ -680,8 +706,16 @@ GPU_API int gpu_dequant_i8(const int8_t* q, const float* s, float* out, int64_t 
 // out = clamp(rint((code - 32) * s_rel), +-127). K % 32 == 0 and G % 16 == 0, as the reference requires.
 GPU_API int gpu_w6_decode(const void* q, const void* s_rel, void* out, int64_t N, int K, int G, void* stream) {
     if (K % 32 || G % 16) return -1;
+    if (N <= 0 || K <= 0) return 0;
+    // rows of 3K/4 bytes keep the 16-byte pieces of the nibble plane aligned when K % 64 == 0 (8-byte pieces of the other plane too)
+    if (G % 32 == 0 && K % 64 == 0 && (((uintptr_t)q | (uintptr_t)out) & 15) == 0) {
+        const int64_t n32 = N * (K / 32);
+        w6_decode32_kernel<<<(unsigned)((n32 + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const uint8_t*)q, (const uint8_t*)s_rel,
+                                                                                          (int8_t*)out, N, K, G);
+        KCHECK();
+        return 0;
+    }
     const int64_t n = N * (K / 16);
-    if (n <= 0) return 0;
     w6_decode_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const uint8_t*)q, (const uint8_t*)s_rel,
                                                                                  (int8_t*)out, N, K, G);
     KCHECK();

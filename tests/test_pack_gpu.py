@@ -218,3 +218,19 @@ def test_sd_group_norm_quantizer(pkg, oracle, dev, N, P, C, G, rotate):
     if R.available():
         qr, sr = R.sd_group_norm_quant_rows(x.to(dev), w.to(dev), b.to(dev), G, 1e-5, rotate)
         assert_bits_equal(s, sr, "scales vs the reference kernels"), assert_bits_equal(q, qr, "codes vs the reference kernels")
+
+
+def test_argument_checks_of_the_packers_and_fused_quantizers(pkg, dev):
+    L = pkg.linear
+    with pytest.raises(RuntimeError, match="-1"):
+        L.w6_requant(torch.zeros((4, 384), dtype=torch.bfloat16, device=dev))                  # K % 256
+    x = torch.zeros((4, 640), dtype=torch.float16, device=dev)
+    w = torch.ones(640, device=dev)
+    with pytest.raises(RuntimeError, match="-1"):
+        L.sd_ln_quant_rows(x, w, w, 1e-5, 256)                                                 # 640 % 256
+    with pytest.raises(RuntimeError, match="-1"):
+        L.sd_geglu_quant_rows(x, 128)                                                          # rotate must be 0, 64 or 256
+    with pytest.raises(RuntimeError, match="-1"):
+        L.sd_group_norm_quant_rows(x.view(1, 4, 640), w, w, 48, 1e-5, 0)                       # 640 % 48
+    q, s = L.sd_unpad_quant_rows(torch.zeros((0, 10, 72), dtype=torch.float16, device=dev), 64, 64)   # no rows: nothing to do
+    assert q.shape == (0, 640)
