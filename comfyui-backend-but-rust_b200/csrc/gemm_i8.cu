@@ -617,9 +617,48 @@ EncodeTiledFn encode_fn() {
     return f;
 }
 
+bool encode_operand_tmap(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t cols, int box_rows);
+bool encode_output_tmap(CUtensorMap* tm, void* ptr, int64_t M, int64_t N, int esz);
+
+// Encoded tensor maps depend only on address, shape and box, not on the data: an inference loop presents the same
+// buffers again and again, so each thread remembers its last few (a map is 128 bytes; the driver call that encodes
+// one takes about a microsecond of host time, three per GEMM call).
+struct TmapKey {
+    const void* ptr;
+    int64_t d0, d1, pitch;
+    int box0, box1, kind;     // kind: element type and swizzle
+    bool operator==(const TmapKey& o) const {
+        return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && pitch == o.pitch && box0 == o.box0 && box1 == o.box1 && kind == o.kind;
+    }
+};
+struct TmapCache {
+    static constexpr int kSlots = 16;
+    TmapKey key[kSlots] = {};
+    CUtensorMap map[kSlots];
+    bool used[kSlots] = {};
+    int next = 0;
+    const CUtensorMap* find(const TmapKey& k) const {
+        for (int i = 0; i < kSlots; ++i)
+            if (used[i] && key[i] == k) return &map[i];
+        return nullptr;
+    }
+    void put(const TmapKey& k, const CUtensorMap& m) {
+        key[next] = k, map[next] = m, used[next] = true;
+        next = (next + 1) % kSlots;
+    }
+};
+thread_local TmapCache g_tmaps;
+
 // Tensor map of a row-major int8 matrix [rows, cols] (cols contiguous), box 128 bytes x box_rows, 128-byte swizzle.
 // Rows and columns beyond the matrix read as zero.
 bool make_operand_tmap(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t cols, int box_rows) {
+    const TmapKey k{ptr, cols, rows, cols, BK, box_rows, 0};
+    if (const CUtensorMap* hit = g_tmaps.find(k)) { *tm = *hit; return true; }
+    if (!encode_operand_tmap(tm, ptr, rows, cols, box_rows)) return false;
+    g_tmaps.put(k, *tm);
+    return true;
+}
+bool encode_operand_tmap(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t cols, int box_rows) {
     EncodeTiledFn enc = encode_fn();
     if (!enc) return false;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -633,6 +672,13 @@ bool make_operand_tmap(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t c
 // Tensor map of the output [M, N] for stores of 32 x 32-element boxes: 64-byte rows (64-byte swizzle) for 2-byte
 // elements, 128-byte rows (128-byte swizzle) for 4-byte elements.
 bool make_output_tmap(CUtensorMap* tm, void* ptr, int64_t M, int64_t N, int esz) {
+    const TmapKey k{ptr, N, M, N * esz, 32, 32, esz == 2 ? 1 : 2};
+    if (const CUtensorMap* hit = g_tmaps.find(k)) { *tm = *hit; return true; }
+    if (!encode_output_tmap(tm, ptr, M, N, esz)) return false;
+    g_tmaps.put(k, *tm);
+    return true;
+}
+bool encode_output_tmap(CUtensorMap* tm, void* ptr, int64_t M, int64_t N, int esz) {
     EncodeTiledFn enc = encode_fn();
     if (!enc) return false;
     const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
