@@ -1,4 +1,6 @@
-"""Builds libgpu_kernels.so (the C-ABI library) from csrc/*.cu with nvcc, for sm_100a only.
+"""Builds libb200_qlinear.so (the C-ABI library) and libb200_qlinear.a (the same objects as a static archive, for hosts
+that link statically) from csrc/*.cu with nvcc, for sm_100a only. The name differs on purpose from the reference's own
+static library `gpu_kernels`, which keeps supplying every symbol this library does not replace.
 
 The GEMM uses tcgen05.mma kind::i8, which exists on sm_100a and not on sm_103a or sm_120: no other -gencode
 may be added. No fast-math: the rounding points of the quantizer and of the epilogue are part of the contract.
@@ -13,7 +15,8 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
-LIB = os.path.join(HERE, "libgpu_kernels.so")
+LIB = os.path.join(HERE, "libb200_qlinear.so")
+ARCHIVE = os.path.join(HERE, "libb200_qlinear.a")
 UNITS = ["quant_rows", "gemm_i8", "gemm_skinny", "weight_pack"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
@@ -47,6 +50,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
         objs = list(ex.map(compile_unit, UNITS))
     if force or _stale(LIB, objs):
         subprocess.check_call([NVCC, "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"])
+    if force or _stale(ARCHIVE, objs):
+        if os.path.exists(ARCHIVE):
+            os.remove(ARCHIVE)
+        subprocess.check_call(["ar", "rcs", ARCHIVE] + objs)
     return LIB
 
 

@@ -32,7 +32,15 @@ struct SkinnyParams {
     int M, N, K;
     int act;
 };
+// Helpers shared between the translation units (a namespace of their own: the static archive exports them).
+namespace b200q {
 // quant_rows.cu: table of bf16(act(x)) over all bf16 x for Act code `act`, built on first use (on `st`)
 int act_lut_ptr(int act, cudaStream_t st, const uint16_t** out);
+// quant_rows.cu: the quantizer's status word (non-zero after a staging wait ran out), read and cleared
+int quant_status_read_clear(int* out);
 bool skinny_gemm_applies(int64_t M, int64_t N, int64_t K);
 int launch_skinny_gemm(int epi, const SkinnyParams& p, int out_dt, int sms, cudaStream_t st);
+// gemm_skinny.cu: the CUDA-core kernel for operands TMA cannot address (K % 16 != 0, bases off a 16-byte boundary)
+int launch_generic_gemm(int epi, const SkinnyParams& p, int out_dt, cudaStream_t st);
+}  // namespace b200q
+using namespace b200q;

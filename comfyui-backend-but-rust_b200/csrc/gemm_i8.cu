@@ -20,6 +20,7 @@
 //     TMA stores (full-line writes; a direct-store path serves outputs that TMA cannot address)
 //   - the persistent grid walks the tiles round-robin; bn is chosen per shape so the last round is not mostly idle
 // Every wait is bounded; a wait that runs out records a code in g_kernel_status and the CTA pair unwinds.
+#include <algorithm>
 #include <atomic>
 #include <cmath>
 #include <cstdlib>
@@ -33,15 +34,6 @@
 #include "w6_decode.cuh"
 
 __device__ int g_kernel_status = 0;
-#ifdef GEMM_PROFILE
-// debug build only: per-CTA cycle counts
-__device__ unsigned long long g_prof[160][8];
-#define PROF_T0() const long long prof_t0__ = clock64()
-#define PROF_ADD(slot) g_prof[blockIdx.x][slot] += (unsigned long long)(clock64() - prof_t0__)
-#else
-#define PROF_T0()
-#define PROF_ADD(slot)
-#endif
 
 namespace {
 
@@ -76,14 +68,17 @@ struct GemmParams {
     int splits;          // K slices per split tile (>= 2), or 0: work items [whole_tiles, whole_tiles + rem * splits)
     int kps;             // stages per K slice
     int num_items;       // whole_tiles + split tiles * splits
-    int* scratch;        // counters [split tiles][2][4][8], zero between launches
-    int* partials;       // [split tiles][2][4][8][32 values][32 lanes] int32 sums, zero between launches
+    // Streamed tail: when the tiles do not fill the last round, the last one to two rounds' tiles are dealt out in K stages
+    // instead of whole tiles, every cluster taking an equal run of consecutive stages. A tile that straddles two clusters
+    // is finished by the one that holds its first stages (it reaches them last); the other, which starts with the tile's
+    // last stages, parks its raw accumulators in `partials`.
+    int dp_tiles;        // tiles of the whole rounds before the streamed part (work items [0, dp_tiles), round-robin)
+    int sk_units;        // K stages of the streamed part = (num_tiles - dp_tiles) * k_iters, or 0
+    int* scratch;        // counters [slot][2][4][8], zero between launches
+    int* partials;       // [slot][2][4][8][32 values][32 lanes] int32 sums, zero between launches
     uint32_t idesc;      // instruction descriptor for M = 256, N = bn
     const uint16_t* act_lut;   // EPI_ACT with bf16 outputs: bf16(act(x)) for every bf16 x (a tanhf or erff per element
                                // made the epilogue, not the tensor core, the limit: 836 against 2740 TOPS), or null
-#ifdef GEMM_PROFILE
-    int dbg;             // debug build: bit 0 skips the TMA loads, bit 1 skips the MMAs
-#endif
 };
 
 // Tile order: bands of 8 row tiles, column tile fastest-varying across the band's rows, so that the clusters
@@ -99,14 +94,49 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
     tn = r / gsize;
 }
 
-// Work item -> tile, K range (in stages) and, for a slice of a split tile, its slice and slot numbers.
-struct WorkItem { int tile, k0, kn, split, slot; };
-__device__ __forceinline__ WorkItem decode_item(const GemmParams& p, int w) {
-    if (w < p.whole_tiles) return {w, 0, p.k_iters, -1, 0};
+// A work item: a tile, a K range (in stages) and what happens to the accumulator.
+enum ItemKind { ITEM_WHOLE = 0, ITEM_SLICE = 1, ITEM_PARK = 2, ITEM_FINISH = 3 };
+struct WorkItem { int tile, k0, kn, kind, slot; };
+// The sequence of work items of one cluster; every role of the cluster walks its own copy.
+struct WorkCursor {
+    int w;          // next round-robin item
+    int u;          // streamed part: next K stage of this cluster's run
+};
+__device__ __forceinline__ WorkCursor first_item(const GemmParams& p, int cluster_id, int nclusters) {
+    return {cluster_id, p.sk_units > 0 ? (int)(((long long)p.sk_units * cluster_id) / nclusters) : 0};
+}
+__device__ __forceinline__ bool next_item(const GemmParams& p, WorkCursor& c, int cluster_id, int nclusters, WorkItem& wi) {
+    if (p.sk_units > 0) {
+        // The streamed run comes first, so that its slower hand-over (global scratch, fences) hides under the whole tiles
+        // that follow and every cluster ends on a whole tile at the same time.
+        const int u_end = (int)(((long long)p.sk_units * (cluster_id + 1)) / nclusters);
+        if (c.u < u_end) {
+            const int t = c.u / p.k_iters, k0 = c.u - t * p.k_iters;
+            const int kn = min(p.k_iters - k0, u_end - c.u);
+            c.u += kn;
+            // a run starts with the last stages of a tile (parked for the previous cluster) and ends with the first stages
+            // of another (finished here with what the next cluster parked as its own first item)
+            const int kind = kn == p.k_iters ? ITEM_WHOLE : (k0 > 0 ? ITEM_PARK : ITEM_FINISH);
+            wi = {p.dp_tiles + t, k0, kn, kind, kind == ITEM_PARK ? cluster_id - 1 : cluster_id};
+            return true;
+        }
+        if (c.w >= p.dp_tiles) return false;
+        wi = {c.w, 0, p.k_iters, ITEM_WHOLE, 0};
+        c.w += nclusters;
+        return true;
+    }
+    if (c.w >= p.num_items) return false;
+    const int w = c.w;
+    c.w += nclusters;
+    if (w < p.whole_tiles) {
+        wi = {w, 0, p.k_iters, ITEM_WHOLE, 0};
+        return true;
+    }
     const int j = w - p.whole_tiles;
     const int slot = j / p.splits, sidx = j - slot * p.splits;
     const int k0 = sidx * p.kps;
-    return {p.whole_tiles + slot, k0, min(p.kps, p.k_iters - k0), sidx, slot};
+    wi = {p.whole_tiles + slot, k0, min(p.kps, p.k_iters - k0), ITEM_SLICE, slot};
+    return true;
 }
 constexpr int kCountersPerSlot = 2 * 4 * 8;   // CTA of the pair x TMEM lane quarter x 32-column chunk
 
@@ -332,7 +362,6 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
     const int nclusters = gridDim.x >> 1, cluster_id = blockIdx.x >> 1;
-    PROF_T0();
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < S; ++i) {
@@ -365,34 +394,19 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int w = cluster_id; w < p.num_items && ok; w += nclusters) {
-                const WorkItem wi = decode_item(p, w);
+            WorkCursor cur = first_item(p, cluster_id, nclusters);
+            WorkItem wi;
+            while (ok && next_item(p, cur, cluster_id, nclusters, wi)) {
                 int tm, tn;
                 tile_coords(wi.tile, p.tiles_m, p.tiles_n, tm, tn);
                 const int row_a = tm * (2 * BM) + (int)rank * BM;
                 const int row_w = tn * BN + (int)rank * (BN / 2);
                 for (int kb = wi.k0; kb < wi.k0 + wi.kn; ++kb) {
                     if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_s, ST_TIMEOUT_EMPTY)) { ok = false; break; }
-#ifdef GEMM_PROFILE
-                    if (p.dbg & 1) {
-                        if (!leader) { ok = false; break; }
-                        mbar_arrive(bar_full + 8 * stage);
-                        if (++stage == S) { stage = 0; phase ^= 1u; }
-                        continue;
-                    }
-#endif
-#ifdef GEMM_PROFILE
-                    const bool skip_a = (p.dbg & 4) && (cluster_id & 1);   // experiment: half the clusters do not load A (wrong results)
-                    const bool skip_b = (p.dbg & 8) && (cluster_id & 1);
-#else
-                    constexpr bool skip_a = false, skip_b = false;
-#endif
-                    if (leader) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * KS * ((skip_a ? 0 : a_bytes) + (skip_b ? 0 : b_bytes)));
+                    if (leader) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * KS * (a_bytes + b_bytes));
                     const uint32_t full = mapa_shared(bar_full + 8 * stage, 0);
                     for (int ks = 0; ks < KS; ++ks) {
-                        if (!skip_a)
                         tma_load_2d_pair(sA + (stage * KS + ks) * a_bytes, &tmap_a, (kb * KS + ks) * BK, row_a, full);
-                        if (!skip_b)
                         tma_load_2d_pair(sB + (stage * KS + ks) * b_bytes, &tmap_w, (kb * KS + ks) * BK, row_w, full);
                     }
                     if (++stage == S) { stage = 0; phase ^= 1u; }
@@ -418,8 +432,10 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             int buf = 0;
             uint32_t tphase = 0;
             bool ok = true;
-            for (int w = cluster_id; w < p.num_items && ok; w += nclusters) {
-                const int kn = decode_item(p, w).kn;
+            WorkCursor cur = first_item(p, cluster_id, nclusters);
+            WorkItem wi;
+            while (ok && next_item(p, cur, cluster_id, nclusters, wi)) {
+                const int kn = wi.kn;
                 if (!mbar_wait(bar_tempty + 8 * buf, tphase ^ 1u, abort_s, ST_TIMEOUT_TMEM_EMPTY)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * 256;
@@ -427,9 +443,6 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     if (!mbar_try_wait(bar_f, phase)) {
                         if (!mbar_wait(bar_f, phase, abort_s, ST_TIMEOUT_FULL)) { ok = false; break; }
                     }
-#ifdef GEMM_PROFILE
-                    if (!(p.dbg & 2))
-#endif
                     {
                         umma_i8_pair_lo(d_tmem, a_lo, b_lo, idesc, kb);
                         umma_i8_pair_lo(d_tmem, a_lo + 2, b_lo + 2, idesc, 1);   // +32 bytes inside the swizzle row
@@ -466,8 +479,9 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         float* my_vec = reinterpret_cast<float*>(my_stage + 2048);   // ws[128] | bias[128] | rscale[128]
         int buf = 0;
         uint32_t tphase = 0;
-        for (int w = cluster_id; w < p.num_items; w += nclusters) {
-            const WorkItem wi = decode_item(p, w);
+        WorkCursor cur = first_item(p, cluster_id, nclusters);
+        WorkItem wi;
+        while (next_item(p, cur, cluster_id, nclusters, wi)) {
             int tm, tn;
             tile_coords(wi.tile, p.tiles_m, p.tiles_n, tm, tn);
             const int n0 = tn * BN;
@@ -491,9 +505,7 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 }
                 __syncwarp();
             }
-            PROF_T0();
             if (!mbar_wait_warp_relaxed(bar_tfull + 8 * buf, tphase, abort_s, ST_TIMEOUT_TMEM_FULL)) break;
-            if (threadIdx.x == 64) PROF_ADD(3);
             tc_fence_after();
             const uint32_t taddr = tmem_base + buf * 256 + ((uint32_t)(quad * 32) << 16);
             // two register sets: the load of the next chunk is in flight while this one is processed
@@ -523,9 +535,7 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     chunk_direct<OutT, EPI>(p, r, row, col0, xs_r);
                 }
             };
-            // A slice of a split tile parks its raw accumulators in global scratch; the slice that arrives last at the
-            // chunk's counter adds the others to its own and runs the epilogue (release/acquire through the fences).
-            if (wi.split < 0) {
+            if (wi.kind == ITEM_WHOLE) {
                 int c = half;
                 if (c < nchunks) tmem_ld32(taddr + c * 32, ra);
 #pragma unroll 1
@@ -540,39 +550,78 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     }
                 }
             } else {
-                // A slice of a split tile (at most one per cluster, in the last round) adds its raw accumulators into the
-                // tile's int32 buffer in global scratch with atomic adds (integer sums do not depend on the order); the
-                // slice that arrives last at a chunk's counter reads the total, leaves buffer and counter at zero for
-                // the next launch, and runs the epilogue (release / acquire through the fences around the counter).
+                // The accumulator holds only part of the tile's K range; the parts meet in global scratch: per warp chunk a
+                // buffer of [32 values][32 lanes] int32 and a counter, all zero between launches.
+                //   ITEM_SLICE   (few-tile problem cut along K) every slice adds its part with atomic adds (integer sums do
+                //                not depend on the order); the slice that arrives last at the chunk's counter reads the total
+                //   ITEM_PARK    (streamed tail, the last K stages of a tile; the cluster's first item) plain stores of all
+                //                the warp's chunks, one fence, then the counter of the warp's first chunk is raised
+                //   ITEM_FINISH  (streamed tail, the first K stages) waits, bounded, for that counter and adds what is parked
+                // Whoever ends up with the total leaves buffer and counter at zero and runs the epilogue (release / acquire
+                // through the fences around the counter).
+                const int sub0 = ((int)rank * 4 + quad) * 8;
+                int* cnt0 = p.scratch + wi.slot * kCountersPerSlot + sub0 + half;
+                bool proceed = true;
+                if (wi.kind == ITEM_FINISH) {
+                    int seen = 1;
+                    if (lane == 0) {
+                        volatile int* vc = cnt0;
+                        seen = *vc;
+                        if (!seen) {
+                            const uint64_t t0 = globaltimer_ns();
+                            while (!(seen = *vc)) {
+                                __nanosleep(64);
+                                if (*abort_s || globaltimer_ns() - t0 > kWaitLimitNs) break;
+                            }
+                        }
+                        if (seen) *vc = 0;
+                        else if (!*abort_s) *abort_s = ST_TIMEOUT_PARKED;
+                    }
+                    proceed = __shfl_sync(0xffffffffu, seen, 0) != 0;
+                    __threadfence();
+                }
+                if (!proceed) break;
 #pragma unroll 1
                 for (int c = half; c < nchunks; c += 2) {
                     tmem_ld32(taddr + c * 32, ra);
                     tmem_ld_wait();
                     if (n0 + c * 32 >= p.N) continue;
-                    const int sub = ((int)rank * 4 + quad) * 8 + c;
-                    int* sum = p.partials + ((size_t)wi.slot * kCountersPerSlot + sub) * 1024 + lane;   // [32 values][32 lanes]
+                    int* sum = p.partials + ((size_t)wi.slot * kCountersPerSlot + sub0 + c) * 1024 + lane;
+                    if (wi.kind == ITEM_PARK) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) atomicAdd(sum + 32 * j, (int)ra[j]);
-                    __threadfence();
-                    __syncwarp();
-                    int* cnt = p.scratch + wi.slot * kCountersPerSlot + sub;
-                    int old = 0;
-                    if (lane == 0) old = atomicAdd(cnt, 1);
-                    old = __shfl_sync(0xffffffffu, old, 0);
-                    if (old != p.splits - 1) continue;
-                    if (lane == 0) *cnt = 0;
-                    __threadfence();
+                        for (int j = 0; j < 32; ++j) __stcg(sum + 32 * j, (int)ra[j]);
+                        continue;
+                    }
+                    if (wi.kind == ITEM_SLICE) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) atomicAdd(sum + 32 * j, (int)ra[j]);
+                        __threadfence();
+                        __syncwarp();
+                        int* cnt = p.scratch + wi.slot * kCountersPerSlot + sub0 + c;
+                        int old = 0;
+                        if (lane == 0) old = atomicAdd(cnt, 1);
+                        old = __shfl_sync(0xffffffffu, old, 0);
+                        if (old != p.splits - 1) continue;
+                        if (lane == 0) *cnt = 0;
+                        __threadfence();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) ra[j] = 0;
+                    }
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        ra[j] = (uint32_t)__ldcg(sum + 32 * j);
+                        ra[j] += (uint32_t)__ldcg(sum + 32 * j);
                         __stcg(sum + 32 * j, 0);
                     }
                     emit(ra, c);
                 }
+                if (wi.kind == ITEM_PARK) {
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) atomicExch(cnt0, 1);
+                }
             }
             tc_fence_before();
             __syncwarp();
-            if (threadIdx.x == 64) PROF_ADD(5);   // wait + drain of this tile
             if (lane == 0) mbar_arrive_cluster(mapa_shared(bar_tempty + 8 * buf, 0));
             buf ^= 1;
             if (buf == 0) tphase ^= 1u;
@@ -585,7 +634,6 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     tc_fence_before();
     __syncthreads();
     cluster_sync_all();   // nobody leaves while the peer may still signal its barriers or read its tiles
-    if (threadIdx.x == 0) PROF_ADD(4);
     if (*abort_s != 0) {
         // a wait ran out: leave time for copies and MMAs still in flight, then report
         for (int i = 0; i < 2000; ++i) __nanosleep(1000);
@@ -699,11 +747,6 @@ int device_sm_count(int dev) {
     return c;
 }
 
-int env_int(const char* name, int dflt) {
-    const char* v = getenv(name);
-    return v && *v ? atoi(v) : dflt;
-}
-
 template <typename OutT, int EPI>
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& td, const GemmParams& p, int grid,
                 cudaStream_t st) {
@@ -732,52 +775,69 @@ int launch_pair_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tw, const
     }
 }
 
-// Scratch of the split tail: per device and stream, one buffer allocated on first need and kept (a stream-ordered
-// allocation per call cost more host time than the tail saves). Counters and sums start at zero and every kernel leaves them
-// at zero. A stream beyond the few slots, or a failed allocation, simply runs without the split.
-constexpr size_t kSplitWorkspaceBytes = (size_t)40 * 256 * 256 * 4 + (1 << 16);   // up to clusters/2 split tiles of 256 x 256 int32
+// Scratch of the K-split forms (split few-tile problems, streamed tail): per device and stream, one buffer allocated on
+// first need and kept (a stream-ordered allocation per call cost more host time than the split saves). Counters and sums
+// are zero between launches: the buffer is cleared on the caller's stream before its first use, every kernel leaves it at
+// zero, and after a kernel has reported a bounded wait that ran out (gpu_kernels_status) it is cleared again before
+// the next use. A stream beyond the few slots, a failed allocation or a stream under capture that has no buffer yet
+// simply runs without the split.
+constexpr int kWorkspaceSlots = 80;                       // tiles of 256 x 256 int32 sums (one per cluster at most)
+constexpr size_t kWorkspaceCounterBytes = 1 << 16;        // counters first, sums behind them
+constexpr size_t kSplitWorkspaceBytes = (size_t)kWorkspaceSlots * 256 * 256 * 4 + kWorkspaceCounterBytes;
+std::atomic<uint64_t> g_workspace_epoch{1};               // raised when a kernel may have left scratch behind
 int* split_workspace(int dev, cudaStream_t st, size_t need) {
-    struct Slot { cudaStream_t st; int* buf; bool used; };
+    struct Slot { cudaStream_t st; int* buf; bool used; uint64_t clean_epoch; };
     static Slot slots[64][4];
     static std::mutex mu;
     if (need > kSplitWorkspaceBytes) return nullptr;
     std::lock_guard<std::mutex> lk(mu);
     Slot* s = slots[dev & 63];
-    for (int i = 0; i < 4; ++i)
-        if (s[i].used && s[i].st == st) return s[i].buf;
-    for (int i = 0; i < 4; ++i) {
-        if (s[i].used) continue;
-        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    Slot* hit = nullptr;
+    for (int i = 0; i < 4 && !hit; ++i)
+        if (s[i].used && s[i].st == st) hit = &s[i];
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    const uint64_t epoch = g_workspace_epoch.load(std::memory_order_acquire);
+    if (!hit || hit->clean_epoch != epoch) {
         if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
             (void)cudaGetLastError();
-            return nullptr;   // no allocation while the stream is being captured
+            return nullptr;   // neither an allocation nor a clear while the stream is being captured
         }
+    }
+    for (int i = 0; i < 4 && !hit; ++i) {
+        if (s[i].used) continue;
         void* b = nullptr;
-        if (cudaMalloc(&b, kSplitWorkspaceBytes) != cudaSuccess || cudaMemset(b, 0, kSplitWorkspaceBytes) != cudaSuccess) {
+        if (cudaMalloc(&b, kSplitWorkspaceBytes) != cudaSuccess) {
             (void)cudaGetLastError();
             return nullptr;
         }
-        s[i] = {st, reinterpret_cast<int*>(b), true};
-        return s[i].buf;
+        s[i] = {st, reinterpret_cast<int*>(b), true, 0};
+        hit = &s[i];
     }
-    return nullptr;
+    if (!hit) return nullptr;
+    if (hit->clean_epoch != epoch) {
+        if (cudaMemsetAsync(hit->buf, 0, kSplitWorkspaceBytes, st) != cudaSuccess) {   // ordered before the kernel that uses it
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        hit->clean_epoch = epoch;
+    }
+    return hit->buf;
 }
 
 // Column-tile width: the candidate whose rounds x (width + fixed per-tile cost) is smallest, so that a shape leaving
 // the last round nearly empty at 256 takes a narrower tile instead; narrower tiles read A from L2 once more per column
 // tile, and on large shapes the L2 -> SM path, not the tensor core, is what the kernel waits for (up-projection: 113 us
 // at 256 against 118 at 224 and 124 at 192, although 224 has the smaller product), hence the mild penalty on width lost.
-int choose_bn(int64_t M, int64_t N, int64_t k_iters, int clusters) {
-    static const int forced = env_int("GPU_KERNELS_BN", 0);
-    if (forced >= 32 && forced <= 256 && forced % 32 == 0) return forced;
-    (void)k_iters;
+// With the streamed tail available a ragged last round costs only its share of a round (plus the hand-over).
+int choose_bn(int64_t M, int64_t N, int clusters, bool can_stream) {
     const int64_t tm = (M + 2 * BM - 1) / (2 * BM);
     int best = 256;
     double best_cost = 1e30;
     for (int bn = 256; bn >= 64; bn -= 32) {
         const int64_t tiles = tm * ((N + bn - 1) / bn);
-        const int64_t rounds = (tiles + clusters - 1) / clusters;
-        const double cost = (double)rounds * (bn + 32) * (1.0 + 0.4 * (256 - bn) / 256.0);
+        double rounds = (double)((tiles + clusters - 1) / clusters);
+        if (can_stream && tiles > clusters && tiles % clusters) rounds = std::min(rounds, (double)tiles / clusters + 0.15);
+        const double cost = rounds * (bn + 32) * (1.0 + 0.4 * (256 - bn) / 256.0);
         if (cost < best_cost) best_cost = cost, best = bn;
     }
     return best;
@@ -791,12 +851,17 @@ int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const f
     if (epi == EPI_RESID && (!rscale || !resid)) return -201;
     if (epi != EPI_ACC && (out_dt < 0 || out_dt > 2)) return epi == EPI_RESID ? -201 : -200;
     if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return -200;
-    // TMA needs 16-byte aligned bases and row pitch
-    if ((K % 16) != 0 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return -202;
+    // like the reference, rows must at least be a whole number of 8-byte pieces (its narrowest tile configurations,
+    // csrc/vendor/cutlass_gemm_int8.cu:265-267); it answers anything else with its "no configuration" code
+    if ((K % 8) != 0) return epi == EPI_RESID ? -201 : -200;
     int dev = 0;
     cudaGetDevice(&dev);
-    static const int no_skinny = env_int("GPU_KERNELS_NO_SKINNY", 0);
-    if (!no_skinny && skinny_gemm_applies(M, N, K)) {
+    // TMA needs 16-byte aligned bases and row pitch; what it cannot address takes the CUDA-core kernel
+    if ((K % 16) != 0 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) {
+        SkinnyParams sp{A, W, xs, ws, bias, rscale, resid, D, (int)M, (int)N, (int)K, act};
+        return launch_generic_gemm(epi, sp, out_dt, st);
+    }
+    if (skinny_gemm_applies(M, N, K)) {
         SkinnyParams sp{A, W, xs, ws, bias, rscale, resid, D, (int)M, (int)N, (int)K, act};
         return launch_skinny_gemm(epi, sp, out_dt, device_sm_count(dev), st);
     }
@@ -809,18 +874,24 @@ int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const f
     if (epi == EPI_ACT && out_dt == DT_BF16 && M * N >= (1 << 20)) {
         if (int rc = act_lut_ptr(act, st, &p.act_lut)) return rc;
     }
-#ifdef GEMM_PROFILE
-    p.dbg = env_int("GEMM_DBG", 0);
-#endif
     const int esz = epi == EPI_ACC ? 4 : (out_dt == DT_F32 ? 4 : 2);
     auto al16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
     p.vec_ok = (N % 8 == 0) && al16(D) && al16(ws) && al16(bias) && al16(rscale) && al16(resid);
-    static const int no_tma_store = env_int("GPU_KERNELS_DIRECT_STORE", 0);
-    p.tma_store = !no_tma_store && al16(D) && ((N * esz) % 16 == 0);
-    static const int ksub_env = env_int("GPU_KERNELS_KSUB", 2);
-    p.ksub = (ksub_env == 1 || K <= BK) ? 1 : 2;
+    p.tma_store = al16(D) && ((N * esz) % 16 == 0);
+    p.ksub = K <= BK ? 1 : 2;
     p.k_iters = (int)((K + p.ksub * BK - 1) / (p.ksub * BK));
-    const int bn = choose_bn(M, N, p.k_iters, clusters);
+    // The K-split forms need scratch; whether this stream has (or can get) some decides the tile width too.
+    const bool long_k = p.k_iters >= 4;
+    int* wsp = nullptr;
+    int bn = choose_bn(M, N, clusters, false);
+    {
+        const int64_t tm = (M + 2 * BM - 1) / (2 * BM);
+        const int64_t t0 = tm * ((N + bn - 1) / bn), t256 = tm * ((N + 255) / 256);
+        const bool few = t0 < clusters && 2 * (t0 % clusters) <= clusters && p.k_iters >= 16;
+        const bool ragged = long_k && t256 > clusters && (clusters - t256 % clusters) % clusters * 100 >= 15 * clusters;
+        if (few || ragged) wsp = split_workspace(dev, st, kSplitWorkspaceBytes);
+        if (wsp && ragged) bn = choose_bn(M, N, clusters, true);
+    }
     p.bn = bn;
     p.idesc = umma_idesc_i8(2 * BM, bn);
     const int stage_bytes = p.ksub * (BM * BK + (bn / 2) * BK);
@@ -836,32 +907,31 @@ int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const f
     } else {
         td = ta;  // unused
     }
-    // K split: a problem with fewer tiles than clusters and a long K (few rows, few columns) is cut along K so that
-    // more SMs stream it. Measured on B200: worth it only when every slice keeps at least eight stages; splitting the
-    // nearly empty last round of a many-round problem costs as much as that round (fences and atomics) and is not done.
     p.whole_tiles = p.num_tiles, p.splits = 0, p.kps = p.k_iters, p.num_items = p.num_tiles;
-    p.scratch = nullptr, p.partials = nullptr;
-    static const int split_mode = env_int("GPU_KERNELS_SPLIT", 1);   // 0 never, 1 few-tile problems, 2 also the last round
+    p.dp_tiles = 0, p.sk_units = 0;
+    p.scratch = wsp;
+    p.partials = wsp ? reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(wsp) + kWorkspaceCounterBytes) : nullptr;
     const int rem = p.num_tiles % clusters;
-    const bool few_tiles = p.num_tiles < clusters;
-    if (split_mode && rem > 0 && 2 * rem <= clusters && p.k_iters >= 2 && (few_tiles || split_mode == 2)) {
+    if (wsp && rem > 0 && p.num_tiles > clusters && long_k && clusters <= kWorkspaceSlots &&
+        (clusters - rem) * 100 >= 15 * clusters) {
+        // Streamed tail: the whole rounds but the last run tile by tile; the remaining one to two rounds' worth of tiles is
+        // dealt out in K stages, an equal run per cluster, so the ragged round costs its share of a round instead of a
+        // whole one (816 tiles on 74 clusters: 11.03 rounds instead of 12).
+        p.dp_tiles = (p.num_tiles / clusters - 1) * clusters;
+        p.sk_units = (p.num_tiles - p.dp_tiles) * p.k_iters;
+    } else if (wsp && rem > 0 && p.num_tiles < clusters && 2 * rem <= clusters && p.k_iters >= 16) {
+        // K split: a problem with fewer tiles than clusters and a long K (few rows, few columns) is cut along K so that
+        // more SMs stream it; partial sums meet by atomic adds and the slice that arrives last runs the epilogue.
+        // Measured on B200: worth it only when every slice keeps at least eight stages.
         int splits = clusters / rem;
-        const int max_by_k = split_mode == 2 ? p.k_iters : p.k_iters / 8;
-        if (splits > max_by_k) splits = max_by_k;
+        if (splits > p.k_iters / 8) splits = p.k_iters / 8;
         if (splits > 16) splits = 16;
         if (splits < 1) splits = 1;
         const int kps = (p.k_iters + splits - 1) / splits;
         splits = (p.k_iters + kps - 1) / kps;
-        if (splits >= 2) {
-            const size_t counter_bytes = 1 << 16;   // fixed counter region, zeroed once; partials always start behind it
-            const size_t partial_bytes = (size_t)rem * kCountersPerSlot * 32 * 32 * sizeof(int);
-            int* ws = split_workspace(dev, st, counter_bytes + partial_bytes);
-            if (ws) {
-                p.scratch = ws;
-                p.partials = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(ws) + counter_bytes);
-                p.whole_tiles = p.num_tiles - rem, p.splits = splits, p.kps = kps;
-                p.num_items = p.whole_tiles + rem * splits;
-            }
+        if (splits >= 2 && rem <= kWorkspaceSlots) {
+            p.whole_tiles = p.num_tiles - rem, p.splits = splits, p.kps = kps;
+            p.num_items = p.whole_tiles + rem * splits;
         }
     }
     const int grid = 2 * (p.num_items < clusters ? p.num_items : clusters);
@@ -984,17 +1054,20 @@ GPU_API int gpu_int8_gemm_noalloc(const int8_t* A, const int8_t* W, const float*
     p.tma_store = al16(D) && ((N * esz) % 16 == 0);
     p.ksub = K <= BK ? 1 : 2;
     p.k_iters = (int)((K + p.ksub * BK - 1) / (p.ksub * BK));
-    const int bn = choose_bn(M, N, p.k_iters, clusters);
+    // the width that fills the clusters best, widened while the tiles outnumber the array's 16 slots
+    int bn = choose_bn(M, N, clusters, false);
+    p.tiles_m = (int)((M + 2 * BM - 1) / (2 * BM));
+    while (bn < 256 && p.tiles_m * ((N + bn - 1) / bn) > kStaticMaxTiles) bn += 32;
     p.bn = bn;
     p.idesc = umma_idesc_i8(2 * BM, bn);
     const int stage_bytes = p.ksub * (BM * BK + (bn / 2) * BK);
     const int stages = (kSmemBytes - 1024 - kTailBytes - kStagingBytes) / stage_bytes;
     p.stages = stages > kMaxStages ? kMaxStages : stages;
-    p.tiles_m = (int)((M + 2 * BM - 1) / (2 * BM));
     p.tiles_n = (int)((N + bn - 1) / bn);
     p.num_tiles = p.tiles_m * p.tiles_n;
     if (p.num_tiles > kStaticMaxTiles) return -205;
     int splits = clusters / p.num_tiles;
+    if (splits < 1) splits = 1;
     if (splits > p.k_iters) splits = p.k_iters;
     if (splits > 16) splits = 16;
     const int kps = (p.k_iters + splits - 1) / splits;
@@ -1023,17 +1096,6 @@ GPU_API int gpu_int8_gemm_noalloc(const int8_t* A, const int8_t* W, const float*
     return launch_pair<bf16, EPI_PLAIN>(ta, tw, td, p, grid, st);
 }
 
-#ifdef GEMM_PROFILE
-GPU_API int gpu_kernels_prof(unsigned long long* out, int clear) {
-    cudaError_t e = cudaMemcpyFromSymbol(out, g_prof, sizeof(g_prof));
-    if (e != cudaSuccess) return (int)e;
-    if (clear) {
-        static unsigned long long z[160][8];
-        cudaMemcpyToSymbol(g_prof, z, sizeof(z));
-    }
-    return 0;
-}
-#endif
 
 // Reads and clears the device status word (synchronises the device). 0 = no kernel gave up a wait.
 GPU_API int gpu_kernels_status(int* status) {
@@ -1043,6 +1105,9 @@ GPU_API int gpu_kernels_status(int* status) {
     const int zero = 0;
     e = cudaMemcpyToSymbol(g_kernel_status, &zero, sizeof(int));
     if (e != cudaSuccess) return (int)e;
-    if (status) *status = v;
+    int qv = 0;
+    if (int rc = quant_status_read_clear(&qv)) return rc;
+    if (v) g_workspace_epoch.fetch_add(1, std::memory_order_acq_rel);   // scratch may hold partial sums: clear before reuse
+    if (status) *status = v ? v : qv;
     return 0;
 }

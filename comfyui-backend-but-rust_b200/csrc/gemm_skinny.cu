@@ -152,11 +152,117 @@ GPU_API int gpu_int8_epilogue(const int32_t* acc, const float* xs, const float* 
     return -200;
 }
 
-bool skinny_gemm_applies(int64_t M, int64_t N, int64_t K) {
+// ---- K not a multiple of 16 ----------------------------------------------------------------------------------
+// The tensor-core kernel stages its operands with TMA, which needs a 16-byte row pitch. The reference serves rows whose
+// K is only a multiple of 8 with narrower-aligned tile configurations (csrc/vendor/cutlass_gemm_int8.cu:190-191,
+// 265-267); such shapes (and 16-byte-misaligned operands) take this plain CUDA-core kernel here: 64 x 64 outputs per CTA,
+// 64 bytes of K per step through shared memory, dp4a into int32 (exact), the same epilogue arithmetic. Rare shapes:
+// built to be right, not fast.
+namespace {
+
+constexpr int kGT = 64;        // tile edge
+constexpr int kGK = 64;        // bytes of K per step
+constexpr int kGPitch = 17;    // words per staged row (16 + 1: conflict-free column reads)
+
+template <typename OutT, int EPI>
+__global__ void __launch_bounds__(256) generic_gemm_kernel(const SkinnyParams p, int vec) {
+    __shared__ uint32_t a_s[kGT][kGPitch], w_s[kGT][kGPitch];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;       // 16 x 16 threads, 4 x 4 outputs each
+    const int m0 = blockIdx.y * kGT, n0 = blockIdx.x * kGT;
+    int acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0;
+    for (int k0 = 0; k0 < p.K; k0 += kGK) {
+        // stage [64 rows][64 bytes] of A and of W, zero beyond M, N and K; `vec` bytes per load (8, 4 or 1)
+        for (int idx = threadIdx.x; idx < 2 * kGT * (kGK / 8); idx += 256) {
+            const bool is_w = idx >= kGT * (kGK / 8);
+            const int j = is_w ? idx - kGT * (kGK / 8) : idx;
+            const int r = j >> 3, c8 = j & 7;
+            const int row = (is_w ? n0 : m0) + r, k = k0 + 8 * c8;
+            const int8_t* src = (is_w ? p.W : p.A) + (int64_t)row * p.K + k;
+            uint32_t lo = 0, hi = 0;
+            if (row < (is_w ? p.N : p.M) && k < p.K) {
+                if (vec == 8 && k + 8 <= p.K) {
+                    const uint2 u = *reinterpret_cast<const uint2*>(src);
+                    lo = u.x, hi = u.y;
+                } else if (vec >= 4 && k + 8 <= p.K) {
+                    lo = reinterpret_cast<const uint32_t*>(src)[0], hi = reinterpret_cast<const uint32_t*>(src)[1];
+                } else {
+                    for (int b = 0; b < 8 && k + b < p.K; ++b) {
+                        const uint32_t v = (uint8_t)src[b];
+                        if (b < 4) lo |= v << (8 * b); else hi |= v << (8 * (b - 4));
+                    }
+                }
+            }
+            uint32_t(*dst)[kGPitch] = is_w ? w_s : a_s;
+            dst[r][2 * c8] = lo, dst[r][2 * c8 + 1] = hi;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < kGK / 4; ++kk) {
+            int a[4], w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = (int)a_s[ty + 16 * i][kk], w[i] = (int)w_s[tx + 16 * i][kk];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = __dp4a(a[i], w[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int m = m0 + ty + 16 * i, n = n0 + tx + 16 * j;
+            if (m >= p.M || n >= p.N) continue;
+            const int64_t o = (int64_t)m * p.N + n;
+            if (EPI == EPI_ACC) reinterpret_cast<int32_t*>(p.D)[o] = acc[i][j];
+            else {
+                const float bias = p.bias ? to_f<OutT>(reinterpret_cast<const OutT*>(p.bias)[n]) : 0.f;
+                const float rs = EPI == EPI_RESID ? to_f<OutT>(reinterpret_cast<const OutT*>(p.rscale)[n]) : 0.f;
+                const float rr = EPI == EPI_RESID ? to_f<OutT>(reinterpret_cast<const OutT*>(p.resid)[o]) : 0.f;
+                reinterpret_cast<OutT*>(p.D)[o] = from_f<OutT>(epilogue1<OutT, EPI>(acc[i][j], p.xs[m], p.ws[n], bias, rs, rr, p.act));
+            }
+        }
+}
+
+template <typename OutT>
+int launch_generic_epi(int epi, const SkinnyParams& p, dim3 grid, int vec, cudaStream_t st) {
+    switch (epi) {
+        case EPI_PLAIN: generic_gemm_kernel<OutT, EPI_PLAIN><<<grid, 256, 0, st>>>(p, vec); break;
+        case EPI_RESID: generic_gemm_kernel<OutT, EPI_RESID><<<grid, 256, 0, st>>>(p, vec); break;
+        case EPI_ACT: generic_gemm_kernel<OutT, EPI_ACT><<<grid, 256, 0, st>>>(p, vec); break;
+        default: return -200;
+    }
+    KCHECK();
+    return 0;
+}
+
+}  // namespace
+
+int b200q::launch_generic_gemm(int epi, const SkinnyParams& p, int out_dt, cudaStream_t st) {
+    const dim3 grid((unsigned)((p.N + kGT - 1) / kGT), (unsigned)((p.M + kGT - 1) / kGT));
+    if (grid.y > 65535u) return -200;
+    const uintptr_t al = (uintptr_t)p.A | (uintptr_t)p.W | (uintptr_t)p.K;
+    const int vec = (al & 7) == 0 ? 8 : (al & 3) == 0 ? 4 : 1;
+    if (epi == EPI_ACC) {
+        generic_gemm_kernel<float, EPI_ACC><<<grid, 256, 0, st>>>(p, vec);
+        KCHECK();
+        return 0;
+    }
+    if (out_dt == DT_F32) return launch_generic_epi<float>(epi, p, grid, vec, st);
+    if (out_dt == DT_F16) return launch_generic_epi<half>(epi, p, grid, vec, st);
+    return launch_generic_epi<bf16>(epi, p, grid, vec, st);
+}
+
+bool b200q::skinny_gemm_applies(int64_t M, int64_t N, int64_t K) {
     return M >= 1 && M <= 8 && K % 16 == 0 && M * K <= 160 * 1024 && N >= 1;
 }
 
-int launch_skinny_gemm(int epi, const SkinnyParams& p, int out_dt, int sms, cudaStream_t st) {
+int b200q::launch_skinny_gemm(int epi, const SkinnyParams& p, int out_dt, int sms, cudaStream_t st) {
     const size_t smem = (size_t)p.M * p.K;
     const int nblocks = (p.N + kRowsPerWarp - 1) / kRowsPerWarp;
     int grid = (nblocks + kWarps - 1) / kWarps;

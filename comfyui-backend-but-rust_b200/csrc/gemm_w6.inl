@@ -14,13 +14,6 @@
 // The arithmetic is exact in half precision: code - 32 has 6 bits, e4m3 has 4, the product at most 10; rint is one
 // addition of 1536 (ulp 1), ties to even, after the clamp.
 
-#ifdef GEMM_PROFILE
-#define W6P_BEGIN() long long w6p_t__ = clock64()
-#define W6P_LAP(slot, cond) do { const long long n__ = clock64(); if (cond) g_prof[blockIdx.x][slot] += (unsigned long long)(n__ - w6p_t__); w6p_t__ = n__; } while (0)
-#else
-#define W6P_BEGIN()
-#define W6P_LAP(slot, cond)
-#endif
 constexpr int kW6EpiWarps = 4;
 constexpr int kW6Groups = 3;                     // unpack groups of four warps, taking K boxes in turn
 constexpr int kW6UnpackWarps = 4 * kW6Groups;
@@ -88,9 +81,6 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
     const int nclusters = gridDim.x >> 1, cluster_id = blockIdx.x >> 1;
-#ifdef GEMM_PROFILE
-    const long long w6_start__ = clock64();
-#endif
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < SA; ++i) {
@@ -160,18 +150,13 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             bool ok = true;
             for (int t = cluster_id; t < p.num_tiles && ok; t += nclusters) {
                 {
-                    W6P_BEGIN();
                     if (!mbar_wait(bar_tempty + 8 * buf, tphase ^ 1u, abort_s, ST_TIMEOUT_TMEM_EMPTY)) break;
-                    W6P_LAP(7, true);
                 }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * 256;
                 for (int kb = 0; kb < p.k_iters; ++kb) {
-                    W6P_BEGIN();
                     if (!mbar_wait(bar_afull + 8 * sa, pa, abort_s, ST_TIMEOUT_FULL)) { ok = false; break; }
-                    W6P_LAP(0, true);
                     if (!mbar_wait(bar_bfull + 8 * sb, pb, abort_s, ST_TIMEOUT_FULL)) { ok = false; break; }
-                    W6P_LAP(1, true);
                     tc_fence_after();
 #pragma unroll
                     for (int h = 0; h < MH; ++h) {
@@ -183,7 +168,6 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                     }
                     umma_commit_pair(bar_bempty + 8 * sb);
                     umma_commit_pair(bar_aempty + 8 * sa);
-                    W6P_LAP(2, true);
                     ++sa, a_lo += a_step;
                     if (sa == SA) sa = 0, pa ^= 1u, a_lo = a_lo0;
                     ++sb, b_lo += b_step;
@@ -240,11 +224,9 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 if (turn == grp) {
                     const int q = kb & 3;
                     const uint32_t sr = q == 0 ? sc_cur.x : q == 1 ? sc_cur.y : q == 2 ? sc_cur.z : sc_cur.w;
-                    W6P_BEGIN();
                     // usually both are complete already: one probe by every lane, the polling form only when not
                     if (!__all_sync(0xffffffffu, mbar_try_wait(bar_pfull + 8 * sa, pa)) &&
                         !mbar_wait_warp(bar_pfull + 8 * sa, pa, abort_s, ST_TIMEOUT_UNPACK)) { ok = false; break; }
-                    W6P_LAP(3, uw == 0 && lane == 0);
                     if (!__all_sync(0xffffffffu, mbar_try_wait(bar_bempty + 8 * sb, pb ^ 1u)) &&
                         !mbar_wait_warp(bar_bempty + 8 * sb, pb ^ 1u, abort_s, ST_TIMEOUT_UNPACK)) { ok = false; break; }
                     {
@@ -268,7 +250,6 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                             }
                         }
                     }
-                    W6P_LAP(6, uw == 0 && lane == 0);
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_remote(bfull_leader + 8 * sb);
@@ -311,7 +292,6 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 __syncwarp();
             }
             if (!mbar_wait_warp_relaxed(bar_tfull + 8 * buf, tphase, abort_s, ST_TIMEOUT_TMEM_FULL)) break;
-            W6P_BEGIN();
             tc_fence_after();
             uint32_t ra[32];
 #pragma unroll 1
@@ -352,7 +332,6 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa_shared(bar_tempty + 8 * buf, 0));
-            W6P_LAP(5, threadIdx.x == 64);
             buf ^= 1;
             if (buf == 0) tphase ^= 1u;
         }
@@ -363,9 +342,6 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     tc_fence_before();
     __syncthreads();
     cluster_sync_all();
-#ifdef GEMM_PROFILE
-    if (threadIdx.x == 0) g_prof[blockIdx.x][4] += (unsigned long long)(clock64() - w6_start__);
-#endif
     if (*abort_s != 0) {
         for (int i = 0; i < 2000; ++i) __nanosleep(1000);
         if (threadIdx.x == 0) atomicCAS(&g_kernel_status, 0, *abort_s);
@@ -436,15 +412,13 @@ int run_w6_gemm(int epi, const int8_t* A, const uint8_t* Wq6, const uint8_t* s_r
     const int esz = epi == EPI_ACC ? 4 : (out_dt == DT_F32 ? 4 : 2);
     auto al16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
     p.vec_ok = (N % 8 == 0) && al16(D) && al16(ws) && al16(bias) && al16(rscale) && al16(resid);
-    static const int no_tma_store = env_int("GPU_KERNELS_DIRECT_STORE", 0);
-    p.tma_store = !no_tma_store && al16(D) && ((N * esz) % 16 == 0);
+    p.tma_store = al16(D) && ((N * esz) % 16 == 0);
     p.ksub = 1;
     p.k_iters = (int)(K / BK);
     // More than 256 rows: tiles of 512 rows x 128 columns, so that each expanded W tile serves two sets of MMAs and the
     // unpack work per MMA halves; otherwise one 256-row half and the column width that fills the clusters best.
-    static const int mh_env = env_int("GPU_KERNELS_W6_MH", 0);
-    const int mh = mh_env ? (mh_env == 2 ? 2 : 1) : (M > 256 && N >= 128 ? 2 : 1);
-    const int bn = mh == 2 ? 128 : choose_bn(M, N, p.k_iters, clusters);
+    const int mh = M > 256 && N >= 128 ? 2 : 1;
+    const int bn = mh == 2 ? 128 : choose_bn(M, N, clusters, false);
     p.bn = bn;
     p.idesc = umma_idesc_i8(2 * BM, bn);
     const int stage_bytes = mh * BM * BK + (bn / 2) * (64 + 32);     // A boxes + packed planes; the expanded ring is separate

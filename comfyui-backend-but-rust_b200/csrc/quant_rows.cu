@@ -7,23 +7,30 @@
 //   scale = max(min(amax, finite_max) * (1/127), 1e-30)      stored fp32
 //   q = clamp(rint(T(T(v) / T(scale))), -128, 127)            T = activation dtype (csrc/kernels.cu:241-255)
 //
-// The kernel is bound by instruction issue, not by HBM, so it is organised around instruction count:
-//   - a 256-wide group belongs to 8 consecutive lanes; a lane loads 32 consecutive elements (16-byte loads)
+// The kernel is bound by instruction issue before HBM, so it is organised around instruction count and around keeping
+// the issue slots busy:
+//   - persistent CTAs: a CTA walks row blocks; while it computes one block, one bulk asynchronous copy per row
+//     (cp.async.bulk, completion on an mbarrier) brings the next block's rows into shared memory, so no warp ever
+//     waits for HBM with nothing else to issue (rows too long for the staging buffer are loaded directly instead)
+//   - a 256-wide group belongs to 8 consecutive lanes; a lane takes 32 consecutive elements (16-byte loads)
 //   - stages 0 and 1 (index bits 0-3) run in registers on packed f32x2 pairs (element i with element i+16)
 //   - the group is transposed through a padded per-warp shared-memory buffer; a lane then holds element pairs
 //     (2t, 2t+1) + 16 r, r = 0..15, and runs stages 2 and 3 (index bits 4-7) in registers, again on packed pairs
 //   - every butterfly adds in the reference's left-to-right order (a - b is fma(b, -1, a): one rounding, the same),
 //     so results are bit-identical whichever thread computes them
 //   - bf16 prologues of one variable (SiLU, GELU, GELU-tanh, the sigmoid of GATE) are a 65536-entry table built on
-//     the device from the very expressions of the reference and read through L1 (staging it in shared memory left
-//     room for too few warps and measured slower)
-//   - quantization rounds with cvt.rni and packs with saturation; the codes go back through shared memory so that
-//     each lane stores 32 contiguous bytes
+//     the device from the very expressions of the reference; the kernel keeps the entries of 2^-14 <= |x| < 128 in
+//     shared memory (10.5 KB: a gather from the whole table through L1 cost one wavefront per distinct line, which
+//     bounded the kernel) and a thread that meets a value outside that range redoes its elements from the whole table
+//   - the division by the scale is a multiplication by its reciprocal (exact for this purpose, see quant2), the
+//     codes are rounded by cvt.rni straight from bf16 and packed with saturation, and go back through shared memory
+//     so that each lane stores 32 contiguous bytes
 #include <atomic>
 #include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
+#include "epilogue.cuh"
 
 namespace {
 
@@ -55,7 +62,7 @@ struct QuantArgs {
     int64_t x_stride;   // elements between rows
     const void* g;      // PRO_GATE: gate logits
     int64_t g_stride;
-    int64_t up_offset;  // PRO_SWIGLU: column of `up` inside the x row
+    int64_t up_offset;  // PRO_SWIGLU, PRO_SITU*: column of the second half inside the x row
     int8_t* q;          // [M, K]
     float* scales;      // [M]
     float* out_f;       // when set: write the rotated fp32 rows here instead of quantizing
@@ -64,7 +71,7 @@ struct QuantArgs {
     int tpr;            // threads per row = K / 32
     int rows_per_cta;
     int nblocks;        // row blocks; CTAs stride over them
-    int lut;            // table index of the prologue (read through L1), or -1
+    int lut;            // table index of the prologue, or -1
     const float* amax_in;   // when set: row maxima to quantize with (rows whose columns are split across devices)
     float* amax_out;        // when set: write each row's maximum here and stop (first pass of the same)
     // normalising prologues
@@ -73,15 +80,36 @@ struct QuantArgs {
     float eps;
     const void* mod_scale;  // [K] in the activation dtype (nullable except ADALN)
     const void* mod_shift;
+    // shared-memory plan (byte offsets from the dynamic shared memory base), filled in by launch_quant
+    int staged;             // rows arrive through the staging buffer (bulk copies) instead of direct loads
+    uint32_t off_amax, off_norm, off_lut, off_stage, off_bar;
 };
 
 template <int PRO> __host__ __device__ constexpr bool is_ln() { return PRO == PRO_LAYERNORM || PRO == PRO_LN_MOD || PRO == PRO_LN_AFFINE; }
 template <int PRO> __host__ __device__ constexpr bool is_norm() { return PRO == PRO_RMS || PRO == PRO_ADALN || is_ln<PRO>(); }
+// prologues that read a second stream per row: the gate logits (GATE) or the other half of the row (SWIGLU, SITU)
+template <int PRO> __host__ __device__ constexpr bool has_aux() {
+    return PRO == PRO_GATE || PRO == PRO_SWIGLU || PRO == PRO_SITU || PRO == PRO_SITU_FAST;
+}
 // floats of shared memory a row needs for the sums of a normalising prologue: one partial per thread of the
 // reference's block (ceil(K / 1024) warps), 32 warp sums, the total
 __host__ __device__ inline int norm_words(int K) { return (((K >> 8) + 3) >> 2) * 32 + 33; }
 
-constexpr int kGroupWords = 304;   // 256 elements + 4 words of padding per 32, rounded so that groups sit 16 banks apart
+// Transposition buffers: per 8-lane team 256 elements + 4 words of padding per 32 (288 words), laid out so that every
+// shared-memory access of the transposition is free of bank conflicts across the four teams of a warp:
+//   - a lane writes element 32 t8 + i as one 32-bit store per i; over a team's lanes these hit banks 4 t8 + i, i.e. one
+//     residue class modulo 4. The four teams must cover the four classes: teams 1 and 3 store each element pair swapped
+//     (column i ^ 1), teams 2 and 3 start two words later
+//   - a lane reads element pairs (2 t8, 2 t8 + 1) + 16 r as 64-bit loads, 16 consecutive banks per team; a half-warp holds
+//     two teams, which start 16 banks apart
+// Teams 1 and 3 therefore hold their pairs as (odd element, even element) from the transposition on; the codes are
+// swapped back when they are written out.
+constexpr int kGroupWords = 304;          // team pitch inside a warp: 16 banks (mod 32) apart
+constexpr int kWarpWords = 4 * 304 + 32;  // warp pitch: a multiple of 32 words with room for the two-word shift
+
+// The part of a 65536-entry activation table kept in shared memory: bf16 bit patterns [kLutLo, kLutLo + kLutRange)
+// (2^-14 <= x < 128) and the same magnitudes with the sign bit, negative half second.
+constexpr uint32_t kLutLo = 0x3880u, kLutRange = 21u * 128u;
 
 __device__ __forceinline__ int tpad(int e) { return e + ((e >> 5) << 2); }
 
@@ -89,30 +117,41 @@ template <typename T> __device__ __forceinline__ float finite_max();
 template <> __device__ __forceinline__ float finite_max<float>() { return FLT_MAX; }
 template <> __device__ __forceinline__ float finite_max<bf16>() { return 3.38953139e38f; }
 
-// 32 consecutive elements -> floats (and, for bf16, their raw 16-bit patterns when a table prologue wants them)
-template <typename T> __device__ __forceinline__ void load32(const T* p, float (&v)[32]);
-template <> __device__ __forceinline__ void load32<bf16>(const bf16* p, float (&v)[32]) {
+__device__ __forceinline__ void unpack_bf16x8(const uint4 u, float* v) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        const uint4 u = __ldg(reinterpret_cast<const uint4*>(p) + c);
-        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+// 32 consecutive elements -> floats, from global memory (read-only path) or from the staging buffer
+template <typename T, bool SMEM> __device__ __forceinline__ void load32(const T* p, float (&v)[32]) {
+    if constexpr (sizeof(T) == 2) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            v[8 * c + 2 * i] = __uint_as_float(w[i] << 16);
-            v[8 * c + 2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        for (int c = 0; c < 4; ++c) {
+            const uint4 u = SMEM ? reinterpret_cast<const uint4*>(p)[c] : __ldg(reinterpret_cast<const uint4*>(p) + c);
+            unpack_bf16x8(u, v + 8 * c);
+        }
+    } else {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const float4 a = SMEM ? reinterpret_cast<const float4*>(p)[c] : __ldg(reinterpret_cast<const float4*>(p) + c);
+            v[4 * c] = a.x, v[4 * c + 1] = a.y, v[4 * c + 2] = a.z, v[4 * c + 3] = a.w;
         }
     }
 }
-template <> __device__ __forceinline__ void load32<float>(const float* p, float (&v)[32]) {
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-        const float4 a = __ldg(reinterpret_cast<const float4*>(p) + c);
-        v[4 * c] = a.x, v[4 * c + 1] = a.y, v[4 * c + 2] = a.z, v[4 * c + 3] = a.w;
-    }
-}
 
-__device__ __forceinline__ float lut_f(const uint16_t* lut, float x) {   // x holds a bf16 value
-    return __uint_as_float((uint32_t)lut[__float_as_uint(x) >> 16] << 16);
+__device__ __forceinline__ float lut_f(const uint16_t* lut, float x) {   // x holds a bf16 value; whole table, global
+    return __uint_as_float((uint32_t)__ldg(lut + (__float_as_uint(x) >> 16)) << 16);
+}
+// The same from the shared-memory part; a value outside it leaves x unchanged and raises `miss`.
+__device__ __forceinline__ float lut_s(const uint16_t* lut_sm, float x, bool& miss) {
+    const uint32_t e = (__float_as_uint(x) >> 16) - kLutLo;
+    const uint32_t m = e & 0x7fffu;
+    const bool in = m < kLutRange;
+    miss |= !in;
+    return in ? __uint_as_float((uint32_t)lut_sm[m + ((e >> 15) & 1u) * kLutRange] << 16) : x;
 }
 
 // Radix-4 butterfly of the regular Hadamard block on packed pairs; outputs in the reference's association:
@@ -135,31 +174,38 @@ __device__ __forceinline__ void two_stages(float2 (&P)[16]) {
     for (int i = 0; i < 4; ++i) h4x2(P[i], P[i + 4], P[i + 8], P[i + 12]);
 }
 
-// Codes of two values: q = sat8(rint(T(T(v) / T(scale)))). bf16 fast path: both operands of the division carry 8
-// significant bits, so the exact quotient is either representable in fp32 or further than 2^-17 (relative) from every
-// bf16 rounding boundary; a reciprocal multiply with one correction step then rounds to the same bf16 as the IEEE
-// division. cvt.rni + saturating pack equal clamp(rint(.)) except for NaN (0 instead of -128): `nanacc` turns NaN
-// (and stays finite otherwise) so the caller can redo such a lane exactly.
+// max(|a|, |b|, |c|) that is NaN as soon as one input is
+__device__ __forceinline__ float max3_abs_nan(float a, float b, float c) {
+    float m;
+    asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(m) : "f"(fabsf(a)), "f"(fabsf(b)), "f"(fabsf(c)));
+    return m;
+}
+
+// Codes of two values: q = sat8(rint(T(T(v) / T(scale)))).
+// bf16 fast path. Both operands of the division carry 8 significant bits: a = A 2^i, st = S 2^j with integers
+// A, S < 256. A bf16 rounding boundary is M 2^k with M odd and 256 < M < 512; a quotient equal to one would need
+// A 2^n = S M, impossible because the odd part of the left side is below 256 and that of the right side is at least 257.
+// So the exact quotient differs from every boundary by at least 1 / (S M) > 2^-17 relative, while a (correctly rounded)
+// reciprocal times a is within 2^-23 of it: both round to the same bf16, and no correction step is needed
+// (tests/test_quant_division.py enumerates every pair of significands).
+// cvt.rni + saturating pack equal clamp(rint(.)) except for NaN (0 instead of -128) and the caller keeps rows that
+// hold a NaN or an infinity off this path.
 template <typename T>
-__device__ __forceinline__ uint32_t quant2(float2 v, float st, float rcp, bool fast, float2& nanacc) {
+__device__ __forceinline__ uint32_t quant2(float2 v, float st, float rcp, bool fast) {
     if (sizeof(T) == 2 && fast) {
         const __nv_bfloat162 ab = __floats2bfloat162_rn(v.x, v.y);
         const uint32_t au = *reinterpret_cast<const uint32_t*>(&ab);
         const float2 a = make_float2(__uint_as_float(au << 16), __uint_as_float(au & 0xffff0000u));
-        const float2 q0 = __fmul2_rn(a, make_float2(rcp, rcp));
-        const float2 r = __ffma2_rn(q0, make_float2(-st, -st), a);
-        const float2 t = __ffma2_rn(r, make_float2(rcp, rcp), q0);
+        const float2 t = __fmul2_rn(a, make_float2(rcp, rcp));
         const __nv_bfloat162 tb = __floats2bfloat162_rn(t.x, t.y);
-        const uint32_t tu = *reinterpret_cast<const uint32_t*>(&tb);
-        const float tx = __uint_as_float(tu << 16), ty = __uint_as_float(tu & 0xffff0000u);
-        nanacc = __ffma2_rn(make_float2(tx, ty), make_float2(0.f, 0.f), nanacc);
         uint32_t packed;
-        asm("{\n\t.reg .s32 a, b;\n\t"
-            "cvt.rni.s32.f32 a, %1;\n\t"
-            "cvt.rni.s32.f32 b, %2;\n\t"
+        asm("{\n\t.reg .b16 lo, hi;\n\t.reg .s32 a, b;\n\t"
+            "mov.b32 {lo, hi}, %1;\n\t"
+            "cvt.rni.s32.bf16 a, lo;\n\t"
+            "cvt.rni.s32.bf16 b, hi;\n\t"
             "cvt.pack.sat.s8.s32.b32 %0, b, a, 0;\n\t}"
             : "=r"(packed)
-            : "f"(tx), "f"(ty));
+            : "r"(*reinterpret_cast<const uint32_t*>(&tb)));
         return packed;   // byte 0 = code of v.x, byte 1 = code of v.y
     }
     const int qx = clamp_rint_i8(rnd<T>(__fdiv_rn(rnd<T>(v.x), st)), -128.f);
@@ -173,10 +219,7 @@ __device__ __forceinline__ void load8v(const float* p, float (&v)[8]) {
     v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
 }
 __device__ __forceinline__ void load8v(const bf16* p, float (&v)[8]) {
-    const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
-    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) v[2 * i] = __uint_as_float(w[i] << 16), v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(p)), v);
 }
 
 // The reference's soft-capped gated activation (csrc/common.cuh:73-91), operation for operation.
@@ -198,55 +241,133 @@ __device__ __forceinline__ float situ_fast_f(float hidden, float gate) {
                      __fmul_rn(25.f, tanh_approx_f(__fmul_rn(hidden, 0.04f))));
 }
 
-template <typename T, int PRO, int MAXT>
-__global__ void __launch_bounds__(MAXT) quant_rows_kernel(const QuantArgs p) {
-    extern __shared__ __align__(16) uint8_t smem[];
-    const uint16_t* lut = g_act_lut[p.lut >= 0 ? p.lut : 0];
-    uint8_t* after_lut = smem;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-    float* tbuf = reinterpret_cast<float*>(after_lut) + (warp * 4 + (lane >> 3)) * kGroupWords;   // this group's buffer
-    unsigned* amax_s = reinterpret_cast<unsigned*>(after_lut + (size_t)nwarps * 4 * kGroupWords * 4);   // [3][rows]
+// One bulk asynchronous copy, global -> this CTA's shared memory, completion credited to an mbarrier. Both addresses
+// 16-byte aligned, size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
 
-    float* norm_s = reinterpret_cast<float*>(amax_s + 3 * p.rows_per_cta);   // [rows][norm_words(K)], normalising prologues only
+__device__ int g_quant_status = 0;   // a staging wait that ran out records ST_TIMEOUT_FULL here
+
+// MAXT = 384 asks for two CTAs per SM (at most 80 registers: 768 threads with the next block's rows in flight);
+// longer rows take one larger CTA.
+template <typename T, int PRO, int MAXT>
+__global__ void __launch_bounds__(MAXT, MAXT <= 384 ? 2 : 1) quant_rows_kernel(const QuantArgs p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint16_t* lut = g_act_lut[p.lut >= 0 ? p.lut : 0];
+    const unsigned wmask = __activemask();            // the last warp of a CTA may be partial (threads = rows * K / 32)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;   // nwarps: whole warps
+    const int team = lane >> 3, tsw = team & 1;        // team of the warp; teams 1 and 3 keep their pairs swapped
+    float* tbuf = reinterpret_cast<float*>(smem) + warp * kWarpWords + team * kGroupWords + 4 * (team >> 1);   // this team's buffer
+    float* tbuf_w = tbuf - 2 * (team >> 1);            // where its transposition writes and reads start (two words later for teams 2, 3)
+    unsigned* amax_s = reinterpret_cast<unsigned*>(smem + p.off_amax);   // [3][rows]
+    float* norm_s = reinterpret_cast<float*>(smem + p.off_norm);         // [rows][norm_words(K)], normalising prologues only
+    const uint16_t* lut_sm = reinterpret_cast<const uint16_t*>(smem + p.off_lut);
+    const bool use_lut = sizeof(T) == 2 && p.lut >= 0;
+    const uint32_t bar = smem_u32(smem + p.off_bar);
+    uint8_t* stage = smem + p.off_stage;              // [x rows | aux rows], one block of rows
+    const uint32_t row_bytes = (uint32_t)p.K * sizeof(T);
 
     for (int i = threadIdx.x; i < 3 * p.rows_per_cta; i += blockDim.x) amax_s[i] = 0u;
+    if (use_lut) {
+        // the shared-memory part of the table: positive half, then negative half
+        uint16_t* dst = reinterpret_cast<uint16_t*>(smem + p.off_lut);
+        for (uint32_t i = threadIdx.x; i < 2 * kLutRange; i += blockDim.x)
+            dst[i] = lut[(i < kLutRange ? kLutLo + i : 0x8000u + kLutLo + (i - kLutRange))];
+    }
+    if (p.staged && threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        fence_mbar_init();
+    }
     __syncthreads();
+
+    // Staging: the rows of block `blk` (and their second stream) -> the staging buffer, one bulk copy each, issued by
+    // the first warp; the barrier's phase completes when all their bytes have landed.
+    auto issue_block = [&](int blk) {
+        if (warp != 0) return;
+        const int64_t m0 = (int64_t)blk * p.rows_per_cta;
+        const int live = (int)min((int64_t)p.rows_per_cta, (int64_t)p.M - m0);
+        if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)live * row_bytes * (has_aux<PRO>() ? 2u : 1u));
+        __syncwarp();
+        for (int r = lane; r < live; r += 32) {
+            const T* src = reinterpret_cast<const T*>(p.x) + (m0 + r) * p.x_stride;
+            bulk_load(smem_u32(stage + (size_t)r * row_bytes), src, row_bytes, bar);
+            if (has_aux<PRO>()) {
+                const T* aux = PRO == PRO_GATE ? reinterpret_cast<const T*>(p.g) + (m0 + r) * p.g_stride : src + p.up_offset;
+                bulk_load(smem_u32(stage + (size_t)(p.rows_per_cta + r) * row_bytes), aux, row_bytes, bar);
+            }
+        }
+    };
+    if (p.staged && (int)blockIdx.x < p.nblocks) issue_block(blockIdx.x);
 
     const int tpr = p.tpr;
     const int rloc = threadIdx.x / tpr;               // row inside the CTA
     const int tin = threadIdx.x - rloc * tpr;         // thread inside the row
     const int grp = tin >> 3, t8 = tin & 7;
+    const int col = (grp << 8) + (t8 << 5);
     int it = 0;
     for (int blk = blockIdx.x; blk < p.nblocks; blk += gridDim.x, ++it) {
         const int64_t m_raw = (int64_t)blk * p.rows_per_cta + rloc;
         const bool live = m_raw < p.M;
-        const int64_t m = live ? m_raw : p.M - 1;      // idle rows recompute the last row and store nothing
-        const int col = (grp << 8) + (t8 << 5);
-        const T* x = reinterpret_cast<const T*>(p.x) + m * p.x_stride + col;
+        const int64_t m = live ? m_raw : p.M - 1;      // idle rows compute on the last row (or on stale staging) and store nothing
 
-        float v[32];
-        load32<T>(x, v);
-        if (PRO == PRO_GATE) {
-            float gg[32];
-            load32<T>(reinterpret_cast<const T*>(p.g) + m * p.g_stride + col, gg);
+        float v[32], u[32];
+        if (p.staged) {
+            // bounded wait for this block's bytes; on expiry the CTA records the fact and leaves
+            bool ok = mbar_try_wait(bar, it & 1);
+            if (!ok) {
+                const uint64_t t0 = globaltimer_ns();
+                for (uint32_t n = 1; !(ok = mbar_try_wait(bar, it & 1)); ++n)
+                    if ((n & 255u) == 0u && globaltimer_ns() - t0 > kWaitLimitNs) break;
+            }
+            if (!ok) {
+                atomicCAS(&g_quant_status, 0, ST_TIMEOUT_FULL);
+                return;
+            }
+            const T* xs = reinterpret_cast<const T*>(stage + (size_t)rloc * row_bytes) + col;
+            load32<T, true>(xs, v);
+            if (has_aux<PRO>()) load32<T, true>(reinterpret_cast<const T*>(stage + (size_t)(p.rows_per_cta + rloc) * row_bytes) + col, u);
+            // every thread holds its elements, so the buffer can take the next block; the copy engine writes through the
+            // asynchronous proxy, hence the proxy fence between these reads and the barrier that releases the buffer
+            fence_proxy_async_smem();
+            __syncthreads();
+            if (blk + (int)gridDim.x < p.nblocks) issue_block(blk + gridDim.x);
+        } else {
+            const T* x = reinterpret_cast<const T*>(p.x) + m * p.x_stride + col;
+            load32<T, false>(x, v);
+            if (PRO == PRO_GATE) load32<T, false>(reinterpret_cast<const T*>(p.g) + m * p.g_stride + col, u);
+            else if (has_aux<PRO>()) load32<T, false>(x + p.up_offset, u);
+        }
+
+        if (PRO == PRO_GATE || PRO == PRO_SWIGLU || PRO == PRO_SILU || PRO == PRO_GELU || PRO == PRO_GELU_TANH) {
+            // v = T(act(a)) [* b]: a is the gate logit (GATE), the row itself otherwise
+            float* a = PRO == PRO_GATE ? u : v;
+            if (use_lut) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-                v[i] = rnd<T>(v[i] * ((sizeof(T) == 2 && p.lut >= 0) ? lut_f(lut, gg[i]) : rnd<T>(sigmoid_f(gg[i]))));
-        } else if (PRO == PRO_SWIGLU) {
-            float u[32];
-            load32<T>(x + p.up_offset, u);
+                for (int c = 0; c < 4; ++c) {
+                    float keep[8];
+                    bool miss = false;
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-                v[i] = rnd<T>(((sizeof(T) == 2 && p.lut >= 0) ? lut_f(lut, v[i]) : rnd<T>(silu_f(v[i]))) * u[i]);
-        } else if (PRO == PRO_SILU || PRO == PRO_GELU || PRO == PRO_GELU_TANH) {
+                    for (int j = 0; j < 8; ++j) keep[j] = a[8 * c + j], a[8 * c + j] = lut_s(lut_sm, keep[j], miss);
+                    if (miss) {                        // a value outside the shared-memory part: the whole table serves these eight
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                if (sizeof(T) == 2 && p.lut >= 0) v[i] = lut_f(lut, v[i]);
-                else v[i] = rnd<T>(PRO == PRO_SILU ? silu_f(v[i]) : PRO == PRO_GELU ? gelu_f(v[i]) : gelu_tanh_f(v[i]));
+                        for (int j = 0; j < 8; ++j) a[8 * c + j] = lut_f(lut, keep[j]);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    a[i] = rnd<T>(PRO == PRO_GATE ? sigmoid_f(a[i]) : (PRO == PRO_SILU || PRO == PRO_SWIGLU) ? silu_f(a[i])
+                                  : PRO == PRO_GELU ? gelu_f(a[i]) : gelu_tanh_f(a[i]));
+            }
+            if (PRO == PRO_GATE || PRO == PRO_SWIGLU) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = rnd<T>(__fmul_rn(v[i], u[i]));
             }
         } else if (PRO == PRO_SITU || PRO == PRO_SITU_FAST) {
-            float u[32];   // the gate half of the row; the product is not rounded here (csrc/kernels.cu:107-112)
-            load32<T>(x + p.up_offset, u);
+            // u = the gate half of the row; the product is not rounded here (csrc/kernels.cu:107-112)
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = PRO == PRO_SITU ? situ_f(v[i], u[i]) : situ_fast_f(v[i], u[i]);
         }
@@ -279,7 +400,8 @@ __global__ void __launch_bounds__(MAXT) quant_rows_kernel(const QuantArgs p) {
                     }
                     __syncthreads();
                 }
-                for (int pi = warp; pi < p.rows_per_cta * nwr; pi += nwarps) {
+                // the two shuffle trees run in whole warps only
+                for (int pi = warp; pi < p.rows_per_cta * nwr && warp < nwarps; pi += nwarps) {
                     const int row = pi / nwr, ww = pi - row * nwr;
                     float* pr = norm_s + row * words;
                     float t = pr[ww * 32 + lane];
@@ -288,7 +410,7 @@ __global__ void __launch_bounds__(MAXT) quant_rows_kernel(const QuantArgs p) {
                     if (lane == 0) pr[nwr * 32 + ww] = t;
                 }
                 __syncthreads();
-                for (int row = warp; row < p.rows_per_cta; row += nwarps) {
+                for (int row = warp; row < p.rows_per_cta && warp < nwarps; row += nwarps) {
                     float* pr = norm_s + row * words;
                     float t = lane < nwr ? pr[nwr * 32 + lane] : 0.f;
 #pragma unroll
@@ -347,17 +469,19 @@ __global__ void __launch_bounds__(MAXT) quant_rows_kernel(const QuantArgs p) {
             for (int i = 0; i < 16; ++i) P[i] = make_float2(v[i], v[i + 16]);
             two_stages(P);
             // transpose inside the group: lane t8 wrote elements 32 t8 + i, now takes (2 t8, 2 t8 + 1) + 16 r
-            const int wbase = tpad(t8 << 5);
+            float* we = tbuf_w + tpad(t8 << 5) + tsw;     // even columns go one word up in a swapping team,
+            float* wo = tbuf_w + tpad(t8 << 5) - tsw;     // odd columns one word down: column i ^ 1
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-                tbuf[wbase + i] = P[i].x;
-                tbuf[wbase + 16 + i] = P[i].y;   // element 32 t8 + 16 + i: same 32-run, no pad in between
+                float* w = (i & 1) ? wo : we;
+                w[i] = P[i].x;
+                w[16 + i] = P[i].y;   // element 32 t8 + 16 + i: same 32-run, no pad in between
             }
-            __syncwarp();
+            __syncwarp(wmask);
 #pragma unroll
-            for (int r = 0; r < 16; ++r) P[r] = *reinterpret_cast<const float2*>(tbuf + tpad(2 * t8 + 16 * r));
-            two_stages(P);   // index bits 4-7 = r
-            __syncwarp();
+            for (int r = 0; r < 16; ++r) P[r] = *reinterpret_cast<const float2*>(tbuf_w + tpad(2 * t8 + 16 * r));
+            two_stages(P);   // index bits 4-7 = r; in a swapping team .x is the odd element of the pair
+            __syncwarp(wmask);
         } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) P[i] = make_float2(v[2 * i], v[2 * i + 1]);   // natural order
@@ -367,18 +491,26 @@ __global__ void __launch_bounds__(MAXT) quant_rows_kernel(const QuantArgs p) {
             if (live) {
                 float* o = p.out_f + m * (int64_t)p.K + (grp << 8) + 2 * t8;
 #pragma unroll
-                for (int r = 0; r < 16; ++r) *reinterpret_cast<float2*>(o + 16 * r) = P[r];
+                for (int r = 0; r < 16; ++r) *reinterpret_cast<float2*>(o + 16 * r) = tsw ? make_float2(P[r].y, P[r].x) : P[r];
             }
             continue;
         }
 
+        // This thread's maximum. The three-input form propagates a NaN, which the reference's fmaxf drops: a thread that
+        // meets one recomputes its maximum without it and takes the exact division below.
         float amax = 0.f;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fmaxf(fabsf(P[i].x), fabsf(P[i].y)));
+        for (int i = 0; i < 16; ++i) amax = max3_abs_nan(amax, P[i].x, P[i].y);
+        const bool has_nan = amax != amax;
+        if (has_nan) {
+            amax = 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fmaxf(fabsf(P[i].x), fabsf(P[i].y)));
+        }
         // the group's 8 lanes first, then one shared-memory atomic per group (non-negative floats order as integers)
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+        amax = fmaxf(amax, __shfl_xor_sync(wmask, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(wmask, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(wmask, amax, 4));
         unsigned* slot = amax_s + (it % 3) * p.rows_per_cta + rloc;
         if (t8 == 0) atomicMax(slot, __float_as_uint(amax));
         __syncthreads();
@@ -393,25 +525,22 @@ __global__ void __launch_bounds__(MAXT) quant_rows_kernel(const QuantArgs p) {
         const float scale = fmaxf(fminf(amax, finite_max<T>()) * (1.f / 127.f), 1.0e-30f);
         if (live && tin == 0) p.scales[m] = scale;
         const float st = rnd<T>(scale);
-        const bool fast = sizeof(T) == 2 && amax <= FLT_MAX;   // rows holding an infinity keep the IEEE division
+        // rows holding an infinity, and threads holding a NaN, keep the IEEE division and the exact clamp
+        const bool fast = sizeof(T) == 2 && amax <= FLT_MAX && !has_nan;
         const float rcp = fast ? __frcp_rn(st) : 0.f;
-        float2 nanacc = make_float2(0.f, 0.f);
         uint32_t c16[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) c16[i] = quant2<T>(P[i], st, rcp, fast, nanacc);
-        if (fast && (nanacc.x != nanacc.x || nanacc.y != nanacc.y)) {   // a NaN in this lane: redo it with exact clamping
-#pragma unroll
-            for (int i = 0; i < 16; ++i) c16[i] = quant2<T>(P[i], st, rcp, false, nanacc);
-        }
+        for (int i = 0; i < 16; ++i) c16[i] = quant2<T>(P[i], st, rcp, fast);
         int8_t* q = p.q + m * (int64_t)p.K + col;
         if (p.rotate) {
             // codes of (2 t8, 2 t8 + 1) + 16 r back through the group's buffer, so each lane stores 32 contiguous bytes
             uint16_t* cb = reinterpret_cast<uint16_t*>(tbuf);
+            const uint32_t order = tsw ? 0x3201u : 0x3210u;   // a swapping team puts its two codes back in element order
 #pragma unroll
-            for (int r = 0; r < 16; ++r) cb[t8 + 8 * r] = (uint16_t)c16[r];
-            __syncwarp();
+            for (int r = 0; r < 16; ++r) cb[t8 + 8 * r] = (uint16_t)__byte_perm(c16[r], 0u, order);
+            __syncwarp(wmask);
             const uint4 lo = reinterpret_cast<const uint4*>(tbuf)[2 * t8], hi = reinterpret_cast<const uint4*>(tbuf)[2 * t8 + 1];
-            __syncwarp();
+            __syncwarp(wmask);
             if (live) {
                 reinterpret_cast<uint4*>(q)[0] = lo;
                 reinterpret_cast<uint4*>(q)[1] = hi;
@@ -477,9 +606,23 @@ int ensure_lut(int which, cudaStream_t st) {
 
 }  // namespace
 
+// Reads and clears the quantizer's status word (a staging wait that ran out); used by gpu_kernels_status.
+int b200q::quant_status_read_clear(int* out) {
+    int v = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, g_quant_status, sizeof(int));
+    if (e != cudaSuccess) return (int)e;
+    if (v != 0) {
+        const int zero = 0;
+        e = cudaMemcpyToSymbol(g_quant_status, &zero, sizeof(int));
+        if (e != cudaSuccess) return (int)e;
+    }
+    *out = v;
+    return 0;
+}
+
 // Device address of the bf16 -> bf16 table of a GEMM-epilogue activation (epilogue.cuh's Act codes), built on first use
 // like the quantizer's own: the epilogue's out(act(out(v))) on bf16 outputs is a function of 16 bits.
-int act_lut_ptr(int act, cudaStream_t st, const uint16_t** out) {
+int b200q::act_lut_ptr(int act, cudaStream_t st, const uint16_t** out) {
     const int which = act == 1 ? LUT_GELU_TANH : act == 2 ? LUT_SILU : act == 3 ? LUT_GELU : -1;
     if (which < 0) return -204;
     if (int rc = ensure_lut(which, st)) return rc;
@@ -501,13 +644,29 @@ int act_lut_ptr(int act, cudaStream_t st, const uint16_t** out) {
 
 namespace {
 
+int sm_count_of(int dev) {
+    static int count[64];
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lk(mu);
+    int& c = count[dev & 63];
+    if (c == 0) cudaDeviceGetAttribute(&c, cudaDevAttrMultiProcessorCount, dev);
+    return c;
+}
+
+// CTAs of one kernel instantiation that fit an SM at a given size: asked of the runtime once per (threads, smem).
+struct OccCache {
+    std::mutex mu;
+    int threads[8] = {}, blocks[8] = {}, n = 0;
+    size_t smem[8] = {};
+};
+
 template <typename T, int PRO, int MAXT>
-int launch_cfg(QuantArgs& p, int threads, size_t smem, int grid, cudaStream_t st) {
+int launch_cfg(QuantArgs& p, int threads, size_t smem, bool persistent, cudaStream_t st) {
     auto kern = quant_rows_kernel<T, PRO, MAXT>;
     static std::atomic<uint64_t> configured{0};
+    int dev = 0;
+    cudaGetDevice(&dev);
     if (smem > 48 * 1024) {
-        int dev = 0;
-        cudaGetDevice(&dev);
         const uint64_t bit = 1ull << (dev & 63);
         if (!(configured.load(std::memory_order_acquire) & bit)) {
             const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
@@ -515,19 +674,46 @@ int launch_cfg(QuantArgs& p, int threads, size_t smem, int grid, cudaStream_t st
             configured.fetch_or(bit, std::memory_order_release);
         }
     }
+    int grid = p.nblocks;
+    if (persistent) {
+        static OccCache occ;
+        int per_sm = 0;
+        {
+            std::lock_guard<std::mutex> lk(occ.mu);
+            for (int i = 0; i < occ.n; ++i)
+                if (occ.threads[i] == threads && occ.smem[i] == smem) per_sm = occ.blocks[i];
+            if (!per_sm) {
+                if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, smem) != cudaSuccess || per_sm < 1) {
+                    (void)cudaGetLastError();
+                    per_sm = 1;
+                }
+                const int slot = occ.n < 8 ? occ.n++ : 7;
+                occ.threads[slot] = threads, occ.smem[slot] = smem, occ.blocks[slot] = per_sm;
+            }
+        }
+        const int resident = per_sm * sm_count_of(dev);
+        if (grid > resident) grid = resident;
+    }
     kern<<<grid, threads, smem, st>>>(p);
     KCHECK();
     return 0;
 }
+
+constexpr size_t kMaxSmem = 227 * 1024;
 
 template <typename T, int PRO>
 int launch_quant(QuantArgs& p, cudaStream_t st) {
     p.tpr = p.K / 32;
     if (p.tpr > 1024) return -2;  // the reference's limit: K <= 32768 (csrc/kernels.cu:264)
     if (p.M <= 0) return 0;
-    static const bool lut_off = [] { const char* e = getenv("GPU_KERNELS_QUANT_LUT"); return e && e[0] == '0'; }();
+    // 16-byte loads and bulk copies: rows must start 16-byte aligned, as the reference's load8 requires too
+    const uintptr_t mis = (uintptr_t)p.x | (uintptr_t)(p.x_stride * sizeof(T)) |
+                          (PRO == PRO_GATE ? (uintptr_t)p.g | (uintptr_t)(p.g_stride * sizeof(T)) : 0) |
+                          (has_aux<PRO>() && PRO != PRO_GATE ? (uintptr_t)(p.up_offset * sizeof(T)) : 0) | (uintptr_t)p.q |
+                          (uintptr_t)p.out_f;
+    if (mis & 15) return -5;
     int lut = -1;
-    if (sizeof(T) == 2 && !lut_off && (int64_t)p.M * p.K >= (1 << 20)) {
+    if (sizeof(T) == 2 && (int64_t)p.M * p.K >= (1 << 20)) {
         lut = PRO == PRO_SILU || PRO == PRO_SWIGLU ? LUT_SILU : PRO == PRO_GELU ? LUT_GELU : PRO == PRO_GELU_TANH ? LUT_GELU_TANH
               : PRO == PRO_GATE ? LUT_SIGMOID : -1;
     }
@@ -535,18 +721,33 @@ int launch_quant(QuantArgs& p, cudaStream_t st) {
         if (int rc = ensure_lut(lut, st)) return rc;
     }
     p.lut = lut;
-    const int gcd32 = p.tpr % 32 == 0 ? 32 : (p.tpr % 16 == 0 ? 16 : 8);
-    const int r0 = 32 / gcd32;    // rows that make the CTA a whole number of warps
-    const int target = 256;
-    int rows = r0 * (target / (p.tpr * r0) > 0 ? target / (p.tpr * r0) : 1);
+    // CTA shape: whole rows, up to 384 threads, at least one warp; any multiple of 8 threads up to 1024 works (the
+    // last warp may be partial), so every K the reference accepts is served
+    int rows = 384 / p.tpr;
+    if (rows < 1) rows = 1;
+    if (rows * p.tpr < 32) rows = (32 + p.tpr - 1) / p.tpr;
     p.rows_per_cta = rows;
     p.nblocks = (p.M + rows - 1) / rows;
     const int threads = rows * p.tpr;
-    const size_t smem = (size_t)(threads / 32) * 4 * kGroupWords * 4 + 3 * rows * 4 +
-                        (is_norm<PRO>() ? (size_t)rows * norm_words(p.K) * 4 : 0);
-    const int grid = p.nblocks;
-    if (threads > 512) return launch_cfg<T, PRO, 1024>(p, threads, smem, grid, st);
-    return launch_cfg<T, PRO, 512>(p, threads, smem, grid, st);
+    auto up = [](size_t v, size_t a) { return (v + a - 1) / a * a; };
+    size_t off = (size_t)((threads + 31) / 32) * kWarpWords * 4;
+    p.off_amax = (uint32_t)off, off += (size_t)3 * rows * 4;
+    p.off_norm = (uint32_t)off, off += is_norm<PRO>() ? (size_t)rows * norm_words(p.K) * 4 : 0;
+    off = up(off, 16);
+    p.off_lut = (uint32_t)off, off += lut >= 0 ? (size_t)2 * kLutRange * 2 : 0;
+    off = up(off, 8);
+    p.off_bar = (uint32_t)off, off += 8;
+    off = up(off, 128);
+    p.off_stage = (uint32_t)off;
+    const size_t stage_bytes = (size_t)rows * p.K * sizeof(T) * (has_aux<PRO>() ? 2 : 1);
+    // staged (persistent CTAs with the next block's rows in flight) when the buffer fits; otherwise one block per CTA
+    // with direct loads
+    p.staged = off + stage_bytes <= kMaxSmem;
+    const size_t smem = p.staged ? off + stage_bytes : off;
+    if (smem > kMaxSmem) return -2;
+    if (threads > 512) return launch_cfg<T, PRO, 1024>(p, threads, smem, p.staged != 0, st);
+    if (threads > 384) return launch_cfg<T, PRO, 512>(p, threads, smem, p.staged != 0, st);
+    return launch_cfg<T, PRO, 384>(p, threads, smem, p.staged != 0, st);
 }
 
 template <typename T>

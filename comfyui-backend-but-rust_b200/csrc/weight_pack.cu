@@ -563,9 +563,8 @@ GPU_API int gpu_sd_quant_rows(const void* x, int64_t x_stride, int8_t* q, float*
     if ((rotate != 0 && rotate != 64 && rotate != 256) || (rotate && K % rotate)) return -1;
     if (M <= 0 || K <= 0) return 0;
     // register kernel: whole 16-value pieces per thread, rotation groups inside a warp, aligned rows
-    static const bool no_reg = [] { const char* e = getenv("GPU_KERNELS_SD_SMEM"); return e && e[0] == '1'; }();
     const int tpr = K / 16;
-    if (!no_reg && K % 16 == 0 && tpr <= 512 && x_stride % 8 == 0 && (((uintptr_t)x & 15) == 0) && (((uintptr_t)q & 15) == 0)) {
+    if (K % 16 == 0 && tpr <= 512 && x_stride % 8 == 0 && (((uintptr_t)x & 15) == 0) && (((uintptr_t)q & 15) == 0)) {
         const int gcd32 = tpr % 32 == 0 ? 32 : tpr % 16 == 0 ? 16 : tpr % 8 == 0 ? 8 : tpr % 4 == 0 ? 4 : tpr % 2 == 0 ? 2 : 1;
         const int r0 = 32 / gcd32;                       // rows that make the CTA a whole number of warps
         int rows = r0 * (256 / (tpr * r0) > 0 ? 256 / (tpr * r0) : 1);

@@ -11,7 +11,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libgpu_kernels.so")
+LIB_PATH = os.path.join(_HERE, "libb200_qlinear.so")
 
 DT_F32, DT_F16, DT_BF16 = 0, 1, 2
 (PRO_PLAIN, PRO_RMS, PRO_GATE, PRO_SWIGLU, PRO_LAYERNORM, PRO_SILU, PRO_GELU, PRO_ADALN, PRO_SITU, PRO_LN_MOD,

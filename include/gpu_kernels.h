@@ -1,4 +1,4 @@
-/* C ABI of libgpu_kernels.so: the quantized-linear path of BetaDoggo/comfyui-backend-but-rust for sm_100a.
+/* C ABI of libb200_qlinear.so / libb200_qlinear.a: the quantized-linear path of BetaDoggo/comfyui-backend-but-rust for sm_100a.
  *
  * Every function keeps the name, argument order and meaning of the symbol the reference's Rust side declares in
  * src/ffi.rs and its CUDA side defines (cited per function as file:line inside the reference project), so the
@@ -33,7 +33,8 @@ enum {
 
 /* Row prologue -> optional ConvRot rotation (R256 per 256-wide group when rotate != 0) -> per-row absmax int8.
  * x [M, x_stride] bf16 or f32, rows 16-byte aligned; q int8 [M, K]; scales f32 [M].
- * Errors: -1 K % 256 != 0, -2 K > 32768, -3 prologue not available, -4 dtype.
+ * Errors: -1 K % 256 != 0, -2 K > 32768, -3 prologue not available, -4 dtype, -5 a row of x (or of g, or the
+ * second half at up_offset), q or out does not start on a 16-byte boundary (the reference's 16-byte loads fault there).
  * Replaces csrc/kernels.cu:271-298 (declared at src/ffi.rs:74). */
 int gpu_quant_rows(int dtype, int prologue, const void* x, int64_t x_stride, const void* g, int64_t g_stride,
                    int64_t up_offset, const float* norm_w, float eps, const void* mod_scale, const void* mod_shift,
@@ -72,8 +73,10 @@ int gpu_sd_group_norm_quant_rows(const void* x, const float* w, const float* b, 
 /* ---- kernels 2 + 3: int8 GEMM mainloop with the fused dequant epilogue -------------------------------- */
 
 /* D[M,N] = out( (A[M,K] . W[N,K]^T) * xs[m] * ws[n] + bias[n] ).  A, W int8 row-major (K contiguous), 16-byte
- * aligned, K % 16 == 0; xs f32 [M]; ws f32 [N]; bias [N] in the OUTPUT dtype or NULL; D [M,N] row-major.
- * M == 0, N == 0 or K == 0 succeed without work. Errors: -200 bad out_dt, -202 alignment, -203 descriptor.
+ * aligned with K % 16 == 0 for the tensor-core kernel (K % 8 == 0 or bases off a 16-byte boundary: a slower CUDA-core
+ * kernel, same results); xs f32 [M]; ws f32 [N]; bias [N] in the OUTPUT dtype or NULL; D [M,N] row-major.
+ * M == 0, N == 0 or K == 0 succeed without work. Errors: -200 bad out_dt or K % 8 != 0 (the reference's "no tile
+ * configuration"; -201 from the residual form), -203 descriptor.
  * Replaces csrc/gemm.cu:123-129 over csrc/vendor/cutlass_gemm_int8.cu:373-388 (src/ffi.rs:38). */
 int gpu_int8_gemm(const int8_t* A, const int8_t* W, const float* xs, const float* ws, const void* bias, void* D,
                   int64_t M, int64_t N, int64_t K, int out_dt, void* stream);

@@ -27,7 +27,7 @@ def oracle():
 
 @pytest.fixture(scope="session")
 def pkg():
-    """The product package; importing it loads libgpu_kernels.so and fails loudly if it is missing."""
+    """The product package; importing it loads libb200_qlinear.so and fails loudly if it is missing."""
     from __graft_entry__ import load_package
     return load_package()
 

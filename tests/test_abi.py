@@ -33,6 +33,25 @@ def test_library_exports_every_declared_symbol(pkg):
     assert set(pkg.ffi.SIGNATURES) == set(_declared()), "ffi.py and the header list the same entry points"
 
 
+def test_dynamic_symbols_are_exactly_the_header(pkg):
+    """Nothing but the declared entry points leaves the shared library, and the static archive (the form a host that
+    links statically takes, under a name that cannot collide with the reference's own `gpu_kernels`) defines the same
+    entry points and otherwise only names inside the library's own namespace."""
+    import subprocess
+    out = subprocess.run(["nm", "-D", "--defined-only", pkg.ffi.LIB_PATH], capture_output=True, text=True, check=True).stdout
+    exported = sorted(ln.split()[2] for ln in out.splitlines() if len(ln.split()) == 3 and ln.split()[1] in "TDB")
+    assert exported == _declared(), set(exported) ^ set(_declared())
+    archive = os.path.join(os.path.dirname(pkg.ffi.LIB_PATH), "libb200_qlinear.a")
+    assert os.path.exists(archive)
+    out = subprocess.run(["nm", "-g", "--defined-only", archive], capture_output=True, text=True, check=True).stdout
+    glob = {ln.split()[2] for ln in out.splitlines() if len(ln.split()) == 3 and ln.split()[1] == "T"}
+    assert set(_declared()) <= glob
+    # what else the objects define is either in the library's namespace or carries nvcc's per-file unique prefix
+    stray = {n for n in glob - set(_declared()) if not (n.startswith("_ZN5b200q") or "_GLOBAL__N_" in n or n.startswith("__cudaRegister")
+                                                        or n.startswith("__sti") or "__nv_" in n)}
+    assert not stray, stray
+
+
 def test_argument_errors_need_no_device(pkg):
     lib = pkg.lib
     # K % 256 != 0 -> -1 (reference: csrc/kernels.cu:275)

@@ -127,8 +127,43 @@ def test_unaligned_output_takes_the_direct_store_path(pkg, oracle, dev):
     acc = oracle.int8_gemm_acc(A, W)
     got = pkg.linear.int8_gemm(A.to(dev), W.to(dev), xs.to(dev), ws.to(dev), None)
     assert_bits_equal(got, oracle.epilogue(acc, xs, ws, None, contract=3), "ragged N")
-    with pytest.raises(pkg.GpuKernelError, match="-202"):
+    # rows that are not a whole number of 8-byte pieces: the reference's "no configuration" code
+    with pytest.raises(pkg.GpuKernelError, match="-200"):
         pkg.linear.int8_gemm(A[:, :250].contiguous().to(dev), W[:, :250].contiguous().to(dev), xs.to(dev), ws.to(dev), None)
+
+
+@pytest.mark.parametrize("M,N,K", [(70, 96, 8), (129, 200, 24), (300, 520, 72), (64, 1000, 264), (513, 136, 1000)])
+def test_rows_of_8_byte_pieces(pkg, oracle, ref, dev, M, N, K):
+    """K a multiple of 8 but not of 16: the reference serves these with its narrow-alignment tile configurations; here a
+    CUDA-core kernel does (TMA needs a 16-byte row pitch). Same bits as the oracle and as the reference's kernel."""
+    g, A, W, xs, ws = _operands(M, N, K, 33)
+    acc = oracle.int8_gemm_acc(A, W)
+    d = lambda t: t.to(dev)
+    L = pkg.linear
+    assert_bits_equal(L.int8_gemm_acc_i32(d(A), d(W)), acc, "accumulators")
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        bias = (torch.randn(N, generator=g) * 0.5).to(dtype)
+        rs = torch.randn(N, generator=g).to(dtype)
+        rr = torch.randn(M, N, generator=g).to(dtype)
+        got = L.int8_gemm(d(A), d(W), d(xs), d(ws), d(bias), out_dtype=dtype)
+        assert_bits_equal(got, oracle.epilogue(acc, xs, ws, bias, out_dtype=dtype, contract=3), f"plain {dtype}")
+        resid = d(rr).clone()
+        L.int8_gemm(d(A), d(W), d(xs), d(ws), d(bias), out_dtype=dtype, rscale=d(rs), resid=resid, out=resid)
+        assert_bits_equal(resid, oracle.epilogue(acc, xs, ws, bias, rs, rr, out_dtype=dtype, contract=3), f"residual {dtype}")
+        if N % 8 == 0:      # the reference's kernels write 16-byte output vectors
+            assert_bits_equal(got, ref.int8_gemm(d(A), d(W), d(xs), d(ws), d(bias), out_dtype=dtype), f"reference kernel {dtype}")
+
+
+def test_misaligned_operand_bases(pkg, oracle, dev):
+    """A and W that start off a 16-byte boundary (views into larger buffers) take the same CUDA-core kernel."""
+    g, A, W, xs, ws = _operands(100, 72, 256, 34)
+    bufA = torch.zeros(100 * 256 + 8, dtype=torch.int8, device=dev)
+    bufW = torch.zeros(72 * 256 + 8, dtype=torch.int8, device=dev)
+    Ad = bufA[8:].view(100, 256); Ad.copy_(A)
+    Wd = bufW[8:].view(72, 256); Wd.copy_(W)
+    acc = oracle.int8_gemm_acc(A, W)
+    assert_bits_equal(pkg.linear.int8_gemm_acc_i32(Ad, Wd), acc, "accumulators")
+    assert_bits_equal(pkg.linear.int8_gemm(Ad, Wd, xs.to(dev), ws.to(dev), None), oracle.epilogue(acc, xs, ws, None, contract=3), "bf16 output")
 
 
 def test_full_size_linearity_and_guard_bands(pkg, dev):
@@ -225,3 +260,28 @@ def test_two_pass_quantizer_and_epilogue_only(pkg, oracle, dev):
     assert_bits_equal(L.int8_epilogue(part, s, ws, bias), L.int8_gemm(q, W, s, ws, bias), "plain")
     assert_bits_equal(L.int8_epilogue(part, s, ws, bias, rscale=rs, resid=rr), L.int8_gemm(q, W, s, ws, bias, rscale=rs, resid=rr), "residual")
     assert_bits_equal(L.int8_epilogue(part, s, ws, bias, act=1), L.int8_gemm(q, W, s, ws, bias, act=1), "gelu")
+
+
+@pytest.mark.parametrize("M,N,K", [(2304, 2560, 1024), (4352, 4608, 2048), (2100, 9000, 1280), (5000, 3100, 3072)])
+def test_streamed_tail(pkg, oracle, dev, M, N, K):
+    """More tiles than clusters and a ragged last round: the last rounds' tiles are dealt out in K stages, tiles that
+    straddle two clusters meet through global scratch. Accumulators and outputs equal the oracle's, twice in a row (the
+    first launch must leave the scratch at zero), then a K-split problem shares the same scratch."""
+    g, A, W, xs, ws = _operands(M, N, K, 91)
+    bias = (torch.randn(N, generator=g) * 0.5).bfloat16()
+    rr = torch.randn(M, N, generator=g).bfloat16()
+    rs = torch.randn(N, generator=g).bfloat16()
+    acc = oracle.int8_gemm_acc(A, W)
+    d = lambda t: t.to(dev)
+    L = pkg.linear
+    for _ in range(2):
+        assert_bits_equal(L.int8_gemm_acc_i32(d(A), d(W)), acc, "accumulators")
+        assert_bits_equal(L.int8_gemm(d(A), d(W), d(xs), d(ws), d(bias)), oracle.epilogue(acc, xs, ws, bias, contract=3), "plain")
+    resid = d(rr).clone()
+    L.int8_gemm(d(A), d(W), d(xs), d(ws), d(bias), rscale=d(rs), resid=resid, out=resid)
+    assert_bits_equal(resid, oracle.epilogue(acc, xs, ws, bias, rs, rr, contract=3), "residual in place")
+    got = L.int8_gemm(d(A), d(W), d(xs), d(ws), d(bias.float()), out_dtype=torch.float32)
+    assert_bits_equal(got, oracle.epilogue(acc, xs, ws, bias.float(), out_dtype=torch.float32, contract=3), "f32 output")
+    g2, A2, W2, xs2, ws2 = _operands(256, 512, 8192, 92)
+    assert_bits_equal(L.int8_gemm_acc_i32(d(A2), d(W2)), oracle.int8_gemm_acc(A2, W2), "K-split problem after")
+    assert L.kernel_status() == 0

@@ -130,3 +130,88 @@ def test_errors(pkg, dev):
         pkg.linear.quant_rows(torch.zeros(1, 33024, device=dev, dtype=torch.bfloat16), 0, 0)
     q, s = pkg.linear.quant_rows(torch.zeros(0, 512, device=dev, dtype=torch.bfloat16), 0, 0)
     assert q.shape == (0, 512)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_every_row_length_the_reference_accepts(pkg, oracle, dev, dtype):
+    """K = 256 n for n = 1 .. 128 (the reference takes every one of them, csrc/kernels.cu:261-268), a few rows each so
+    that CTAs hold several rows, rows straddle warps and the last warp of a CTA is partial."""
+    g = torch.Generator().manual_seed(4242)
+    for n in range(1, 129):
+        K, M = 256 * n, 5 if n < 64 else 2
+        x = torch.randn(M, K, generator=g)
+        x[:, torch.randperm(K, generator=g)[:3]] *= 25.0
+        x = x.to(dtype)
+        xd = x.to(dev)
+        for rotate in (0, 1):
+            q, s = pkg.linear.quant_rows(xd, PLAIN, rotate)
+            qo, so = oracle.quant_rows(x, PLAIN, rotate)
+            assert_bits_equal(s, so, f"scales K={K} rot={rotate}")
+            assert_bits_equal(q, qo, f"codes K={K} rot={rotate}")
+    assert pkg.linear.kernel_status() == 0
+
+
+@pytest.mark.parametrize("n", [1, 3, 12, 33, 48, 66, 127])
+def test_many_row_blocks_through_the_staging_buffer(pkg, oracle, dev, n):
+    """Enough rows that every CTA walks several row blocks (bulk copies into the staging buffer, one block ahead), with a
+    row stride larger than K and a ragged last block."""
+    K = 256 * n
+    M = 3001 if n <= 12 else 701
+    g = torch.Generator().manual_seed(n)
+    x = torch.randn(M, K + 256, generator=g).bfloat16()
+    for rotate in (0, 1):
+        q, s = pkg.linear.quant_rows(x.to(dev), PLAIN, rotate, K=K)
+        qo, so = oracle.quant_rows(x, PLAIN, rotate, K=K)
+        assert_bits_equal(s, so, f"scales rot={rotate}")
+        assert_bits_equal(q, qo, f"codes rot={rotate}")
+    assert pkg.linear.kernel_status() == 0
+
+
+@pytest.mark.parametrize("pro", [SILU, GELU, GELU_TANH, SWIGLU, GATE])
+def test_tabulated_prologues_bit_exact_against_the_reference_kernel(pkg, ref, dev, pro):
+    """Rows of 2^20 elements and more take the one-variable activations from tables (the hot part in shared memory, the
+    rest from the whole table). Inputs cover the table's whole domain: zeros, subnormals, tiny and huge magnitudes of both
+    signs, infinities and NaN beside ordinary values."""
+    M, K = 420, 3072
+    g = torch.Generator().manual_seed(90 + pro)
+    x = torch.randn(M, 2 * K, generator=g) * 2.0
+    special = torch.tensor([0.0, -0.0, 1e-40, -1e-40, 1e-30, -1e-30, 6e-5, -6e-5, 3e-5, 127.0, 128.0, -128.0, 200.0, -200.0,
+                            1e30, -1e30, 3.3e38, -3.3e38, float("inf"), float("-inf"), float("nan")])
+    idx = torch.randint(0, M * 2 * K, (4000,), generator=g)
+    x.view(-1)[idx] = special[torch.randint(0, len(special), (4000,), generator=g)]
+    x[7] = 0.0                                  # a whole row outside the shared-memory part
+    x[9, :K] = 1e-20
+    x = x.bfloat16().to(dev)
+    gt = (torch.randn(M, K, generator=g) * 3.0).bfloat16().to(dev)
+    kw = dict(K=K)
+    if pro == SWIGLU:
+        kw["up_offset"] = K
+    if pro == GATE:
+        kw["g"] = gt
+    for rot in (0, 1):
+        q, s = pkg.linear.quant_rows(x, pro, rot, **kw)
+        qr, sr = ref.quant_rows(x, pro, rot, **kw)
+        assert_bits_equal(s, sr, f"scales pro={pro} rot={rot}")
+        assert_bits_equal(q, qr, f"codes pro={pro} rot={rot}")
+    assert pkg.linear.kernel_status() == 0
+
+
+def test_every_bf16_value_through_the_tabulated_prologues(pkg, ref, dev):
+    """All 65536 bf16 bit patterns, each as a one-hot row (so that its own code is +-127 or 0 and the scale exposes the
+    activation's value), through SiLU / GELU / GELU-tanh with the tables in use: scales and codes equal the reference's."""
+    bits = torch.arange(65536, dtype=torch.int32).to(torch.int16)
+    vals = bits.view(torch.bfloat16)
+    x = torch.zeros(65536, 256, dtype=torch.bfloat16)
+    x[:, 17] = vals
+    x = x.to(dev)
+    for pro in (SILU, GELU, GELU_TANH):
+        q, s = pkg.linear.quant_rows(x, pro, 0)
+        qr, sr = ref.quant_rows(x, pro, 0)
+        assert_bits_equal(s, sr, f"scales pro={pro}")
+        assert_bits_equal(q, qr, f"codes pro={pro}")
+
+
+def test_misaligned_rows_are_refused(pkg, dev):
+    x = torch.zeros(4, 520, device=dev, dtype=torch.bfloat16)
+    with pytest.raises(pkg.GpuKernelError, match="-5"):
+        pkg.linear.quant_rows(x[:, 4:], PLAIN, 0, K=512)          # rows start 8 bytes off a 16-byte boundary

@@ -122,3 +122,31 @@ def test_error_codes(pkg, dev):
         pkg.linear.quant_rows(x, RMS, 1, norm_w=w, norm_b=w)    # gpu_quant_rows_b takes LN_MOD and LN_AFFINE only
     with pytest.raises(RuntimeError, match="-4"):
         pkg.linear.quant_rows(x.float(), LN_AFFINE, 1, norm_w=w, norm_b=w)
+
+
+@pytest.mark.parametrize("pro,variant", [(RMS, 2), (RMS, 3), (LAYERNORM, 3)])
+def test_f32_rows_with_modulation_for_every_row_length(pkg, ref, dev, pro, variant):
+    """f32 rows with modulation: where nothing rounds between a * n and + shift the reference's build decides whether the
+    two fuse, and for RMS it depends on which of the four groups of a reference warp an element belongs to. Every
+    K = 256 n, n = 1 .. 128, against the reference's kernel."""
+    for n in range(1, 129):
+        K, M = 256 * n, 3 if n < 64 else 2
+        c = _case(M, K, 1000 + n, torch.float32)
+        kw = _to(dev, _kwargs(pro, c, variant))
+        for rotate in (0, 1):
+            q, s = pkg.linear.quant_rows(c["x"].to(dev), pro, rotate, **kw)
+            qr, sr = ref.quant_rows(c["x"].to(dev), pro, rotate, **kw)
+            assert_bits_equal(s, sr, f"scales K={K} rot={rotate}")
+            assert_bits_equal(q, qr, f"codes K={K} rot={rotate}")
+
+
+@pytest.mark.parametrize("pro,variant", [(RMS, 3), (LN_MOD, 2), (ADALN, 0), (LN_AFFINE, 0)])
+def test_bf16_norm_prologues_for_every_row_length(pkg, ref, dev, pro, variant):
+    for n in list(range(1, 40)) + [47, 54, 64, 66, 97, 128]:
+        K, M = 256 * n, 3
+        c = _case(M, K, 2000 + n)
+        kw = _to(dev, _kwargs(pro, c, variant))
+        q, s = pkg.linear.quant_rows(c["x"].to(dev), pro, 1, **kw)
+        qr, sr = ref.quant_rows(c["x"].to(dev), pro, 1, **kw)
+        assert_bits_equal(s, sr, f"scales K={K}")
+        assert_bits_equal(q, qr, f"codes K={K}")

@@ -20,7 +20,9 @@ def _call(fn, A, W, xs, ws, bias, D, out_dt):
 
 
 @pytest.mark.parametrize("M,N,K,dtype,code", [(256, 512, 8192, torch.bfloat16, DT_BF16), (200, 300, 4096, torch.float32, DT_F32),
-                                              (130, 1000, 2048, torch.bfloat16, DT_BF16)])
+                                              (130, 1000, 2048, torch.bfloat16, DT_BF16),
+                                              (256, 2048, 8192, torch.bfloat16, DT_BF16),      # 8 tiles once the width is 256
+                                              (1024, 1024, 1024, torch.bfloat16, DT_BF16)])    # the full 16 tiles of 256 x 256
 def test_matches_the_allocating_entry_point_twice_in_a_row(pkg, dev, M, N, K, dtype, code):
     g = torch.Generator().manual_seed(M + N + K)
     A = torch.randint(-128, 128, (M, K), generator=g, dtype=torch.int8).to(dev)
@@ -55,4 +57,30 @@ def test_rejects_what_the_static_array_cannot_hold(pkg, dev):
     ws = torch.ones(N, device=dev)
     D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
     assert _call(pkg.lib.gpu_int8_gemm_noalloc, A, W, xs, ws, None, D, DT_BF16) == -205
-    assert _call(pkg.lib.gpu_int8_gemm_noalloc, A[:, :8], W[:, :8], xs, ws, None, D, DT_BF16) in (-202, -205)
+    # 17 tiles at the widest tile: one beyond the array
+    W17 = torch.zeros((17 * 256, K), dtype=torch.int8, device=dev)
+    assert _call(pkg.lib.gpu_int8_gemm_noalloc, A[:256], W17, xs, torch.ones(17 * 256, device=dev), None,
+                 torch.empty((256, 17 * 256), dtype=torch.bfloat16, device=dev), DT_BF16) == -205
+    # K not a multiple of 16: refused before anything else is looked at
+    A8 = torch.zeros((64, 8), dtype=torch.int8, device=dev)
+    assert _call(pkg.lib.gpu_int8_gemm_noalloc, A8, A8, xs, ws, None, D, DT_BF16) == -202
+
+
+def test_second_call_allocates_no_device_memory(pkg, dev):
+    """After one warm-up call per output type (module load and kernel set-up are the runtime's), further calls leave the
+    free device memory as it is."""
+    M, N, K = 256, 512, 4096
+    A = torch.ones((M, K), dtype=torch.int8, device=dev)
+    W = torch.ones((N, K), dtype=torch.int8, device=dev)
+    xs = torch.ones(M, device=dev)
+    ws = torch.ones(N, device=dev)
+    D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    assert _call(pkg.lib.gpu_int8_gemm_noalloc, A, W, xs, ws, None, D, DT_BF16) == 0
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        assert _call(pkg.lib.gpu_int8_gemm_noalloc, A, W, xs, ws, None, D, DT_BF16) == 0
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0
+    assert bool((D.float() == K).all())
