@@ -30,7 +30,6 @@ enum KernelStatus {
     ST_TIMEOUT_TMEM_FULL = 3,  // epilogue waited for an accumulator
     ST_TIMEOUT_TMEM_EMPTY = 4, // MMA issuer waited for a drained accumulator
     ST_TIMEOUT_UNPACK = 5,   // W6 unpack warps waited for a packed stage
-    ST_TIMEOUT_PARKED = 6,   // epilogue waited for the accumulators another cluster parks for a shared tile
 };
 
 // ---- rounding to a storage type and back (what materialising a tensor of that type does) ----------

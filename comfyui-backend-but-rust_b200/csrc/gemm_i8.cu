@@ -68,12 +68,6 @@ struct GemmParams {
     int splits;          // K slices per split tile (>= 2), or 0: work items [whole_tiles, whole_tiles + rem * splits)
     int kps;             // stages per K slice
     int num_items;       // whole_tiles + split tiles * splits
-    // Streamed tail: when the tiles do not fill the last round, the last one to two rounds' tiles are dealt out in K stages
-    // instead of whole tiles, every cluster taking an equal run of consecutive stages. A tile that straddles two clusters
-    // is finished by the one that holds its first stages (it reaches them last); the other, which starts with the tile's
-    // last stages, parks its raw accumulators in `partials`.
-    int dp_tiles;        // tiles of the whole rounds before the streamed part (work items [0, dp_tiles), round-robin)
-    int sk_units;        // K stages of the streamed part = (num_tiles - dp_tiles) * k_iters, or 0
     int* scratch;        // counters [slot][2][4][8], zero between launches
     int* partials;       // [slot][2][4][8][32 values][32 lanes] int32 sums, zero between launches
     uint32_t idesc;      // instruction descriptor for M = 256, N = bn
@@ -94,49 +88,15 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
     tn = r / gsize;
 }
 
-// A work item: a tile, a K range (in stages) and what happens to the accumulator.
-enum ItemKind { ITEM_WHOLE = 0, ITEM_SLICE = 1, ITEM_PARK = 2, ITEM_FINISH = 3 };
+// Work item -> tile, K range (in stages) and, for a slice of a split tile, its slot in the scratch.
+enum ItemKind { ITEM_WHOLE = 0, ITEM_SLICE = 1 };
 struct WorkItem { int tile, k0, kn, kind, slot; };
-// The sequence of work items of one cluster; every role of the cluster walks its own copy.
-struct WorkCursor {
-    int w;          // next round-robin item
-    int u;          // streamed part: next K stage of this cluster's run
-};
-__device__ __forceinline__ WorkCursor first_item(const GemmParams& p, int cluster_id, int nclusters) {
-    return {cluster_id, p.sk_units > 0 ? (int)(((long long)p.sk_units * cluster_id) / nclusters) : 0};
-}
-__device__ __forceinline__ bool next_item(const GemmParams& p, WorkCursor& c, int cluster_id, int nclusters, WorkItem& wi) {
-    if (p.sk_units > 0) {
-        // The streamed run comes first, so that its slower hand-over (global scratch, fences) hides under the whole tiles
-        // that follow and every cluster ends on a whole tile at the same time.
-        const int u_end = (int)(((long long)p.sk_units * (cluster_id + 1)) / nclusters);
-        if (c.u < u_end) {
-            const int t = c.u / p.k_iters, k0 = c.u - t * p.k_iters;
-            const int kn = min(p.k_iters - k0, u_end - c.u);
-            c.u += kn;
-            // a run starts with the last stages of a tile (parked for the previous cluster) and ends with the first stages
-            // of another (finished here with what the next cluster parked as its own first item)
-            const int kind = kn == p.k_iters ? ITEM_WHOLE : (k0 > 0 ? ITEM_PARK : ITEM_FINISH);
-            wi = {p.dp_tiles + t, k0, kn, kind, kind == ITEM_PARK ? cluster_id - 1 : cluster_id};
-            return true;
-        }
-        if (c.w >= p.dp_tiles) return false;
-        wi = {c.w, 0, p.k_iters, ITEM_WHOLE, 0};
-        c.w += nclusters;
-        return true;
-    }
-    if (c.w >= p.num_items) return false;
-    const int w = c.w;
-    c.w += nclusters;
-    if (w < p.whole_tiles) {
-        wi = {w, 0, p.k_iters, ITEM_WHOLE, 0};
-        return true;
-    }
+__device__ __forceinline__ WorkItem decode_item(const GemmParams& p, int w) {
+    if (w < p.whole_tiles) return {w, 0, p.k_iters, ITEM_WHOLE, 0};
     const int j = w - p.whole_tiles;
     const int slot = j / p.splits, sidx = j - slot * p.splits;
     const int k0 = sidx * p.kps;
-    wi = {p.whole_tiles + slot, k0, min(p.kps, p.k_iters - k0), ITEM_SLICE, slot};
-    return true;
+    return {p.whole_tiles + slot, k0, min(p.kps, p.k_iters - k0), ITEM_SLICE, slot};
 }
 constexpr int kCountersPerSlot = 2 * 4 * 8;   // CTA of the pair x TMEM lane quarter x 32-column chunk
 
@@ -394,9 +354,8 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            WorkCursor cur = first_item(p, cluster_id, nclusters);
-            WorkItem wi;
-            while (ok && next_item(p, cur, cluster_id, nclusters, wi)) {
+            for (int w = cluster_id; w < p.num_items && ok; w += nclusters) {
+                const WorkItem wi = decode_item(p, w);
                 int tm, tn;
                 tile_coords(wi.tile, p.tiles_m, p.tiles_n, tm, tn);
                 const int row_a = tm * (2 * BM) + (int)rank * BM;
@@ -432,10 +391,8 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             int buf = 0;
             uint32_t tphase = 0;
             bool ok = true;
-            WorkCursor cur = first_item(p, cluster_id, nclusters);
-            WorkItem wi;
-            while (ok && next_item(p, cur, cluster_id, nclusters, wi)) {
-                const int kn = wi.kn;
+            for (int w = cluster_id; w < p.num_items && ok; w += nclusters) {
+                const int kn = decode_item(p, w).kn;
                 if (!mbar_wait(bar_tempty + 8 * buf, tphase ^ 1u, abort_s, ST_TIMEOUT_TMEM_EMPTY)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * 256;
@@ -479,9 +436,8 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         float* my_vec = reinterpret_cast<float*>(my_stage + 2048);   // ws[128] | bias[128] | rscale[128]
         int buf = 0;
         uint32_t tphase = 0;
-        WorkCursor cur = first_item(p, cluster_id, nclusters);
-        WorkItem wi;
-        while (next_item(p, cur, cluster_id, nclusters, wi)) {
+        for (int w = cluster_id; w < p.num_items; w += nclusters) {
+            const WorkItem wi = decode_item(p, w);
             int tm, tn;
             tile_coords(wi.tile, p.tiles_m, p.tiles_n, tm, tn);
             const int n0 = tn * BN;
@@ -550,74 +506,34 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     }
                 }
             } else {
-                // The accumulator holds only part of the tile's K range; the parts meet in global scratch: per warp chunk a
-                // buffer of [32 values][32 lanes] int32 and a counter, all zero between launches.
-                //   ITEM_SLICE   (few-tile problem cut along K) every slice adds its part with atomic adds (integer sums do
-                //                not depend on the order); the slice that arrives last at the chunk's counter reads the total
-                //   ITEM_PARK    (streamed tail, the last K stages of a tile; the cluster's first item) plain stores of all
-                //                the warp's chunks, one fence, then the counter of the warp's first chunk is raised
-                //   ITEM_FINISH  (streamed tail, the first K stages) waits, bounded, for that counter and adds what is parked
-                // Whoever ends up with the total leaves buffer and counter at zero and runs the epilogue (release / acquire
-                // through the fences around the counter).
-                const int sub0 = ((int)rank * 4 + quad) * 8;
-                int* cnt0 = p.scratch + wi.slot * kCountersPerSlot + sub0 + half;
-                bool proceed = true;
-                if (wi.kind == ITEM_FINISH) {
-                    int seen = 1;
-                    if (lane == 0) {
-                        volatile int* vc = cnt0;
-                        seen = *vc;
-                        if (!seen) {
-                            const uint64_t t0 = globaltimer_ns();
-                            while (!(seen = *vc)) {
-                                __nanosleep(64);
-                                if (*abort_s || globaltimer_ns() - t0 > kWaitLimitNs) break;
-                            }
-                        }
-                        if (seen) *vc = 0;
-                        else if (!*abort_s) *abort_s = ST_TIMEOUT_PARKED;
-                    }
-                    proceed = __shfl_sync(0xffffffffu, seen, 0) != 0;
-                    __threadfence();
-                }
-                if (!proceed) break;
+                // A slice of a split tile adds its raw accumulators into the tile's int32 buffer in global scratch with
+                // atomic adds (integer sums do not depend on the order); the slice that arrives last at a chunk's counter
+                // reads the total, leaves buffer and counter at zero for the next launch, and runs the epilogue
+                // (release / acquire through the fences around the counter).
 #pragma unroll 1
                 for (int c = half; c < nchunks; c += 2) {
                     tmem_ld32(taddr + c * 32, ra);
                     tmem_ld_wait();
                     if (n0 + c * 32 >= p.N) continue;
-                    int* sum = p.partials + ((size_t)wi.slot * kCountersPerSlot + sub0 + c) * 1024 + lane;
-                    if (wi.kind == ITEM_PARK) {
+                    const int sub = ((int)rank * 4 + quad) * 8 + c;
+                    int* sum = p.partials + ((size_t)wi.slot * kCountersPerSlot + sub) * 1024 + lane;   // [32 values][32 lanes]
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) __stcg(sum + 32 * j, (int)ra[j]);
-                        continue;
-                    }
-                    if (wi.kind == ITEM_SLICE) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) atomicAdd(sum + 32 * j, (int)ra[j]);
-                        __threadfence();
-                        __syncwarp();
-                        int* cnt = p.scratch + wi.slot * kCountersPerSlot + sub0 + c;
-                        int old = 0;
-                        if (lane == 0) old = atomicAdd(cnt, 1);
-                        old = __shfl_sync(0xffffffffu, old, 0);
-                        if (old != p.splits - 1) continue;
-                        if (lane == 0) *cnt = 0;
-                        __threadfence();
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) ra[j] = 0;
-                    }
+                    for (int j = 0; j < 32; ++j) atomicAdd(sum + 32 * j, (int)ra[j]);
+                    __threadfence();
+                    __syncwarp();
+                    int* cnt = p.scratch + wi.slot * kCountersPerSlot + sub;
+                    int old = 0;
+                    if (lane == 0) old = atomicAdd(cnt, 1);
+                    old = __shfl_sync(0xffffffffu, old, 0);
+                    if (old != p.splits - 1) continue;
+                    if (lane == 0) *cnt = 0;
+                    __threadfence();
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        ra[j] += (uint32_t)__ldcg(sum + 32 * j);
+                        ra[j] = (uint32_t)__ldcg(sum + 32 * j);
                         __stcg(sum + 32 * j, 0);
                     }
                     emit(ra, c);
-                }
-                if (wi.kind == ITEM_PARK) {
-                    __threadfence();
-                    __syncwarp();
-                    if (lane == 0) atomicExch(cnt0, 1);
                 }
             }
             tc_fence_before();
@@ -781,7 +697,7 @@ int launch_pair_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tw, const
 // zero, and after a kernel has reported a bounded wait that ran out (gpu_kernels_status) it is cleared again before
 // the next use. A stream beyond the few slots, a failed allocation or a stream under capture that has no buffer yet
 // simply runs without the split.
-constexpr int kWorkspaceSlots = 80;                       // tiles of 256 x 256 int32 sums (one per cluster at most)
+constexpr int kWorkspaceSlots = 40;                       // tiles of 256 x 256 int32 sums (at most half the clusters' worth)
 constexpr size_t kWorkspaceCounterBytes = 1 << 16;        // counters first, sums behind them
 constexpr size_t kSplitWorkspaceBytes = (size_t)kWorkspaceSlots * 256 * 256 * 4 + kWorkspaceCounterBytes;
 std::atomic<uint64_t> g_workspace_epoch{1};               // raised when a kernel may have left scratch behind
@@ -828,16 +744,14 @@ int* split_workspace(int dev, cudaStream_t st, size_t need) {
 // the last round nearly empty at 256 takes a narrower tile instead; narrower tiles read A from L2 once more per column
 // tile, and on large shapes the L2 -> SM path, not the tensor core, is what the kernel waits for (up-projection: 113 us
 // at 256 against 118 at 224 and 124 at 192, although 224 has the smaller product), hence the mild penalty on width lost.
-// With the streamed tail available a ragged last round costs only its share of a round (plus the hand-over).
-int choose_bn(int64_t M, int64_t N, int clusters, bool can_stream) {
+int choose_bn(int64_t M, int64_t N, int clusters) {
     const int64_t tm = (M + 2 * BM - 1) / (2 * BM);
     int best = 256;
     double best_cost = 1e30;
     for (int bn = 256; bn >= 64; bn -= 32) {
         const int64_t tiles = tm * ((N + bn - 1) / bn);
-        double rounds = (double)((tiles + clusters - 1) / clusters);
-        if (can_stream && tiles > clusters && tiles % clusters) rounds = std::min(rounds, (double)tiles / clusters + 0.15);
-        const double cost = rounds * (bn + 32) * (1.0 + 0.4 * (256 - bn) / 256.0);
+        const int64_t rounds = (tiles + clusters - 1) / clusters;
+        const double cost = (double)rounds * (bn + 32) * (1.0 + 0.4 * (256 - bn) / 256.0);
         if (cost < best_cost) best_cost = cost, best = bn;
     }
     return best;
@@ -880,18 +794,7 @@ int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const f
     p.tma_store = al16(D) && ((N * esz) % 16 == 0);
     p.ksub = K <= BK ? 1 : 2;
     p.k_iters = (int)((K + p.ksub * BK - 1) / (p.ksub * BK));
-    // The K-split forms need scratch; whether this stream has (or can get) some decides the tile width too.
-    const bool long_k = p.k_iters >= 4;
-    int* wsp = nullptr;
-    int bn = choose_bn(M, N, clusters, false);
-    {
-        const int64_t tm = (M + 2 * BM - 1) / (2 * BM);
-        const int64_t t0 = tm * ((N + bn - 1) / bn), t256 = tm * ((N + 255) / 256);
-        const bool few = t0 < clusters && 2 * (t0 % clusters) <= clusters && p.k_iters >= 16;
-        const bool ragged = long_k && t256 > clusters && (clusters - t256 % clusters) % clusters * 100 >= 15 * clusters;
-        if (few || ragged) wsp = split_workspace(dev, st, kSplitWorkspaceBytes);
-        if (wsp && ragged) bn = choose_bn(M, N, clusters, true);
-    }
+    const int bn = choose_bn(M, N, clusters);
     p.bn = bn;
     p.idesc = umma_idesc_i8(2 * BM, bn);
     const int stage_bytes = p.ksub * (BM * BK + (bn / 2) * BK);
@@ -907,29 +810,27 @@ int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const f
     } else {
         td = ta;  // unused
     }
+    // K split: a problem with fewer tiles than clusters and a long K (few rows, few columns) is cut along K so that
+    // more SMs stream it; partial sums meet by atomic adds and the slice that arrives last runs the epilogue. Measured
+    // on B200: worth it only when every slice keeps at least eight stages. Cutting the ragged last round of a many-round
+    // problem instead (stream-K: the last rounds' tiles dealt out in K stages, tiles shared by two clusters meeting
+    // through scratch) was built and measured slower than whole tiles on both benchmark linears (121 against 116 us on the
+    // up-projection; 155 against 121 us on the down-projection, where clusters no longer walk K in step and the L2 has to
+    // hold both matrices), so many-round problems run whole tiles only.
     p.whole_tiles = p.num_tiles, p.splits = 0, p.kps = p.k_iters, p.num_items = p.num_tiles;
-    p.dp_tiles = 0, p.sk_units = 0;
-    p.scratch = wsp;
-    p.partials = wsp ? reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(wsp) + kWorkspaceCounterBytes) : nullptr;
+    p.scratch = nullptr, p.partials = nullptr;
     const int rem = p.num_tiles % clusters;
-    if (wsp && rem > 0 && p.num_tiles > clusters && long_k && clusters <= kWorkspaceSlots &&
-        (clusters - rem) * 100 >= 15 * clusters) {
-        // Streamed tail: the whole rounds but the last run tile by tile; the remaining one to two rounds' worth of tiles is
-        // dealt out in K stages, an equal run per cluster, so the ragged round costs its share of a round instead of a
-        // whole one (816 tiles on 74 clusters: 11.03 rounds instead of 12).
-        p.dp_tiles = (p.num_tiles / clusters - 1) * clusters;
-        p.sk_units = (p.num_tiles - p.dp_tiles) * p.k_iters;
-    } else if (wsp && rem > 0 && p.num_tiles < clusters && 2 * rem <= clusters && p.k_iters >= 16) {
-        // K split: a problem with fewer tiles than clusters and a long K (few rows, few columns) is cut along K so that
-        // more SMs stream it; partial sums meet by atomic adds and the slice that arrives last runs the epilogue.
-        // Measured on B200: worth it only when every slice keeps at least eight stages.
+    if (rem > 0 && p.num_tiles < clusters && 2 * rem <= clusters && p.k_iters >= 16) {
         int splits = clusters / rem;
         if (splits > p.k_iters / 8) splits = p.k_iters / 8;
         if (splits > 16) splits = 16;
         if (splits < 1) splits = 1;
         const int kps = (p.k_iters + splits - 1) / splits;
         splits = (p.k_iters + kps - 1) / kps;
-        if (splits >= 2 && rem <= kWorkspaceSlots) {
+        int* wsp = splits >= 2 && rem <= kWorkspaceSlots ? split_workspace(dev, st, kSplitWorkspaceBytes) : nullptr;
+        if (wsp) {
+            p.scratch = wsp;
+            p.partials = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(wsp) + kWorkspaceCounterBytes);
             p.whole_tiles = p.num_tiles - rem, p.splits = splits, p.kps = kps;
             p.num_items = p.whole_tiles + rem * splits;
         }
@@ -1055,7 +956,7 @@ GPU_API int gpu_int8_gemm_noalloc(const int8_t* A, const int8_t* W, const float*
     p.ksub = K <= BK ? 1 : 2;
     p.k_iters = (int)((K + p.ksub * BK - 1) / (p.ksub * BK));
     // the width that fills the clusters best, widened while the tiles outnumber the array's 16 slots
-    int bn = choose_bn(M, N, clusters, false);
+    int bn = choose_bn(M, N, clusters);
     p.tiles_m = (int)((M + 2 * BM - 1) / (2 * BM));
     while (bn < 256 && p.tiles_m * ((N + bn - 1) / bn) > kStaticMaxTiles) bn += 32;
     p.bn = bn;

@@ -418,7 +418,7 @@ int run_w6_gemm(int epi, const int8_t* A, const uint8_t* Wq6, const uint8_t* s_r
     // More than 256 rows: tiles of 512 rows x 128 columns, so that each expanded W tile serves two sets of MMAs and the
     // unpack work per MMA halves; otherwise one 256-row half and the column width that fills the clusters best.
     const int mh = M > 256 && N >= 128 ? 2 : 1;
-    const int bn = mh == 2 ? 128 : choose_bn(M, N, clusters, false);
+    const int bn = mh == 2 ? 128 : choose_bn(M, N, clusters);
     p.bn = bn;
     p.idesc = umma_idesc_i8(2 * BM, bn);
     const int stage_bytes = mh * BM * BK + (bn / 2) * (64 + 32);     // A boxes + packed planes; the expanded ring is separate

@@ -9,9 +9,9 @@
 //
 // The kernel is bound by instruction issue before HBM, so it is organised around instruction count and around keeping
 // the issue slots busy:
-//   - persistent CTAs: a CTA walks row blocks; while it computes one block, one bulk asynchronous copy per row
-//     (cp.async.bulk, completion on an mbarrier) brings the next block's rows into shared memory, so no warp ever
-//     waits for HBM with nothing else to issue (rows too long for the staging buffer are loaded directly instead)
+//   - without the rotation the kernel is short enough to wait for HBM: persistent CTAs walk row blocks and, while one
+//     block is computed, one bulk asynchronous copy per row (cp.async.bulk, completion on an mbarrier) brings the next
+//     block's rows into shared memory; with the rotation (arithmetic-bound) each CTA takes one block with direct loads
 //   - a 256-wide group belongs to 8 consecutive lanes; a lane takes 32 consecutive elements (16-byte loads)
 //   - stages 0 and 1 (index bits 0-3) run in registers on packed f32x2 pairs (element i with element i+16)
 //   - the group is transposed through a padded per-warp shared-memory buffer; a lane then holds element pairs
@@ -19,9 +19,9 @@
 //   - every butterfly adds in the reference's left-to-right order (a - b is fma(b, -1, a): one rounding, the same),
 //     so results are bit-identical whichever thread computes them
 //   - bf16 prologues of one variable (SiLU, GELU, GELU-tanh, the sigmoid of GATE) are a 65536-entry table built on
-//     the device from the very expressions of the reference; the kernel keeps the entries of 2^-14 <= |x| < 128 in
-//     shared memory (10.5 KB: a gather from the whole table through L1 cost one wavefront per distinct line, which
-//     bounded the kernel) and a thread that meets a value outside that range redoes its elements from the whole table
+//     the device from the very expressions of the reference and read through L1 (keeping the hot part, 2^-14 <= |x| < 128,
+//     in shared memory measured slower: 129 against 101 us at M = 4352, K = 12288, the index arithmetic and the bank
+//     conflicts of 32 scattered 2-byte reads cost more than the L1 gather)
 //   - the division by the scale is a multiplication by its reciprocal (exact for this purpose, see quant2), the
 //     codes are rounded by cvt.rni straight from bf16 and packed with saturation, and go back through shared memory
 //     so that each lane stores 32 contiguous bytes
@@ -82,7 +82,7 @@ struct QuantArgs {
     const void* mod_shift;
     // shared-memory plan (byte offsets from the dynamic shared memory base), filled in by launch_quant
     int staged;             // rows arrive through the staging buffer (bulk copies) instead of direct loads
-    uint32_t off_amax, off_norm, off_lut, off_stage, off_bar;
+    uint32_t off_amax, off_norm, off_stage, off_bar;
 };
 
 template <int PRO> __host__ __device__ constexpr bool is_ln() { return PRO == PRO_LAYERNORM || PRO == PRO_LN_MOD || PRO == PRO_LN_AFFINE; }
@@ -106,10 +106,6 @@ __host__ __device__ inline int norm_words(int K) { return (((K >> 8) + 3) >> 2) 
 // swapped back when they are written out.
 constexpr int kGroupWords = 304;          // team pitch inside a warp: 16 banks (mod 32) apart
 constexpr int kWarpWords = 4 * 304 + 32;  // warp pitch: a multiple of 32 words with room for the two-word shift
-
-// The part of a 65536-entry activation table kept in shared memory: bf16 bit patterns [kLutLo, kLutLo + kLutRange)
-// (2^-14 <= x < 128) and the same magnitudes with the sign bit, negative half second.
-constexpr uint32_t kLutLo = 0x3880u, kLutRange = 21u * 128u;
 
 __device__ __forceinline__ int tpad(int e) { return e + ((e >> 5) << 2); }
 
@@ -145,15 +141,6 @@ template <typename T, bool SMEM> __device__ __forceinline__ void load32(const T*
 __device__ __forceinline__ float lut_f(const uint16_t* lut, float x) {   // x holds a bf16 value; whole table, global
     return __uint_as_float((uint32_t)__ldg(lut + (__float_as_uint(x) >> 16)) << 16);
 }
-// The same from the shared-memory part; a value outside it leaves x unchanged and raises `miss`.
-__device__ __forceinline__ float lut_s(const uint16_t* lut_sm, float x, bool& miss) {
-    const uint32_t e = (__float_as_uint(x) >> 16) - kLutLo;
-    const uint32_t m = e & 0x7fffu;
-    const bool in = m < kLutRange;
-    miss |= !in;
-    return in ? __uint_as_float((uint32_t)lut_sm[m + ((e >> 15) & 1u) * kLutRange] << 16) : x;
-}
-
 // Radix-4 butterfly of the regular Hadamard block on packed pairs; outputs in the reference's association:
 //   r0 = .5*(((x0+x1)+x2)-x3)  r1 = .5*(((x0+x1)-x2)+x3)  r2 = .5*(((x0-x1)+x2)+x3)  r3 = .5*(((-x0+x1)+x2)+x3)
 __device__ __forceinline__ void h4x2(float2& x0, float2& x1, float2& x2, float2& x3) {
@@ -188,8 +175,8 @@ __device__ __forceinline__ float max3_abs_nan(float a, float b, float c) {
 // So the exact quotient differs from every boundary by at least 1 / (S M) > 2^-17 relative, while a (correctly rounded)
 // reciprocal times a is within 2^-23 of it: both round to the same bf16, and no correction step is needed
 // (tests/test_quant_division.py enumerates every pair of significands).
-// cvt.rni + saturating pack equal clamp(rint(.)) except for NaN (0 instead of -128) and the caller keeps rows that
-// hold a NaN or an infinity off this path.
+// The magic-number rint + saturating pack equal clamp(rint(.)) for finite values; the caller keeps rows that hold a NaN
+// or an infinity off this path.
 template <typename T>
 __device__ __forceinline__ uint32_t quant2(float2 v, float st, float rcp, bool fast) {
     if (sizeof(T) == 2 && fast) {
@@ -198,14 +185,15 @@ __device__ __forceinline__ uint32_t quant2(float2 v, float st, float rcp, bool f
         const float2 a = make_float2(__uint_as_float(au << 16), __uint_as_float(au & 0xffff0000u));
         const float2 t = __fmul2_rn(a, make_float2(rcp, rcp));
         const __nv_bfloat162 tb = __floats2bfloat162_rn(t.x, t.y);
+        const uint32_t tu = *reinterpret_cast<const uint32_t*>(&tb);
+        // rint by adding 1.5 * 2^23 (round to nearest even at unit spacing, |t| <= 128): the integer sits in the low bits.
+        // The float -> integer conversion instructions share a narrow pipe with the bf16 conversions above, and that
+        // pipe, not HBM, bounded this kernel; the addition runs on the FP32 pipe instead.
+        const float2 u = __fadd2_rn(make_float2(__uint_as_float(tu << 16), __uint_as_float(tu & 0xffff0000u)),
+                                    make_float2(12582912.f, 12582912.f));
+        const int n0 = (int)__float_as_uint(u.x) - 0x4B400000, n1 = (int)__float_as_uint(u.y) - 0x4B400000;
         uint32_t packed;
-        asm("{\n\t.reg .b16 lo, hi;\n\t.reg .s32 a, b;\n\t"
-            "mov.b32 {lo, hi}, %1;\n\t"
-            "cvt.rni.s32.bf16 a, lo;\n\t"
-            "cvt.rni.s32.bf16 b, hi;\n\t"
-            "cvt.pack.sat.s8.s32.b32 %0, b, a, 0;\n\t}"
-            : "=r"(packed)
-            : "r"(*reinterpret_cast<const uint32_t*>(&tb)));
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(packed) : "r"(n1), "r"(n0));
         return packed;   // byte 0 = code of v.x, byte 1 = code of v.y
     }
     const int qx = clamp_rint_i8(rnd<T>(__fdiv_rn(rnd<T>(v.x), st)), -128.f);
@@ -264,19 +252,12 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 384 ? 2 : 1) quant_rows_kernel(c
     float* tbuf_w = tbuf - 2 * (team >> 1);            // where its transposition writes and reads start (two words later for teams 2, 3)
     unsigned* amax_s = reinterpret_cast<unsigned*>(smem + p.off_amax);   // [3][rows]
     float* norm_s = reinterpret_cast<float*>(smem + p.off_norm);         // [rows][norm_words(K)], normalising prologues only
-    const uint16_t* lut_sm = reinterpret_cast<const uint16_t*>(smem + p.off_lut);
     const bool use_lut = sizeof(T) == 2 && p.lut >= 0;
     const uint32_t bar = smem_u32(smem + p.off_bar);
     uint8_t* stage = smem + p.off_stage;              // [x rows | aux rows], one block of rows
     const uint32_t row_bytes = (uint32_t)p.K * sizeof(T);
 
     for (int i = threadIdx.x; i < 3 * p.rows_per_cta; i += blockDim.x) amax_s[i] = 0u;
-    if (use_lut) {
-        // the shared-memory part of the table: positive half, then negative half
-        uint16_t* dst = reinterpret_cast<uint16_t*>(smem + p.off_lut);
-        for (uint32_t i = threadIdx.x; i < 2 * kLutRange; i += blockDim.x)
-            dst[i] = lut[(i < kLutRange ? kLutLo + i : 0x8000u + kLutLo + (i - kLutRange))];
-    }
     if (p.staged && threadIdx.x == 0) {
         mbar_init(bar, 1);
         fence_mbar_init();
@@ -346,16 +327,7 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 384 ? 2 : 1) quant_rows_kernel(c
             float* a = PRO == PRO_GATE ? u : v;
             if (use_lut) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    float keep[8];
-                    bool miss = false;
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) keep[j] = a[8 * c + j], a[8 * c + j] = lut_s(lut_sm, keep[j], miss);
-                    if (miss) {                        // a value outside the shared-memory part: the whole table serves these eight
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) a[8 * c + j] = lut_f(lut, keep[j]);
-                    }
-                }
+                for (int i = 0; i < 32; ++i) a[i] = lut_f(lut, a[i]);
             } else {
 #pragma unroll
                 for (int i = 0; i < 32; ++i)
@@ -529,8 +501,13 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 384 ? 2 : 1) quant_rows_kernel(c
         const bool fast = sizeof(T) == 2 && amax <= FLT_MAX && !has_nan;
         const float rcp = fast ? __frcp_rn(st) : 0.f;
         uint32_t c16[16];
+        if (fast) {      // one branch for the row, not one per pair
 #pragma unroll
-        for (int i = 0; i < 16; ++i) c16[i] = quant2<T>(P[i], st, rcp, fast);
+            for (int i = 0; i < 16; ++i) c16[i] = quant2<T>(P[i], st, rcp, true);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) c16[i] = quant2<T>(P[i], st, rcp, false);
+        }
         int8_t* q = p.q + m * (int64_t)p.K + col;
         if (p.rotate) {
             // codes of (2 t8, 2 t8 + 1) + 16 r back through the group's buffer, so each lane stores 32 contiguous bytes
@@ -701,6 +678,7 @@ int launch_cfg(QuantArgs& p, int threads, size_t smem, bool persistent, cudaStre
 
 constexpr size_t kMaxSmem = 227 * 1024;
 
+
 template <typename T, int PRO>
 int launch_quant(QuantArgs& p, cudaStream_t st) {
     p.tpr = p.K / 32;
@@ -721,9 +699,9 @@ int launch_quant(QuantArgs& p, cudaStream_t st) {
         if (int rc = ensure_lut(lut, st)) return rc;
     }
     p.lut = lut;
-    // CTA shape: whole rows, up to 384 threads, at least one warp; any multiple of 8 threads up to 1024 works (the
+    // CTA shape: whole rows, about 256 threads, at least one warp; any multiple of 8 threads up to 1024 works (the
     // last warp may be partial), so every K the reference accepts is served
-    int rows = 384 / p.tpr;
+    int rows = 256 / p.tpr;
     if (rows < 1) rows = 1;
     if (rows * p.tpr < 32) rows = (32 + p.tpr - 1) / p.tpr;
     p.rows_per_cta = rows;
@@ -734,15 +712,15 @@ int launch_quant(QuantArgs& p, cudaStream_t st) {
     p.off_amax = (uint32_t)off, off += (size_t)3 * rows * 4;
     p.off_norm = (uint32_t)off, off += is_norm<PRO>() ? (size_t)rows * norm_words(p.K) * 4 : 0;
     off = up(off, 16);
-    p.off_lut = (uint32_t)off, off += lut >= 0 ? (size_t)2 * kLutRange * 2 : 0;
     off = up(off, 8);
     p.off_bar = (uint32_t)off, off += 8;
     off = up(off, 128);
     p.off_stage = (uint32_t)off;
     const size_t stage_bytes = (size_t)rows * p.K * sizeof(T) * (has_aux<PRO>() ? 2 : 1);
-    // staged (persistent CTAs with the next block's rows in flight) when the buffer fits; otherwise one block per CTA
-    // with direct loads
-    p.staged = off + stage_bytes <= kMaxSmem;
+    // Measured on B200 (M = 4352, K = 12288, bf16): without the rotation, persistent CTAs with the next block's rows in
+    // flight through the staging buffer win (49 against 54 us); with it the kernel is bound by its arithmetic and the
+    // transposition, not by waiting for HBM, and one block per CTA with direct loads is as fast or faster (74 against 78).
+    p.staged = !p.rotate && !is_norm<PRO>() && off + stage_bytes <= kMaxSmem;
     const size_t smem = p.staged ? off + stage_bytes : off;
     if (smem > kMaxSmem) return -2;
     if (threads > 512) return launch_cfg<T, PRO, 1024>(p, threads, smem, p.staged != 0, st);

@@ -263,10 +263,9 @@ def test_two_pass_quantizer_and_epilogue_only(pkg, oracle, dev):
 
 
 @pytest.mark.parametrize("M,N,K", [(2304, 2560, 1024), (4352, 4608, 2048), (2100, 9000, 1280), (5000, 3100, 3072)])
-def test_streamed_tail(pkg, oracle, dev, M, N, K):
-    """More tiles than clusters and a ragged last round: the last rounds' tiles are dealt out in K stages, tiles that
-    straddle two clusters meet through global scratch. Accumulators and outputs equal the oracle's, twice in a row (the
-    first launch must leave the scratch at zero), then a K-split problem shares the same scratch."""
+def test_many_rounds_with_a_ragged_last_one(pkg, oracle, dev, M, N, K):
+    """More tiles than clusters, a last round that is only partly filled, ragged M and N: accumulators and every output
+    form equal the oracle's, twice in a row, and a K-split problem (which uses the global scratch) runs right after."""
     g, A, W, xs, ws = _operands(M, N, K, 91)
     bias = (torch.randn(N, generator=g) * 0.5).bfloat16()
     rr = torch.randn(M, N, generator=g).bfloat16()
