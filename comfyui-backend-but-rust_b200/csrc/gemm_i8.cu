@@ -861,6 +861,15 @@ GPU_API int gpu_w6a8_gemm_residual(const int8_t* A, const uint8_t* Wq6, const ui
                                    int64_t M, int64_t N, int64_t K, int G, int out_dt, void* stream) {
     return run_w6_gemm(EPI_RESID, A, Wq6, s_rel, xs, ws, bias, rscale, resid, D, M, N, K, G, out_dt, (cudaStream_t)stream);
 }
+// The same with the activation the next quantizer's prologue would apply (the FFN-up linear of the W6A8 video DiT):
+// D = out(act(out(acc * xs * ws + bias))), act as in gpu_int8_gemm_act.
+GPU_API int gpu_w6a8_gemm_act(const int8_t* A, const uint8_t* Wq6, const uint8_t* s_rel, const float* xs, const float* ws,
+                              const void* bias, void* D, int64_t M, int64_t N, int64_t K, int G, int out_dt, int act,
+                              void* stream) {
+    if (act == ACT_NONE) return gpu_w6a8_gemm(A, Wq6, s_rel, xs, ws, bias, D, M, N, K, G, out_dt, stream);
+    if (act < 0 || act > 3) return -204;
+    return run_w6_gemm(EPI_ACT, A, Wq6, s_rel, xs, ws, bias, nullptr, nullptr, D, M, N, K, G, out_dt, (cudaStream_t)stream, act);
+}
 // For tests: the raw int32 accumulators of the fused-unpack GEMM.
 GPU_API int gpu_w6a8_gemm_acc_i32(const int8_t* A, const uint8_t* Wq6, const uint8_t* s_rel, int32_t* D, int64_t M,
                                   int64_t N, int64_t K, int G, void* stream) {

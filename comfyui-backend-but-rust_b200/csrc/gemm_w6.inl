@@ -395,7 +395,7 @@ int launch_w6(const CUtensorMap& ta, const CUtensorMap& tlo, const CUtensorMap& 
 
 int run_w6_gemm(int epi, const int8_t* A, const uint8_t* Wq6, const uint8_t* s_rel, const float* xs, const float* ws,
                 const void* bias, const void* rscale, const void* resid, void* D, int64_t M, int64_t N, int64_t K, int G,
-                int out_dt, cudaStream_t st) {
+                int out_dt, cudaStream_t st, int act = 0) {
     if (M == 0 || N == 0) return 0;
     if (G != 32) return -206;                                  // the fused unpack is built for the reference's group size
     if (epi == EPI_RESID && (!rscale || !resid)) return -201;
@@ -409,6 +409,11 @@ int run_w6_gemm(int epi, const int8_t* A, const uint8_t* Wq6, const uint8_t* s_r
     GemmParams p{};
     p.xs = xs, p.ws = ws, p.bias = bias, p.rscale = rscale, p.resid = resid, p.D = D;
     p.M = (int)M, p.N = (int)N, p.K = (int)K;
+    p.act = act;
+    p.act_lut = nullptr;
+    if (epi == EPI_ACT && out_dt == DT_BF16 && M * N >= (1 << 20)) {
+        if (int rc = act_lut_ptr(act, st, &p.act_lut)) return rc;
+    }
     const int esz = epi == EPI_ACC ? 4 : (out_dt == DT_F32 ? 4 : 2);
     auto al16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
     p.vec_ok = (N % 8 == 0) && al16(D) && al16(ws) && al16(bias) && al16(rscale) && al16(resid);
@@ -444,6 +449,7 @@ int run_w6_gemm(int epi, const int8_t* A, const uint8_t* Wq6, const uint8_t* s_r
     if (epi == EPI_ACC) return launch_w6<float, EPI_ACC>(ta, tlo, thi, td, p, x6, mh, grid, st);
 #define W6_DISPATCH(T)                                                                                   \
     (epi == EPI_RESID ? launch_w6<T, EPI_RESID>(ta, tlo, thi, td, p, x6, mh, grid, st)                      \
+     : epi == EPI_ACT ? launch_w6<T, EPI_ACT>(ta, tlo, thi, td, p, x6, mh, grid, st)                        \
                       : launch_w6<T, EPI_PLAIN>(ta, tlo, thi, td, p, x6, mh, grid, st))
     if (out_dt == DT_F32) return W6_DISPATCH(float);
     if (out_dt == DT_F16) return W6_DISPATCH(half);

@@ -38,6 +38,7 @@ SIGNATURES = {
     "gpu_int8_gemm_acc_i32": [P, P, P, i64, i64, i64, P],
     "gpu_w6a8_gemm": [P, P, P, P, P, P, P, i64, i64, i64, i32, i32, P],
     "gpu_w6a8_gemm_residual": [P, P, P, P, P, P, P, P, P, i64, i64, i64, i32, i32, P],
+    "gpu_w6a8_gemm_act": [P, P, P, P, P, P, P, i64, i64, i64, i32, i32, i32, P],
     "gpu_w6a8_gemm_acc_i32": [P, P, P, P, i64, i64, i64, i32, P],
     "gpu_quant_rows_amax": [i32, i32, P, i64, P, i64, i64, P, i32, i32, i32, P],
     "gpu_quant_rows_scaled": [i32, i32, P, i64, P, i64, i64, P, P, P, i32, i32, i32, P],

@@ -234,9 +234,10 @@ def int8_gemm_acc_i32(A, W):
     return D
 
 
-def w6a8_gemm(A, packed, s_rel, xs, s_channel, bias=None, *, out_dtype=torch.bfloat16, rscale=None, resid=None, out=None,
-              G: int = 32):
-    """gpu_w6a8_gemm / gpu_w6a8_gemm_residual: the W6A8 linear from the packed weight [N, 3K/4] and e4m3 scales [N, K/G]."""
+def w6a8_gemm(A, packed, s_rel, xs, s_channel, bias=None, *, out_dtype=torch.bfloat16, act: int = 0, rscale=None, resid=None,
+              out=None, G: int = 32):
+    """gpu_w6a8_gemm / gpu_w6a8_gemm_act / gpu_w6a8_gemm_residual: the W6A8 linear from the packed weight [N, 3K/4] and
+    e4m3 scales [N, K/G]."""
     _cuda(A)
     M, K = A.shape
     N = packed.shape[0]
@@ -245,6 +246,9 @@ def w6a8_gemm(A, packed, s_rel, xs, s_channel, bias=None, *, out_dtype=torch.bfl
     if resid is not None:
         ok(lib.gpu_w6a8_gemm_residual(_ptr(A), _ptr(packed), _ptr(s_rel), _ptr(xs), _ptr(s_channel), _ptr(bias), _ptr(rscale),
                                       _ptr(resid), _ptr(D), M, N, K, G, _DT[D.dtype], _stream()), "gpu_w6a8_gemm_residual")
+    elif act:
+        ok(lib.gpu_w6a8_gemm_act(_ptr(A), _ptr(packed), _ptr(s_rel), _ptr(xs), _ptr(s_channel), _ptr(bias), _ptr(D), M, N, K, G,
+                                 _DT[D.dtype], act, _stream()), "gpu_w6a8_gemm_act")
     else:
         ok(lib.gpu_w6a8_gemm(_ptr(A), _ptr(packed), _ptr(s_rel), _ptr(xs), _ptr(s_channel), _ptr(bias), _ptr(D), M, N, K, G,
                              _DT[D.dtype], _stream()), "gpu_w6a8_gemm")

@@ -113,12 +113,16 @@ int gpu_int8_gemm_acc_i32(const int8_t* A, const int8_t* W, int32_t* D, int64_t 
  * Wq6 [N, 3K/4] (nibble plane, then 2-bit plane) and the e4m3 group scales s_rel [N, K/G] and expand them in shared
  * memory on the way to the tensor cores. Results equal gpu_w6_decode followed by gpu_int8_gemm[_residual] bit for bit;
  * ws is the per-output-channel scale (s_channel). K % 128 == 0, Wq6 16-byte and s_rel 4-byte aligned (-202), G == 32
- * (-206). gpu_w6a8_gemm_acc_i32 (for tests) returns the raw int32 accumulators. */
+ * (-206). gpu_w6a8_gemm_act applies the activation of gpu_int8_gemm_act to the rounded output (the FFN-up linear with
+ * GELU of the W6A8 video DiT; act 1 gelu-tanh, 2 silu, 3 gelu-erf, -204 otherwise). gpu_w6a8_gemm_acc_i32 (for tests)
+ * returns the raw int32 accumulators. */
 int gpu_w6a8_gemm(const int8_t* A, const uint8_t* Wq6, const uint8_t* s_rel, const float* xs, const float* ws,
                   const void* bias, void* D, int64_t M, int64_t N, int64_t K, int G, int out_dt, void* stream);
 int gpu_w6a8_gemm_residual(const int8_t* A, const uint8_t* Wq6, const uint8_t* s_rel, const float* xs, const float* ws,
                            const void* bias, const void* rscale, const void* resid, void* D, int64_t M, int64_t N,
                            int64_t K, int G, int out_dt, void* stream);
+int gpu_w6a8_gemm_act(const int8_t* A, const uint8_t* Wq6, const uint8_t* s_rel, const float* xs, const float* ws,
+                      const void* bias, void* D, int64_t M, int64_t N, int64_t K, int G, int out_dt, int act, void* stream);
 int gpu_w6a8_gemm_acc_i32(const int8_t* A, const uint8_t* Wq6, const uint8_t* s_rel, int32_t* D, int64_t M, int64_t N,
                           int64_t K, int G, void* stream);
 

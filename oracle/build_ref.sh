@@ -11,10 +11,11 @@
 # csrc/gemm.cu is not built (it pulls cuBLASLt and conv templates); its two int8 wrappers only forward to
 # launch_cutlass_int8_dequant[_residual] (gemm.cu:123-140), which the tests call directly.
 #
-# Usage: oracle/build_ref.sh [REFERENCE_ROOT]     (or the REFERENCE_ROOT variable; skipped when the tree is absent)
+# Usage: oracle/build_ref.sh [REFERENCE_ROOT]     (or the REFERENCE_ROOT variable, or a checkout named "reference" beside
+# this repository; skipped when the tree is absent)
 set -euo pipefail
-REF="${1:-${REFERENCE_ROOT:-/root/reference}}"
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
+REF="${1:-${REFERENCE_ROOT:-$(dirname "$(dirname "$HERE")")/reference}}"
 OUT="$HERE/_ref"
 if [ ! -d "$REF/csrc" ]; then echo "build_ref: no reference tree at $REF; nothing built"; exit 0; fi
 CUTLASS_INC="$(python - <<'PY'

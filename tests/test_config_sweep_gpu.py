@@ -128,6 +128,8 @@ def test_linear_bit_exact_against_the_reference_kernels(pkg, ref, dev, index):
         q2r, s2r = ref.quant_rows(y_ref, 11, 1 if sp.rotate else 0)
         assert_bits_equal(s2, s2r, "scales after the GELU epilogue")
         assert_bits_equal(q2, q2r, "codes after the GELU epilogue")
+        if sp.weight_format == "w6":
+            assert_bits_equal(L.w6a8_gemm(a8, packed, s_rel, xs, ws, bias, out_dtype=dt, act=1), ya, "W6A8 GEMM with the GELU epilogue")
         q3, s3 = L.quant_rows(y, 11, 1 if sp.rotate else 0)                                    # and the prologue form itself
         assert_bits_equal(q3, q2r, "codes of the GELU-tanh prologue")
         assert_bits_equal(s3, s2r, "scales of the GELU-tanh prologue")

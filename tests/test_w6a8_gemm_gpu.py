@@ -91,6 +91,28 @@ def test_full_size_layer_matches_decode_then_gemm(pkg, dev):
     assert L.kernel_status() == 0
 
 
+@pytest.mark.parametrize("act", [1, 2, 3])
+@pytest.mark.parametrize("M", [96, 1300])
+def test_activation_epilogue_equals_the_int8_form(pkg, dev, act, M):
+    """gpu_w6a8_gemm_act == gpu_w6_decode + gpu_int8_gemm_act, bit for bit, below and above the output size from which
+    the activation comes from the table (1300 x 1024 outputs) and in both tile forms (up to / above 256 rows)."""
+    from importlib import import_module
+    wl = import_module(pkg.__name__ + ".workloads")
+    N, K = 1024, 768
+    g = torch.Generator().manual_seed(40 + act)
+    packed, s_rel, s_channel = (t.to(dev) for t in wl.w6_pack(torch.randn(N, K, generator=g) * 0.02, True))
+    A = torch.randint(-128, 128, (M, K), generator=g, dtype=torch.int8).to(dev)
+    xs = (torch.rand(M, generator=g) * 0.02 + 1e-3).to(dev)
+    bias = (torch.randn(N, generator=g) * 0.5).bfloat16().to(dev)
+    L = pkg.linear
+    got = L.w6a8_gemm(A, packed, s_rel, xs, s_channel, bias, act=act)
+    want = L.int8_gemm(A, L.w6_decode(packed, s_rel, K), xs, s_channel, bias, act=act)
+    assert_bits_equal(got, want, f"act {act}")
+    with pytest.raises(RuntimeError, match="-204"):
+        L.w6a8_gemm(A, packed, s_rel, xs, s_channel, bias, act=7)
+    assert L.kernel_status() == 0
+
+
 def test_argument_checks(pkg, dev):
     L = pkg.linear
     A = torch.zeros((8, 192), dtype=torch.int8, device=dev)
