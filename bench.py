@@ -31,10 +31,14 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+CHAIN_BLOCKS = 60       # blocks between one host-to-device and one device-to-host copy in the chained end-to-end leg
+SETTLE_S = 1.2          # untimed back-to-back load before the timed steps (see main)
 METRIC = "w8a8_linear_tops"
 UNIT = "TOPS"
 WORKLOAD = "convrot_int8_mmdit_mlp_pair_M4352_K3072_N12288"
 INT8_NOMINAL_TOPS = 4500.0
+# the same `config` in both arms: what is computed, not how
+CONFIG = {"workload": WORKLOAD, "step": "quant(R256) -> gemm -> gelu+quant(R256) -> gemm+residual", "tokens_per_gpu": 4352}
 
 
 # --mode kernel: one kernel of the step alone, on the step's own buffers (what profiles/ summarises)
@@ -61,6 +65,8 @@ def parse_args():
                     help="--mode kernel: the one kernel to launch --steps times (the command ncu captures are taken from)")
     ap.add_argument("--cpu-rows", type=int, default=4352, help="rows of the batch the CPU baseline computes")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-stack", action="store_true", help="skip the 60-block stack record")
+    ap.add_argument("--stack-blocks", type=int, default=60)
     return ap.parse_args()
 
 
@@ -288,14 +294,21 @@ def measured_peaks():
     return 1590.0, 1400.0, 6650.0, "fallback"
 
 
+def load_workloads():
+    """workloads.py by file path: the CPU arm needs the shapes and seeded inputs, not the CUDA library the package loads."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("cbr_b200_workloads", os.path.join(ROOT, "comfyui-backend-but-rust_b200", "workloads.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = mod            # dataclasses look their module up by name
+    spec.loader.exec_module(mod)
+    return mod
+
+
 def run_reference_cpu(args, rank):
     """The reference arm: the CPU restatement of the reference's arithmetic on the host cores, rank 0 only."""
     if rank != 0:
         return
-    from __graft_entry__ import load_package
-    load_package()
-    import importlib
-    wl = importlib.import_module("cbr_b200.workloads")
+    wl = load_workloads()
     vals, base = [], None
     for i in range(max(1, min(args.steps, 3))):       # each step is seconds of CPU work: at most three are timed
         base = cpu_baseline(wl, args.cpu_rows)
@@ -306,14 +319,21 @@ def run_reference_cpu(args, rank):
     ms = 2.0 * args.cpu_rows * (up.N * up.K + down.N * down.K) / (v * 1e12) * 1e3
     print(json.dumps({"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": len(vals),
                       "warmup": 0, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                      "dtype": "int8", "data": "synthetic", "config": {"workload": WORKLOAD, "rows_per_step": args.cpu_rows},
+                      "dtype": "int8", "data": "synthetic", "config": dict(CONFIG), "rows_per_step": args.cpu_rows,
                       "cpu_baseline": base,
                       "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
 
 
-# DRAM bytes (read + write) of one launch of the dominant kernel, from the ncu capture summarised in
-# profiles/gemm_i8_pair_mlp_up.md (same shape, full size: 100.6 MB read + 76.0 MB written).
-GEMM_UP_DRAM_BYTES_PER_LAUNCH = 176.6e6
+def profiled_dram_bytes():
+    """DRAM bytes (read + write) of one launch of the dominant kernel, from the record line of the committed ncu summary
+    profiles/gemm_i8_pair_mlp_up.md ("dram_bytes_per_launch: <read> + <write>"); None when the summary is absent."""
+    import re
+    try:
+        text = open(os.path.join(ROOT, "profiles", "gemm_i8_pair_mlp_up.md")).read()
+    except OSError:
+        return None
+    m = re.search(r"dram_bytes_per_launch:\s*([0-9.eE+]+)\s*\+\s*([0-9.eE+]+)", text)
+    return float(m.group(1)) + float(m.group(2)) if m else None
 
 
 def main():
@@ -370,22 +390,27 @@ def main():
         print(json.dumps({"kernel": args.kernel, "us_per_launch": k_ms * 1e3, "launches": args.steps,
                           "kernel_status": pkg.linear.kernel_status()}), flush=True)
         return
+    # A 1 kW part reaches its power-capped clock only after about a second of load, and a few dozen steps last milliseconds:
+    # the warm-up therefore continues, untimed, until the step has run back to back for SETTLE_S seconds, and the K timed
+    # steps follow without a pause, so that `value` is the sustained figure and the clock samples describe the same state.
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ms = time_steps(torch, blk.step, args.steps, args.warmup, barrier)
+    for _ in range(args.warmup):
+        blk.step()
+    torch.cuda.synchronize()
+    t_settle, settle_steps = time.perf_counter(), 0
+    while time.perf_counter() - t_settle < SETTLE_S:
+        for _ in range(100):
+            blk.step()
+        torch.cuda.synchronize()
+        settle_steps += 100
+    ms = time_steps(torch, blk.step, args.steps, 0, barrier)
+    tail_ms = time_steps(torch, blk.step, max(args.steps, 300), 0)        # keeps the load up while the sampler takes its last samples
     clocks = sampler.stop() if rank == 0 else None
-    if rank == 0 and (clocks.get("samples") or 0) < 3:
-        # nvidia-smi samples every 100 ms and the timed region was shorter than that: sample a second, untimed run of the
-        # same step that lasts about 1.5 s, and report its clocks and its (power-capped) step time beside the timed one
-        n_sus = max(args.steps, int(1500.0 / max(ms / args.steps, 1e-3)))
-        sus = ClockSampler(local)
-        sus.start()
-        sus_ms = time_steps(torch, blk.step, n_sus, 0)
-        clocks = sus.stop()
-        clocks["source"] = (f"{n_sus} more back-to-back steps after the timed region, which lasted only {ms:.1f} ms; "
-                            f"under that sustained load a step took {sus_ms / n_sus:.4f} ms")
-        clocks["ms_per_step_sustained"] = sus_ms / n_sus
+    if rank == 0:
+        clocks["source"] = (f"sampled over {settle_steps} untimed settling steps ({SETTLE_S} s), the {args.steps} timed steps "
+                            f"and {max(args.steps, 300)} more steps right after them ({tail_ms / max(args.steps, 300):.4f} ms per step)")
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -442,7 +467,48 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     e2e_value = blk.ops() * world * args.steps / (e2e_ms * 1e-3) / 1e12
+    # The same path as the product drives it: a chain of CHAIN_BLOCKS blocks between one copy in and one copy out
+    # (the reference uploads a step's input once and downloads once at its end, src/h3.rs:1361-1364). The blocks share
+    # this block's weights; every block still runs its four kernels on the previous block's output.
+    def chain_run(n):
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        xa, xb = torch.empty_like(blk.x), torch.empty_like(blk.out)
+        torch.cuda.synchronize()
+        t0.record()
+        for _ in range(n):
+            xa.copy_(x_host, non_blocking=True)
+            cur, nxt = xa, xb
+            for _b in range(CHAIN_BLOCKS):
+                blk.step(cur, nxt)
+                cur, nxt = nxt, cur
+            out_host.copy_(cur, non_blocking=True)
+        t1.record()
+        torch.cuda.synchronize()
+        return t0.elapsed_time(t1)
+
+    chain_run(1)
+    if barrier:
+        barrier()
+    chain_n = max(1, min(args.steps, 5))
+    chain_ms = chain_run(chain_n)
+    if world > 1:
+        t = torch.tensor([chain_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        chain_ms = float(t.item())
+    chain_value = blk.ops() * CHAIN_BLOCKS * world * chain_n / (chain_ms * 1e-3) / 1e12
     status = pkg.linear.kernel_status()
+
+    # The 60-block stack of the scaling configuration (M = 16896 tokens at 2048 x 2048, adaLN linear included) on these N
+    # GPUs: token-sharded, and under column / row tensor parallelism in both modes. Every rank takes part.
+    dit_stack = None
+    if args.impl == "ours" and not args.no_stack:
+        tp = importlib.import_module("cbr_b200.tensor_parallel")
+        dit_stack = {"workload": "mmdit_linear_stack_60blocks_M16896_hidden3072 (QKV, attention-out, MLP up/down, adaLN)",
+                     "peer_gbs_assumed": tp.PEER_GBS, "runs": []}
+        modes = ["token"] + (["tp_fast", "tp_exact"] if world > 1 and 12 % world == 0 else [])
+        for mode in modes:
+            dit_stack["runs"].append(tp.run_stack(mode, rank, world, local, blocks=args.stack_blocks, steps=2, warmup=1,
+                                                  gemm_clusters=66))
 
     if rank != 0:
         return
@@ -457,24 +523,44 @@ def main():
                 "peak": peak, "unit": "TOPS", "frac": achieved / peak,
                 "peak_source": f"2 x {src} dense bf16 burst ({bf16_burst} TFLOP/s); no int8 figure is measured on this pool",
                 "frac_of_nominal_4500": achieved / INT8_NOMINAL_TOPS, "us_per_launch": k_ms * 1e3,
-                "traffic": GEMM_UP_DRAM_BYTES_PER_LAUNCH}
+                "traffic": profiled_dram_bytes()}
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD, "step": "quant(R256) -> gemm -> gelu+quant(R256) -> gemm+residual",
-                       "tokens_per_gpu": up.M, "sharding": "tokens (replicated weights), no data-path collective",
-                       "fused_gelu_epilogue": fused, "l2": "working set per step ~300 MB exceeds the 126 MB L2"},
+            "config": dict(CONFIG),
+            "run": {"sharding": "tokens (replicated weights), no data-path collective", "fused_gelu_epilogue": fused,
+                    "l2": "working set per step ~300 MB exceeds the 126 MB L2",
+                    "settle": f"{settle_steps} untimed steps ({SETTLE_S} s) directly before the timed ones: value is the power-capped, sustained rate"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
                     "pipelining": "every step copies its own input and output; copies of neighbouring steps overlap its kernels "
-                                  "(three streams, two device buffer sets)"},
+                                  "(three streams, two device buffer sets)",
+                    "chain": {"value": chain_value, "unit": UNIT, "blocks_per_copy": CHAIN_BLOCKS, "ms_per_chain": chain_ms / chain_n,
+                              "h2d_bytes_per_chain": x_host.numel() * 2, "d2h_bytes_per_chain": out_host.numel() * 2,
+                              "what": "one copy in, 60 blocks back to back, one copy out: how the reference's engine drives the path"}},
             "gpu_launches": blk.launches_per_step * args.steps, "kernel_status": status, "roofline": roofline,
             "frac_of_nominal_int8_peak": value / world / INT8_NOMINAL_TOPS}
+    if dit_stack is not None:
+        line["dit_stack"] = dit_stack
     if args.impl == "reference-gpu":
         line["impl"] = "reference-gpu"
-    elif not args.no_cpu_baseline and world == 1:
-        line["cpu_baseline"] = cpu_baseline(wl, args.cpu_rows)
+    else:
+        # the incumbent on the same GPU: the reference's own CUDA kernels (CUTLASS 2.x mma.sync GEMM, its quantizer),
+        # compiled unmodified for sm_100a, driving the same four launches on the same buffers
+        try:
+            from oracle import ref as R
+            if R.available():
+                inc = Block(RefImpl(R), torch, dev, up, down, x, w1, w2, b1, b2, False)
+                inc_ms = time_steps(torch, inc.step, 20, 3) / 20
+                line["incumbent"] = {"impl": "reference CUDA kernels compiled for sm_100a (oracle/_ref/libref.so)", "ms_per_step": inc_ms,
+                                     "value": inc.ops() / (inc_ms * 1e-3) / 1e12, "unit": UNIT}
+            else:
+                line["incumbent"] = {"unavailable": "oracle/_ref/libref.so is not built"}
+        except Exception as e:                                   # the checker's absence must not cost the bench line
+            line["incumbent"] = {"unavailable": repr(e)[:200]}
+        if not args.no_cpu_baseline and world == 1:
+            line["cpu_baseline"] = cpu_baseline(wl, args.cpu_rows)
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -654,6 +654,9 @@ bool encode_output_tmap(CUtensorMap* tm, void* ptr, int64_t M, int64_t N, int es
                CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Upper bound on the CTA pairs a GEMM launch occupies (0 = every SM pair of the device); see gpu_int8_gemm_set_cluster_limit.
+std::atomic<int> g_cluster_limit{0};
+
 int device_sm_count(int dev) {
     static int count[64];
     static std::mutex mu;
@@ -779,7 +782,8 @@ int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const f
         SkinnyParams sp{A, W, xs, ws, bias, rscale, resid, D, (int)M, (int)N, (int)K, act};
         return launch_skinny_gemm(epi, sp, out_dt, device_sm_count(dev), st);
     }
-    const int clusters = device_sm_count(dev) / 2;
+    int clusters = device_sm_count(dev) / 2;
+    if (const int lim = g_cluster_limit.load(std::memory_order_relaxed); lim > 0 && lim < clusters) clusters = lim;
     GemmParams p{};
     p.xs = xs, p.ws = ws, p.bias = bias, p.rscale = rscale, p.resid = resid, p.D = D;
     p.M = (int)M, p.N = (int)N, p.K = (int)K;
@@ -1006,6 +1010,14 @@ GPU_API int gpu_int8_gemm_noalloc(const int8_t* A, const int8_t* W, const float*
     return launch_pair<bf16, EPI_PLAIN>(ta, tw, td, p, grid, st);
 }
 
+
+// New (tensor parallelism): the persistent GEMM normally takes every SM pair of the device, and a collective's kernels
+// launched beside it on another stream then wait for it to end. A limit of n > 0 makes gpu_int8_gemm* launches that follow
+// (any thread, any device of the process) occupy at most n CTA pairs, leaving the other SMs to concurrent kernels;
+// 0 restores the default. Returns the previous limit.
+GPU_API int gpu_int8_gemm_set_cluster_limit(int clusters) {
+    return g_cluster_limit.exchange(clusters < 0 ? 0 : clusters, std::memory_order_relaxed);
+}
 
 // Reads and clears the device status word (synchronises the device). 0 = no kernel gave up a wait.
 GPU_API int gpu_kernels_status(int* status) {

@@ -152,6 +152,69 @@ GPU_API int gpu_int8_epilogue(const int32_t* acc, const float* xs, const float* 
     return -200;
 }
 
+// ---- bias + residual over reduced partial outputs ------------------------------------------------------------------
+// The tail of a row-parallel linear whose dequantized partial outputs were summed across devices (fast tensor-parallel
+// mode): out[m, n0 + n] = T(T(y[m, n] + bias[n0 + n]) + resid[m, n0 + n]) for a column block [n0, n0 + Nc) of the
+// output, y contiguous [M, Nc], resid and out with row pitch ld. 8 elements per thread, 16-byte accesses.
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(256) bias_residual_kernel(const T* __restrict__ y, const T* __restrict__ bias, const T* resid,
+                                                            T* out, int64_t M, int Nc, int64_t ld, int n0) {
+    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (i >= M * Nc) return;
+    const int64_t m = i / Nc;
+    const int n = (int)(i - m * Nc);
+    float a[8], b[8], r[8];
+    if constexpr (sizeof(T) == 2) {
+        const uint4 ya = *reinterpret_cast<const uint4*>(y + i);
+        const T* yh = reinterpret_cast<const T*>(&ya);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[e] = to_f<T>(yh[e]);
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[e] = to_f<T>(y[i + e]);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        b[e] = bias ? to_f<T>(bias[n0 + n + e]) : 0.f;
+        r[e] = resid ? to_f<T>(resid[m * ld + n0 + n + e]) : 0.f;
+    }
+    T o[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        float v = bias ? rnd<T>(__fadd_rn(a[e], b[e])) : a[e];
+        if (resid) v = __fadd_rn(v, r[e]);
+        o[e] = from_f<T>(v);
+    }
+    T* dst = out + m * ld + n0 + n;
+    if constexpr (sizeof(T) == 2) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
+    else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dst[e] = o[e];
+    }
+}
+
+}  // namespace
+
+// New (tensor parallelism; the reference is single-device): out[:, n0:n0+Nc] = y + bias[n0:n0+Nc] + resid[:, n0:n0+Nc].
+// y [M, Nc] contiguous in the activation dtype; bias [>= n0 + Nc] and resid [M, ld] nullable; out [M, ld] may alias resid.
+// Nc, n0 and ld multiples of 8, pointers 16-byte aligned (-202).
+GPU_API int gpu_bias_residual_add(const void* y, const void* bias, const void* resid, void* out, int64_t M, int64_t Nc,
+                                  int64_t ld, int64_t n0, int dt, void* stream) {
+    if (M <= 0 || Nc <= 0) return 0;
+    if ((Nc | ld | n0) & 7 || (((uintptr_t)y | (uintptr_t)bias | (uintptr_t)resid | (uintptr_t)out) & 15)) return -202;
+    if (Nc > INT32_MAX || n0 > INT32_MAX) return -200;
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned grid = (unsigned)((M * Nc / 8 + 255) / 256);
+    if (dt == DT_F32) bias_residual_kernel<float><<<grid, 256, 0, st>>>((const float*)y, (const float*)bias, (const float*)resid, (float*)out, M, (int)Nc, ld, (int)n0);
+    else if (dt == DT_F16) bias_residual_kernel<half><<<grid, 256, 0, st>>>((const half*)y, (const half*)bias, (const half*)resid, (half*)out, M, (int)Nc, ld, (int)n0);
+    else if (dt == DT_BF16) bias_residual_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)y, (const bf16*)bias, (const bf16*)resid, (bf16*)out, M, (int)Nc, ld, (int)n0);
+    else return -200;
+    KCHECK();
+    return 0;
+}
+
 // ---- K not a multiple of 16 ----------------------------------------------------------------------------------
 // The tensor-core kernel stages its operands with TMA, which needs a 16-byte row pitch. The reference serves rows whose
 // K is only a multiple of 8 with narrower-aligned tile configurations (csrc/vendor/cutlass_gemm_int8.cu:190-191,

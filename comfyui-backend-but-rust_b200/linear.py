@@ -61,25 +61,26 @@ def quant_rows(x: torch.Tensor, prologue: int = ffi.PRO_PLAIN, rotate: int = 0, 
 
 
 def quant_rows_amax(x: torch.Tensor, prologue: int = ffi.PRO_PLAIN, rotate: int = 0, *, K: Optional[int] = None,
-                    g: Optional[torch.Tensor] = None, up_offset: int = 0) -> torch.Tensor:
+                    g: Optional[torch.Tensor] = None, up_offset: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """gpu_quant_rows_amax: row maxima after prologue and rotation, f32 [M]."""
     _cuda(x)
     M = x.shape[0]
     K = K if K is not None else x.shape[1]
-    amax = torch.empty((M,), dtype=torch.float32, device=x.device)
+    amax = out if out is not None else torch.empty((M,), dtype=torch.float32, device=x.device)
     ok(_lib().gpu_quant_rows_amax(_DT[x.dtype], prologue, _ptr(x), x.stride(0), _ptr(g), g.stride(0) if g is not None else 0,
                                   up_offset, _ptr(amax), M, K, rotate, _stream()), "gpu_quant_rows_amax")
     return amax
 
 
 def quant_rows_scaled(x: torch.Tensor, amax: torch.Tensor, prologue: int = ffi.PRO_PLAIN, rotate: int = 0, *,
-                      K: Optional[int] = None, g: Optional[torch.Tensor] = None, up_offset: int = 0):
+                      K: Optional[int] = None, g: Optional[torch.Tensor] = None, up_offset: int = 0,
+                      q: Optional[torch.Tensor] = None, scales: Optional[torch.Tensor] = None):
     """gpu_quant_rows_scaled: quantize with given row maxima -> (q int8 [M, K], scales f32 [M])."""
     _cuda(x)
     M = x.shape[0]
     K = K if K is not None else x.shape[1]
-    q = torch.empty((M, K), dtype=torch.int8, device=x.device)
-    scales = torch.empty((M,), dtype=torch.float32, device=x.device)
+    q = q if q is not None else torch.empty((M, K), dtype=torch.int8, device=x.device)
+    scales = scales if scales is not None else torch.empty((M,), dtype=torch.float32, device=x.device)
     ok(_lib().gpu_quant_rows_scaled(_DT[x.dtype], prologue, _ptr(x), x.stride(0), _ptr(g),
                                     g.stride(0) if g is not None else 0, up_offset, _ptr(amax), _ptr(q), _ptr(scales), M, K,
                                     rotate, _stream()), "gpu_quant_rows_scaled")
@@ -93,6 +94,21 @@ def int8_epilogue(acc, xs, ws, bias=None, *, out_dtype=torch.bfloat16, act: int 
     ok(_lib().gpu_int8_epilogue(_ptr(acc), _ptr(xs), _ptr(ws), _ptr(bias), _ptr(rscale), _ptr(resid), _ptr(D), M, N,
                                 _DT[D.dtype], act, _stream()), "gpu_int8_epilogue")
     return D
+
+
+def bias_residual_add(y, bias=None, resid=None, *, out=None, n0: int = 0):
+    """gpu_bias_residual_add: out[:, n0:n0+Nc] = y + bias[n0:n0+Nc] + resid[:, n0:n0+Nc]; y [M, Nc] contiguous, resid / out
+    [M, ld] (out defaults to a new [M, Nc] tensor when neither is given a wider one)."""
+    M, Nc = y.shape
+    D = out if out is not None else torch.empty((M, Nc), dtype=y.dtype, device=y.device)
+    ok(_lib().gpu_bias_residual_add(_ptr(y), _ptr(bias), _ptr(resid), _ptr(D), M, Nc, D.stride(0), n0, _DT[y.dtype], _stream()),
+       "gpu_bias_residual_add")
+    return D
+
+
+def set_gemm_cluster_limit(clusters: int) -> int:
+    """gpu_int8_gemm_set_cluster_limit: GEMM launches that follow occupy at most this many CTA pairs (0 = all)."""
+    return _lib().gpu_int8_gemm_set_cluster_limit(clusters)
 
 
 def rotate_rows_f32(x: torch.Tensor, prologue: int = ffi.PRO_PLAIN, *, K: Optional[int] = None, up_offset: int = 0,
@@ -226,10 +242,10 @@ def int8_gemm(A, W, xs, ws, bias=None, *, out_dtype=torch.bfloat16, act: int = 0
     return D
 
 
-def int8_gemm_acc_i32(A, W):
+def int8_gemm_acc_i32(A, W, out=None):
     M, K = A.shape
     N = W.shape[0]
-    D = torch.empty((M, N), dtype=torch.int32, device=A.device)
+    D = out if out is not None else torch.empty((M, N), dtype=torch.int32, device=A.device)
     ok(_lib().gpu_int8_gemm_acc_i32(_ptr(A), _ptr(W), _ptr(D), M, N, K, _stream()), "gpu_int8_gemm_acc_i32")
     return D
 

@@ -42,23 +42,25 @@ class Comm:
         self.world = self.dist.get_world_size(group) if self.dist else 1
         self.rank = self.dist.get_rank(group) if self.dist else 0
 
-    def all_gather_rows(self, t: torch.Tensor) -> torch.Tensor:
+    def all_gather_rows(self, t: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         if self.world == 1:
             return t
-        out = torch.empty((t.shape[0] * self.world,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
-        self.dist.all_gather_into_tensor(out, t.contiguous(), group=self.group)
+        if out is None:
+            out = torch.empty((t.shape[0] * self.world,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        self.dist.all_gather_into_tensor(out, t, group=self.group)
         return out
 
-    def reduce_scatter_rows(self, t: torch.Tensor) -> torch.Tensor:
+    def reduce_scatter_rows(self, t: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         if self.world == 1:
             return t
-        out = torch.empty((t.shape[0] // self.world,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
         if t.device.type == "cpu":   # gloo has no reduce-scatter (nor bf16 sums): all-reduce and keep this rank's rows
             full = t.float() if t.dtype == torch.bfloat16 else t.clone()
             self.dist.all_reduce(full, group=self.group)
             rows = t.shape[0] // self.world
             return full[self.rank * rows:(self.rank + 1) * rows].to(t.dtype).contiguous()
-        self.dist.reduce_scatter_tensor(out, t.contiguous(), group=self.group)
+        if out is None:
+            out = torch.empty((t.shape[0] // self.world,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        self.dist.reduce_scatter_tensor(out, t, group=self.group)
         return out
 
     def all_reduce_max(self, t: torch.Tensor) -> torch.Tensor:
@@ -102,64 +104,159 @@ def shard_pair(w1q, s1, b1, w2q, s2, b2, rank: int, world: int, hidden_of=None) 
 
 
 class TPPair:
-    """One (column-parallel, row-parallel) pair with a residual around it: out = x + W2 act(W1 x)."""
+    """One (column-parallel, row-parallel) pair with a residual around it: out = x + W2 act(W1 x).
+
+    Every step is one of the library's kernels or a collective: no eager tensor arithmetic, no copies (the V part of a
+    QKV output is read in place through its row stride), and on CUDA every intermediate lives in buffers allocated once
+    (`bufs`, shared by the pairs of a stack), so that a pass allocates nothing and can be captured in a CUDA graph.
+
+    `chunks` > 1 (fast mode, CUDA): the row-parallel GEMM runs as that many column blocks of the output; the
+    reduce-scatter of block i runs on `comm_stream` while the GEMM of block i + 1 runs on the compute stream (the caller
+    limits the GEMM's share of the SMs with gpu_int8_gemm_set_cluster_limit so that the collective's kernels find room)."""
 
     def __init__(self, ops, comm: Comm, weights: PairWeights, *, rotate: int = 1, act_prologue: int = PRO_PLAIN,
-                 hidden_cols: Optional[slice] = None, exact: bool = False):
+                 hidden_cols: Optional[slice] = None, exact: bool = False, bufs: Optional[dict] = None, chunks: int = 1,
+                 comm_stream=None):
         self.ops, self.comm, self.w = ops, comm, weights
         self.rotate, self.pro, self.hidden_cols, self.exact = rotate, act_prologue, hidden_cols, exact
+        self.bufs = bufs if bufs is not None else {}
+        self.chunks, self.comm_stream = chunks, comm_stream
         self.ones = None
 
-    def forward(self, x_local: torch.Tensor) -> torch.Tensor:
+    def _buf(self, name, shape, dtype, like):
+        """A persistent buffer on CUDA (keyed by name and shape, shared across pairs); None on CPU (the stand-in allocates)."""
+        if like.device.type != "cuda":
+            return None
+        key = (name, tuple(shape), dtype)
+        t = self.bufs.get(key)
+        if t is None:
+            t = self.bufs[key] = torch.empty(tuple(shape), dtype=dtype, device=like.device)
+        return t
+
+    def forward(self, x_local: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         ops, comm, w = self.ops, self.comm, self.w
-        a8, xs = ops.quant_rows(x_local, PRO_PLAIN, self.rotate)
-        a8, xs = comm.all_gather_rows(a8), comm.all_gather_rows(xs)
-        h = ops.int8_gemm(a8, w.w1, xs, w.s1, w.b1, out_dtype=x_local.dtype)             # [M, N1 / P]
+        rows, F = x_local.shape
+        M, dt, P = rows * comm.world, x_local.dtype, comm.world
+        kw = {}
+        if x_local.device.type == "cuda":
+            kw = dict(q=self._buf("a8_local", (rows, F), torch.int8, x_local), scales=self._buf("xs_local", (rows,), torch.float32, x_local))
+        a8, xs = ops.quant_rows(x_local, PRO_PLAIN, self.rotate, **kw)
+        a8 = comm.all_gather_rows(a8, self._buf("a8", (M, F), torch.int8, x_local) if P > 1 else None)
+        xs = comm.all_gather_rows(xs, self._buf("xs", (M,), torch.float32, x_local) if P > 1 else None)
+        n1 = w.w1.shape[0]
+        h = ops.int8_gemm(a8, w.w1, xs, w.s1, w.b1, out_dtype=dt, out=self._buf("h", (M, n1), dt, x_local))       # [M, N1 / P]
         if self.hidden_cols is not None:
-            h = h[:, self.hidden_cols].contiguous()
+            h = h[:, self.hidden_cols]            # a view: the quantizers take the row stride
+        kh, n2 = h.shape[1], w.w2.shape[0]
         if self.ones is None:
-            self.ones = torch.ones(w.w2.shape[0], dtype=x_local.dtype, device=x_local.device)
-        rows = x_local.shape[0]
+            self.ones = torch.ones(n2, dtype=dt, device=x_local.device)
+        cuda = x_local.device.type == "cuda"
+        if out is None:
+            out = self._buf("out_" + ("a" if self.hidden_cols is not None else "m"), (rows, n2), dt, x_local)
         if self.exact:
-            amax = comm.all_reduce_max(ops.quant_rows_amax(h, self.pro, self.rotate))
-            a2, xs2 = ops.quant_rows_scaled(h, amax, self.pro, self.rotate)
-            acc = comm.reduce_scatter_rows(ops.int8_gemm_acc_i32(a2, w.w2))                # int32 [M / P, N2]
-            xs2_local = xs2[comm.rank * rows:(comm.rank + 1) * rows].contiguous()
-            return ops.int8_epilogue(acc, xs2_local, w.s2, w.b2, out_dtype=x_local.dtype, rscale=self.ones, resid=x_local)
-        a2, xs2 = ops.quant_rows(h, self.pro, self.rotate)
-        part = ops.int8_gemm(a2, w.w2, xs2, w.s2, None, out_dtype=x_local.dtype)          # partial sums, all rows
-        y = comm.reduce_scatter_rows(part)
-        if w.b2 is not None:
-            y = y + w.b2
-        return y + x_local
+            amax = comm.all_reduce_max(ops.quant_rows_amax(h, self.pro, self.rotate, **(dict(out=self._buf("amax", (M,), torch.float32, x_local)) if cuda else {})))
+            qkw = dict(q=self._buf("a2", (M, kh), torch.int8, x_local), scales=self._buf("xs2", (M,), torch.float32, x_local)) if cuda else {}
+            a2, xs2 = ops.quant_rows_scaled(h, amax, self.pro, self.rotate, **qkw)
+            acc = ops.int8_gemm_acc_i32(a2, w.w2, out=self._buf("acc", (M, n2), torch.int32, x_local))
+            acc = comm.reduce_scatter_rows(acc, self._buf("acc_local", (rows, n2), torch.int32, x_local) if P > 1 else None)  # int32 [M / P, N2]
+            xs2_local = xs2[comm.rank * rows:(comm.rank + 1) * rows]
+            return ops.int8_epilogue(acc, xs2_local, w.s2, w.b2, out_dtype=dt, rscale=self.ones, resid=x_local, out=out)
+        qkw = dict(q=self._buf("a2", (M, kh), torch.int8, x_local), scales=self._buf("xs2", (M,), torch.float32, x_local)) if cuda else {}
+        a2, xs2 = ops.quant_rows(h, self.pro, self.rotate, **qkw)
+        C = self.chunks if (cuda and P > 1 and self.comm_stream is not None and n2 % (8 * self.chunks) == 0) else 1
+        if C == 1:
+            part = ops.int8_gemm(a2, w.w2, xs2, w.s2, None, out_dtype=dt, out=self._buf("part", (M, n2), dt, x_local))   # partial sums, all rows
+            y = comm.reduce_scatter_rows(part, self._buf("y", (rows, n2), dt, x_local) if P > 1 else None)
+            return ops.bias_residual_add(y, w.b2, x_local, out=out)
+        # column blocks of the row-parallel GEMM, each reduce-scattered on the communication stream while the next one runs
+        nc = n2 // C
+        cur = torch.cuda.current_stream()
+        ys, done = [], []
+        for c in range(C):
+            part = ops.int8_gemm(a2, w.w2[c * nc:(c + 1) * nc], xs2, w.s2[c * nc:(c + 1) * nc], None, out_dtype=dt,
+                                 out=self._buf(f"part{c}", (M, nc), dt, x_local))
+            ready = torch.cuda.Event()
+            ready.record(cur)
+            with torch.cuda.stream(self.comm_stream):
+                self.comm_stream.wait_event(ready)
+                ys.append(comm.reduce_scatter_rows(part, self._buf(f"y{c}", (rows, nc), dt, x_local)))
+                ev = torch.cuda.Event()
+                ev.record(self.comm_stream)
+                done.append(ev)
+        for c in range(C):
+            cur.wait_event(done[c])
+            ops.bias_residual_add(ys[c], w.b2, x_local, out=out, n0=c * nc)
+        return out
 
 
 class TPBlock:
-    """The linears of one MMDiT block: joint QKV -> (attention taken as identity on V) -> out, and MLP up -> down."""
+    """The linears of one MMDiT block: joint QKV -> (attention taken as identity on V) -> out, and MLP up -> down, plus
+    the adaLN modulation linear (M = 1, hidden -> 6 x hidden, weight-streaming; column-parallel with no exchange: every
+    rank computes its slice of the modulation vector, which the block's own ranks would consume)."""
 
-    def __init__(self, ops, comm: Comm, attn: PairWeights, mlp: PairWeights, exact: bool = False):
+    def __init__(self, ops, comm: Comm, attn: PairWeights, mlp: PairWeights, exact: bool = False, bufs: Optional[dict] = None,
+                 chunks: int = 1, comm_stream=None, adaln=None):
         v_cols = attn.w2.shape[1]
-        self.attn = TPPair(ops, comm, attn, rotate=1, act_prologue=PRO_PLAIN, hidden_cols=slice(2 * v_cols, 3 * v_cols), exact=exact)
-        self.mlp = TPPair(ops, comm, mlp, rotate=1, act_prologue=PRO_GELU_TANH, exact=exact)
+        self.ops, self.adaln = ops, adaln
+        self.bufs = bufs if bufs is not None else {}
+        common = dict(exact=exact, bufs=self.bufs, chunks=chunks, comm_stream=comm_stream)
+        self.attn = TPPair(ops, comm, attn, rotate=1, act_prologue=PRO_PLAIN, hidden_cols=slice(2 * v_cols, 3 * v_cols), **common)
+        self.mlp = TPPair(ops, comm, mlp, rotate=1, act_prologue=PRO_GELU_TANH, **common)
 
-    def forward(self, x_local: torch.Tensor) -> torch.Tensor:
-        return self.mlp.forward(self.attn.forward(x_local))
+    def forward(self, x_local: torch.Tensor, cond: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self.adaln is not None and cond is not None:
+            wq, ws, b = self.adaln
+            key = ("mod", tuple(wq.shape))
+            c8 = self.bufs.get(key)
+            if c8 is None:
+                c8 = self.bufs[key] = (torch.empty((1, wq.shape[1]), dtype=torch.int8, device=cond.device),
+                                       torch.empty((1,), dtype=torch.float32, device=cond.device),
+                                       torch.empty((1, wq.shape[0]), dtype=cond.dtype, device=cond.device))
+            q, sc = self.ops.quant_rows(cond, 5, 1, q=c8[0], scales=c8[1])          # SiLU prologue, as the DiTs' modulation does
+            self.ops.int8_gemm(q, wq, sc, ws, b, out_dtype=cond.dtype, out=c8[2])
+        # two output buffers alternate so that a pair never writes the rows it still reads as its residual
+        mid = self.attn.forward(x_local)
+        return self.mlp.forward(mid)
 
 
-# ---- benchmark leg: `bench.py --mode tp` ----------------------------------------------------------------------------
-def bench_main(args, rank, world, local, metric, unit):
-    """The 60-block Qwen-Image-shaped MMDiT linear stack at 2048x2048 (M = 16896 tokens, hidden 3072) under column/row
-    tensor parallelism: tokens sharded between blocks, int8 all-gather before the column-parallel linears,
-    reduce-scatter after the row-parallel ones. Random int8 weights per block (generated on the device)."""
-    import os
+# ---- benchmark legs ---------------------------------------------------------------------------------------------------
+STACK_M, STACK_F, STACK_MLP = 16896, 3072, 12288          # the Qwen-Image-shaped MMDiT stack at 2048 x 2048
+PEER_GBS = 770.0                                          # measured peer-copy bandwidth per direction per GPU on this pool
+
+
+def stack_ops_per_block(M: int = STACK_M) -> float:
+    F, MLP = STACK_F, STACK_MLP
+    return 2.0 * M * (3 * F * F + F * F + MLP * F + F * MLP) + 2.0 * 6 * F * F      # four linears + adaLN (M = 1)
+
+
+def link_model_ms(world: int, exact: bool, M: int = STACK_M) -> float:
+    """Time per block the NVLink transfers alone need at the measured peer bandwidth: per pair, every rank receives the
+    other ranks' int8 rows (+ scales) and sends (world - 1) / world of its partial outputs (bf16, or int32 in exact mode)."""
+    if world == 1:
+        return 0.0
+    f = (world - 1) / world
+    per_pair = f * M * (STACK_F + 4) + f * M * STACK_F * (4 if exact else 2) + (f * M * 4 if exact else 0)
+    return 2 * per_pair / (PEER_GBS * 1e9) * 1e3
+
+
+def run_stack(mode: str, rank: int, world: int, local: int, *, blocks: int = 60, steps: int = 3, warmup: int = 1,
+              chunks: int = 3, gemm_clusters: int = 0, graph: bool = True) -> dict:
+    """One of the three ways to run the 60-block linear stack (QKV, attention-out, MLP up / down with GELU-tanh, adaLN) on
+    `world` GPUs, timed with CUDA events (maximum over ranks):
+      token     tokens sharded over the ranks, weights replicated, no data-path collective
+      tp_fast   column / row tensor parallelism, bf16 partial outputs reduce-scattered (overlapped in column blocks)
+      tp_exact  the same with int32 accumulators reduce-scattered: bit-identical to one GPU
+    Random int8 weights per block, generated on the device from one seed on every rank."""
     import torch.distributed as dist
     from . import linear as ops
 
     dev = torch.device("cuda", local)
-    comm = Comm()
-    blocks = int(os.environ.get("BENCH_TP_BLOCKS", "60"))
-    exact = os.environ.get("BENCH_TP_EXACT", "0") == "1"
-    M, F, MLP = 16896, 3072, 12288
+    tp = mode != "token"
+    exact = mode == "tp_exact"
+    comm = Comm() if tp else Comm.__new__(Comm)
+    if not tp:
+        comm.dist, comm.group, comm.world, comm.rank = None, None, 1, 0
+    M, F, MLP = STACK_M, STACK_F, STACK_MLP
     assert M % world == 0 and F // 256 >= world
     g = torch.Generator(device=dev).manual_seed(1234)          # same seed on every rank: identical full weights, then sliced
 
@@ -168,67 +265,90 @@ def bench_main(args, rank, world, local, metric, unit):
                 torch.rand(n, generator=g, device=dev) * 2e-4 + 1e-5,
                 (torch.randn(n, generator=g, device=dev) * 0.01).bfloat16())
 
+    bufs: dict = {}
+    comm_stream = torch.cuda.Stream(dev) if (tp and world > 1 and not exact and chunks > 1) else None
     stack: List[TPBlock] = []
     for _ in range(blocks):
         wqkv, sqkv, bqkv = qweight(3 * F, F)
         wo, so, bo = qweight(F, F)
         wu, su, bu = qweight(MLP, F)
         wd, sd, bd = qweight(F, MLP)
-        attn = shard_pair(wqkv, sqkv, bqkv, wo, so, bo, rank, world, hidden_of=(0, F))
-        mlp = shard_pair(wu, su, bu, wd, sd, bd, rank, world)
-        stack.append(TPBlock(ops, comm, attn, mlp, exact))
-        del wqkv, wo, wu, wd
+        wa, sa, ba = qweight(6 * F, F)
+        r, w = (rank, world) if tp else (0, 1)
+        attn = shard_pair(wqkv, sqkv, bqkv, wo, so, bo, r, w, hidden_of=(0, F))
+        mlp = shard_pair(wu, su, bu, wd, sd, bd, r, w)
+        n_mod = 6 * F // w                                       # the modulation vector's slice of this rank
+        adaln = (wa[r * n_mod:(r + 1) * n_mod].contiguous(), sa[r * n_mod:(r + 1) * n_mod].contiguous(), ba[r * n_mod:(r + 1) * n_mod].contiguous())
+        stack.append(TPBlock(ops, comm, attn, mlp, exact, bufs=bufs, chunks=chunks, comm_stream=comm_stream, adaln=adaln))
+        del wqkv, wo, wu, wd, wa
     rows = M // world
     x = torch.randn(rows, F, generator=torch.Generator(device=dev).manual_seed(99 + rank), device=dev).bfloat16()
+    cond = torch.randn(1, F, generator=torch.Generator(device=dev).manual_seed(7), device=dev).bfloat16()
+    if comm_stream is not None and gemm_clusters > 0:
+        ops.set_gemm_cluster_limit(gemm_clusters)
 
-    # Micro-batches (BENCH_TP_MICRO, default 1 = off): the rank's rows split into independent parts, each on its own stream
-    # and walked through the stack block by block in turn, so that the collectives of one part could overlap the kernels of
-    # the other. Measured on two GPUs it does not pay: the persistent GEMM holds every SM, NCCL's kernels wait for it, and
-    # the halved GEMMs are less efficient (fast mode 105 against 99.6 ms per stack, exact 141 against 125).
-    micro = int(os.environ.get("BENCH_TP_MICRO", "1"))
-    assert rows % micro == 0
-    parts = [x[i * (rows // micro):(i + 1) * (rows // micro)].contiguous() for i in range(micro)]
-    streams = [torch.cuda.Stream(dev) for _ in range(micro)]
-
-    def step():
-        cur = torch.cuda.current_stream()
-        hs = list(parts)
-        for s in streams:
-            s.wait_stream(cur)
+    def one_pass():
+        h = x
         for b in stack:
-            for i, s in enumerate(streams):
-                with torch.cuda.stream(s):
-                    hs[i] = b.forward(hs[i])
-        for s in streams:
-            cur.wait_stream(s)
-        return hs
+            h = b.forward(h, cond)
+        return h
 
-    for _ in range(max(1, args.warmup)):
-        step()
+    one_pass()                                                  # lazy set-up (tables, scratch, buffers) before any capture
+    torch.cuda.synchronize()
+    run, graphed = one_pass, False
+    if graph and (world == 1 or not tp):                        # no collective inside: the whole pass replays as one CUDA graph
+        try:
+            side = torch.cuda.Stream(dev)
+            with torch.cuda.stream(side):
+                cg = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(cg, stream=side):
+                    one_pass()
+            torch.cuda.synchronize()
+            run, graphed = cg.replay, True
+        except Exception:                                       # capture is an optimisation only
+            torch.cuda.synchronize()
+            run, graphed = one_pass, False
+    for _ in range(warmup):
+        run()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier(device_ids=[local])
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
-        step()
+    for _ in range(steps):
+        run()
     e1.record()
     torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
+    ms = e0.elapsed_time(e1) / steps
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    ops_per_block = 2.0 * M * (3 * F * F + F * F + MLP * F + F * MLP)
-    value = ops_per_block * blocks * args.steps / (ms * 1e-3) / 1e12
+    ops.set_gemm_cluster_limit(0)
+    status = ops.kernel_status()
+    del stack, bufs
+    torch.cuda.empty_cache()
+    tops = stack_ops_per_block() * blocks / (ms * 1e-3) / 1e12
+    launches = blocks * ((12 if exact else 10 + (2 * (chunks - 1) if comm_stream is not None else 0)) + 2)
+    return {"mode": mode, "blocks": blocks, "stack_ms": ms, "dit_block_gemm_ms": ms / blocks, "tops": tops, "cuda_graph": graphed,
+            "link_model_ms_per_block": link_model_ms(world if tp else 1, exact), "launches_per_pass": launches,
+            "kernel_status": status}
+
+
+def bench_main(args, rank, world, local, metric, unit):
+    """`bench.py --mode tp`: the stack under tensor parallelism alone (BENCH_TP_EXACT=1 for the exact mode), one JSON line."""
+    import os
+    import torch.distributed as dist
+    mode = "tp_exact" if os.environ.get("BENCH_TP_EXACT", "0") == "1" else "tp_fast"
+    r = run_stack(mode, rank, world, local, blocks=int(os.environ.get("BENCH_TP_BLOCKS", "60")), steps=args.steps,
+                  warmup=max(1, args.warmup), chunks=int(os.environ.get("BENCH_TP_CHUNKS", "3")),
+                  gemm_clusters=int(os.environ.get("BENCH_TP_CLUSTERS", "66")))
     if rank == 0:
-        print(json.dumps({"metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
-                          "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+        print(json.dumps({"metric": metric, "value": r["tops"], "unit": unit, "n_gpus": world, "steps": args.steps,
+                          "warmup": args.warmup, "ms_per_step": r["stack_ms"], "higher_is_better": True, "scaling": "strong",
                           "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-                          "config": {"workload": f"mmdit_linear_stack_{blocks}blocks_M16896_hidden3072", "parallelism": f"tp{world}",
-                                     "mode": "exact (int32 reduce-scatter)" if exact else "fast (bf16 reduce-scatter)",
-                                     "micro_batches": micro,
-                                     "dit_block_gemm_ms": ms / args.steps / blocks},
-                          "gpu_launches": args.steps * blocks * (10 if exact else 8), "kernel_status": ops.kernel_status()}), flush=True)
+                          "config": {"workload": f"mmdit_linear_stack_{r['blocks']}blocks_M16896_hidden3072", "parallelism": f"tp{world}",
+                                     **{k: r[k] for k in ("mode", "dit_block_gemm_ms", "link_model_ms_per_block", "cuda_graph")}},
+                          "gpu_launches": args.steps * r["launches_per_pass"], "kernel_status": r["kernel_status"]}), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -142,6 +142,18 @@ int gpu_quant_rows_scaled(int dtype, int prologue, const void* x, int64_t x_stri
 int gpu_int8_epilogue(const int32_t* acc, const float* xs, const float* ws, const void* bias, const void* rscale,
                       const void* resid, void* D, int64_t M, int64_t N, int out_dt, int act, void* stream);
 
+/* New (tensor parallelism): the tail of a row-parallel linear whose dequantized partial outputs were summed across
+ * devices: out[:, n0:n0+Nc] = T(T(y + bias[n0:n0+Nc]) + resid[:, n0:n0+Nc]); y [M, Nc] contiguous, resid / out [M, ld]
+ * (out may alias resid), bias and resid nullable, all in the activation dtype dt. Nc, n0, ld multiples of 8 and
+ * pointers 16-byte aligned (-202). No counterpart in the reference (single device). */
+int gpu_bias_residual_add(const void* y, const void* bias, const void* resid, void* out, int64_t M, int64_t Nc, int64_t ld,
+                          int64_t n0, int dt, void* stream);
+
+/* New (tensor parallelism): gpu_int8_gemm* launches that follow occupy at most `clusters` CTA pairs (0 = all of the
+ * device's SM pairs, the default), so that a collective running on another stream finds SMs free. Process-wide;
+ * returns the previous value. No counterpart in the reference. */
+int gpu_int8_gemm_set_cluster_limit(int clusters);
+
 /* W6A8: q [N, 3K/4] u8 (per row K/2 nibble bytes then K/4 bytes of top bits), s_rel [N, K/G] fp8-e4m3 ->
  * out int8 [N, K] = clamp(rint((code - 32) * s_rel), +-127). -1 when K % 32 or G % 16.
  * Replaces csrc/h3.cu:40-46 (src/ffi.rs:121). */

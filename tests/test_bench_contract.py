@@ -32,3 +32,21 @@ def test_ours_without_a_gpu_fails_loudly():
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--steps", "1", "--warmup", "0"], capture_output=True,
                          text=True, timeout=600, cwd=ROOT)
     assert out.returncode != 0 and "no CPU fallback" in (out.stderr + out.stdout)
+
+
+def test_reference_arm_does_not_map_the_cuda_library():
+    """The CPU arm takes shapes and seeded inputs from workloads.py by file path; the product's shared library stays out
+    of its process."""
+    code = ("import sys; sys.path.insert(0, %r); import bench; wl = bench.load_workloads(); assert wl.config(1)[0].N == 12288; "
+            "assert 'libb200_qlinear' not in open('/proc/self/maps').read(); assert 'cbr_b200' not in sys.modules" % ROOT)
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300, cwd=ROOT)
+    assert out.returncode == 0, out.stderr[-2000:]
+
+
+def test_both_arms_print_the_same_config():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench_mod", os.path.join(ROOT, "bench.py"))
+    b = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(b)
+    assert b.CONFIG["workload"] == b.WORKLOAD and b.CONFIG["tokens_per_gpu"] == 4352
+    assert b.profiled_dram_bytes() == 176.6e6        # the roofline's traffic comes from the committed ncu summary

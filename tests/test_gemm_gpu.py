@@ -284,3 +284,35 @@ def test_many_rounds_with_a_ragged_last_one(pkg, oracle, dev, M, N, K):
     g2, A2, W2, xs2, ws2 = _operands(256, 512, 8192, 92)
     assert_bits_equal(L.int8_gemm_acc_i32(d(A2), d(W2)), oracle.int8_gemm_acc(A2, W2), "K-split problem after")
     assert L.kernel_status() == 0
+
+
+def test_bias_residual_add_and_cluster_limit(pkg, oracle, dev):
+    """The two tensor-parallel helpers: the bias + residual tail over reduced partial outputs (whole and by column blocks,
+    in place), and GEMM launches restricted to part of the SMs (same results)."""
+    g = torch.Generator().manual_seed(101)
+    M, N = 130, 512
+    L = pkg.linear
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        y = torch.randn(M, N, generator=g).to(dtype)
+        bias = torch.randn(N, generator=g).to(dtype)
+        resid = torch.randn(M, N, generator=g).to(dtype)
+        want = ((y.float() + bias.float()).to(dtype).float() + resid.float()).to(dtype)
+        got = L.bias_residual_add(y.to(dev), bias.to(dev), resid.to(dev))
+        assert_bits_equal(got, want, f"whole {dtype}")
+        out = resid.to(dev).clone()
+        for c in range(4):                                   # column blocks of contiguous partial outputs, written in place
+            L.bias_residual_add(y[:, 128 * c:128 * (c + 1)].contiguous().to(dev), bias.to(dev), out, out=out, n0=128 * c)
+        assert_bits_equal(out, want, f"column blocks in place {dtype}")
+        assert_bits_equal(L.bias_residual_add(y.to(dev), None, None), y, "nothing to add")
+    g, A, W, xs, ws = _operands(2304, 2560, 1024, 102)
+    acc = oracle.int8_gemm_acc(A, W)
+    want = oracle.epilogue(acc, xs, ws, None, contract=3)
+    d = lambda t: t.to(dev)
+    try:
+        assert L.set_gemm_cluster_limit(40) == 0
+        assert_bits_equal(L.int8_gemm(d(A), d(W), d(xs), d(ws), None), want, "40 CTA pairs")
+        assert L.set_gemm_cluster_limit(3) == 40
+        assert_bits_equal(L.int8_gemm_acc_i32(d(A), d(W)), acc, "3 CTA pairs")
+    finally:
+        L.set_gemm_cluster_limit(0)
+    assert L.kernel_status() == 0
