@@ -54,6 +54,47 @@ KERNELS = {
 }
 
 
+# Kernels outside the step, HBM-bound: set-up (returns the algorithmic bytes of one launch) and the launch itself.
+def _setup_hbm(name, b, torch, dev, wl, I):
+    g = torch.Generator(device=dev).manual_seed(11)
+    rnd = lambda *shape: torch.randn(*shape, generator=g, device=dev)
+    if name in ("pack_f32", "pack_bf16"):                        # quantize-at-load of an MLP-up weight (gpu_convrot_requant, seed 0)
+        N, K, esz = 12288, 3072, 4 if name == "pack_f32" else 2
+        b.hw = (rnd(N, K) * 0.02).to(torch.float32 if esz == 4 else torch.bfloat16)
+        return esz * N * K + N * K + 4 * N
+    if name == "sd_quant":                                       # fp16 rows, R256: activations at run time, weights at load
+        M, K = 32768, 2560
+        b.hx = rnd(M, K).half()
+        return 3 * M * K + 4 * M
+    if name == "w6_requant":                                     # the W6 packer (bf16 weight -> two-plane 6-bit + e4m3 group scales)
+        N, K = 13824, 5120
+        b.hw = (rnd(N, K) * 0.015).bfloat16()
+        return 2 * N * K + N * K * 3 // 4 + N * K // 32 + 4 * N
+    if name == "w6_decode":
+        N, K = 13824, 5120
+        b.h6 = I.w6_requant((rnd(N, K) * 0.015).bfloat16(), 1)
+        return N * K * 3 // 4 + N * K // 32 + N * K
+    if name == "adaln":                                          # few-rows weight-streaming GEMM: M = 1, 3072 -> 18432
+        N, K = 18432, 3072
+        b.ha = torch.randint(-128, 128, (1, K), generator=g, dtype=torch.int8, device=dev)
+        b.hw = torch.randint(-128, 128, (N, K), generator=g, dtype=torch.int8, device=dev)
+        b.hs = (torch.rand(1, generator=g, device=dev) * 0.01, torch.rand(N, generator=g, device=dev) * 1e-3, rnd(N).bfloat16())
+        b.hd = torch.empty((1, N), dtype=torch.bfloat16, device=dev)
+        return N * K + K + 4 + 4 * N + 2 * N + 2 * N
+    raise KeyError(name)
+
+
+HBM_KERNELS = {
+    "pack_f32": lambda b, I: I.convrot_requant(b.hw, 0),
+    "pack_bf16": lambda b, I: I.convrot_requant(b.hw, 0),
+    "sd_quant": lambda b, I: I.sd_quant_rows(b.hx, 256),
+    "w6_requant": lambda b, I: I.w6_requant(b.hw, 1),
+    "w6_decode": lambda b, I: I.w6_decode(b.h6[0], b.h6[1], 5120),
+    "adaln": lambda b, I: I.int8_gemm(b.ha, b.hw, b.hs[0], b.hs[1], b.hs[2], out=b.hd),
+}
+QUANT_BYTES = {"quant_rot": 3 * 4352 * 12288, "quant_gelu": 3 * 4352 * 12288, "quant_in": 3 * 4352 * 3072}
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -61,7 +102,7 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
     ap.add_argument("--mode", default="replicas", choices=["replicas", "tp", "kernel", "shapes"])
-    ap.add_argument("--kernel", default="gemm_up", choices=sorted(KERNELS),
+    ap.add_argument("--kernel", default="gemm_up", choices=sorted(list(KERNELS) + list(HBM_KERNELS)),
                     help="--mode kernel: the one kernel to launch --steps times (the command ncu captures are taken from)")
     ap.add_argument("--cpu-rows", type=int, default=4352, help="rows of the batch the CPU baseline computes")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -385,10 +426,37 @@ def main():
         if args.kernel.startswith("w6a8"):
             blk.w6 = tuple(t.to(dev) for t in wl.w6_pack(w1, True))
             blk.w6u = tuple(t.to(dev) for t in wl.w6_pack(w1, False))
-        fn = KERNELS[args.kernel]
-        k_ms = time_steps(torch, lambda: fn(blk, impl), args.steps, args.warmup) / args.steps
-        print(json.dumps({"kernel": args.kernel, "us_per_launch": k_ms * 1e3, "launches": args.steps,
-                          "kernel_status": pkg.linear.kernel_status()}), flush=True)
+        nbytes = QUANT_BYTES.get(args.kernel)
+        if args.kernel in HBM_KERNELS:
+            nbytes = _setup_hbm(args.kernel, blk, torch, dev, wl, impl)
+            fn = HBM_KERNELS[args.kernel]
+        else:
+            fn = KERNELS[args.kernel]
+        out = {"kernel": args.kernel, "launches": args.steps}
+        if nbytes is not None and nbytes < 200e6:
+            # operands that would stay in the 126 MB L2 between launches: one launch at a time, a 256 MB buffer read in between
+            flush = torch.zeros(64 * 1024 * 1024, device=dev)
+            sink = torch.zeros((), device=dev)
+            for _ in range(args.warmup):
+                fn(blk, impl)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            tot = 0.0
+            for _ in range(args.steps):
+                sink.copy_(flush.sum())
+                e0.record(); fn(blk, impl); e1.record()
+                torch.cuda.synchronize()
+                tot += e0.elapsed_time(e1)
+            k_ms = tot / args.steps
+            out["l2"] = "flushed by a 256 MB read before every launch"
+        else:
+            k_ms = time_steps(torch, lambda: fn(blk, impl), args.steps, args.warmup) / args.steps
+        out["us_per_launch"] = k_ms * 1e3
+        if nbytes is not None:
+            _, _, hbm, src = measured_peaks()
+            out.update(algorithmic_bytes=nbytes, gbs=nbytes / (k_ms * 1e-3) / 1e9, frac_of_hbm=nbytes / (k_ms * 1e-3) / 1e9 / hbm,
+                       hbm_peak_gbs=hbm, peak_source=src)
+        out["kernel_status"] = pkg.linear.kernel_status()
+        print(json.dumps(out), flush=True)
         return
     # A 1 kW part reaches its power-capped clock only after about a second of load, and a few dozen steps last milliseconds:
     # the warm-up therefore continues, untimed, until the step has run back to back for SETTLE_S seconds, and the K timed

@@ -27,25 +27,36 @@ __global__ void __launch_bounds__(kWarps * 32) skinny_gemm_kernel(const SkinnyPa
         for (int r = 0; r < kRowsPerWarp; ++r)
 #pragma unroll
             for (int m = 0; m < MT; ++m) acc[r][m] = 0;
-        for (int k0 = lane * 16; k0 < K; k0 += 512) {
-            uint4 w[kRowsPerWarp];
+        // several 512-byte K steps of the four rows are requested before the first is consumed: twelve to twenty-four
+        // 16-byte loads in flight per lane instead of four
+        constexpr int kAhead = MT <= 2 ? 6 : 3;      // one or two rows of A leave registers for twice the loads
+        for (int kb = lane * 16; kb < K; kb += 512 * kAhead) {
+            uint4 w[kAhead][kRowsPerWarp];
 #pragma unroll
-            for (int r = 0; r < kRowsPerWarp; ++r) {
-                const int n = min(n0 + r, p.N - 1);   // rows past N repeat the last row; their results are dropped
-                w[r] = __ldg(reinterpret_cast<const uint4*>(p.W + (int64_t)n * K + k0));
-            }
-#pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                if (m >= p.M) break;
-                const uint4 a = *reinterpret_cast<const uint4*>(a_s + m * K + k0);
+            for (int u = 0; u < kAhead; ++u)
 #pragma unroll
                 for (int r = 0; r < kRowsPerWarp; ++r) {
-                    int s = acc[r][m];
-                    s = __dp4a((int)a.x, (int)w[r].x, s);
-                    s = __dp4a((int)a.y, (int)w[r].y, s);
-                    s = __dp4a((int)a.z, (int)w[r].z, s);
-                    s = __dp4a((int)a.w, (int)w[r].w, s);
-                    acc[r][m] = s;
+                    const int n = min(n0 + r, p.N - 1);   // rows past N repeat the last row; their results are dropped
+                    const int k0 = kb + 512 * u;
+                    w[u][r] = k0 < K ? __ldg(reinterpret_cast<const uint4*>(p.W + (int64_t)n * K + k0)) : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+            for (int u = 0; u < kAhead; ++u) {
+                const int k0 = kb + 512 * u;
+                if (k0 >= K) break;
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    if (m >= p.M) break;
+                    const uint4 a = *reinterpret_cast<const uint4*>(a_s + m * K + k0);
+#pragma unroll
+                    for (int r = 0; r < kRowsPerWarp; ++r) {
+                        int s = acc[r][m];
+                        s = __dp4a((int)a.x, (int)w[u][r].x, s);
+                        s = __dp4a((int)a.y, (int)w[u][r].y, s);
+                        s = __dp4a((int)a.z, (int)w[u][r].z, s);
+                        s = __dp4a((int)a.w, (int)w[u][r].w, s);
+                        acc[r][m] = s;
+                    }
                 }
             }
         }

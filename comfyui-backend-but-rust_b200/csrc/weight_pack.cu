@@ -19,6 +19,11 @@
 #include "common.cuh"
 #include "w6_decode.cuh"
 
+// quant_rows.cu
+GPU_API int gpu_quant_rows(int dtype, int prologue, const void* x, int64_t x_stride, const void* g, int64_t g_stride,
+                           int64_t up_offset, const float* norm_w, float eps, const void* mod_scale, const void* mod_shift,
+                           int8_t* q, float* scales, int M, int K, int rotate, void* stream);
+
 namespace {
 
 // element i of the row sits at word i + 4*(i/16): 16-element runs stay 16-byte aligned and consecutive runs start
@@ -646,6 +651,13 @@ GPU_API int gpu_sd_group_norm_quant_rows(const void* x, const float* w, const fl
 GPU_API int gpu_convrot_requant(int dtype, const void* x, void* q, void* s, int64_t N, int K, uint64_t seed, void* stream) {
     if (K % 256) return -1;
     if (N <= 0) return 0;
+    if (dtype != DT_F32 && dtype != DT_BF16) return -4;
+    // Round-to-nearest packing (seed 0) is, operation for operation, the activation quantizer with no prologue and the
+    // rotation on (the reference's two kernels share the scale rule and the rounding points, csrc/kernels.cu:241-255 and
+    // :1372-1383), so it runs on that kernel, which keeps the row in registers: 12288 x 3072 f32 in a third of the time of
+    // the shared-memory kernel below (which stays for the stochastic rounding and for rows the quantizer does not take).
+    if (seed == 0 && K <= 32768 && N <= INT32_MAX && ((((uintptr_t)x | (uintptr_t)q) & 15) == 0))
+        return gpu_quant_rows(dtype, 0, x, K, nullptr, 0, 0, nullptr, 0.f, nullptr, nullptr, (int8_t*)q, (float*)s, (int)N, K, 1, stream);
     const size_t smem = (size_t)padded_words(K) * sizeof(float);
     const int threads = row_threads(K / 16, 512);
     if (dtype == DT_F32) {
