@@ -38,6 +38,8 @@ namespace b200q {
 int act_lut_ptr(int act, cudaStream_t st, const uint16_t** out);
 // quant_rows.cu: the quantizer's status word (non-zero after a staging wait ran out), read and cleared
 int quant_status_read_clear(int* out);
+// quant_rows.cu: the fp16 row quantizer on the register kernel; false when the shape is outside what it takes
+bool sd_quant_rows_fast(const void* x, int64_t x_stride, int8_t* q, float* scales, int M, int K, int rotate, cudaStream_t st, int* rc);
 bool skinny_gemm_applies(int64_t M, int64_t N, int64_t K);
 int launch_skinny_gemm(int epi, const SkinnyParams& p, int out_dt, int sms, cudaStream_t st);
 // gemm_skinny.cu: the CUDA-core kernel for operands TMA cannot address (K % 16 != 0, bases off a 16-byte boundary)

@@ -532,6 +532,160 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 384 ? 2 : 1) quant_rows_kernel(c
     }
 }
 
+// ---- fp16 (SD / SDXL) flavour ------------------------------------------------------------------------------------------
+// The reference's fp16 row quantizer (csrc/sd.cu:578-597) differs from the one above in its rounding points: values are
+// rounded to half after the rotation, the row maximum is taken over the rounded values, scale = max(mx, 1e-30) / 127 is
+// a division, the divisor is half(scale) unless that underflows, and q = clamp(rint(half(half(v) / st))). Rotation groups
+// are 256 (four stages) or 64 (three). Same thread layout as above (32 consecutive elements per lane): 256-groups go
+// through the same conflict-free transposition; a 64-group is two neighbouring lanes, whose third stage is one exchange
+// of registers. The division is a reciprocal multiply with one Newton step: the exact quotient of two 11-bit significands
+// is never on a half rounding boundary and at least 2^-23 (relative) away from one, and the refined product is within
+// 2^-24 of it, so both round to the same half (tests/test_quant_division.py enumerates the significand pairs).
+template <int ROT>
+__global__ void __launch_bounds__(512) sd_quant_fast_kernel(const half* __restrict__ x, int64_t x_stride, int8_t* __restrict__ q,
+                                                            float* __restrict__ scales, int M, int K, int tpr, int rows,
+                                                            uint32_t off_amax) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const unsigned wmask = __activemask();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int team = lane >> 3, tsw = team & 1, t8 = lane & 7;
+    float* tbuf = reinterpret_cast<float*>(smem) + warp * kWarpWords + team * kGroupWords + 4 * (team >> 1);
+    float* tbuf_w = tbuf - 2 * (team >> 1);
+    unsigned* amax_s = reinterpret_cast<unsigned*>(smem + off_amax);
+    for (int i = threadIdx.x; i < rows; i += blockDim.x) amax_s[i] = 0u;
+    __syncthreads();
+    const int rloc = threadIdx.x / tpr, tin = threadIdx.x - rloc * tpr;
+    const int64_t m_raw = (int64_t)blockIdx.x * rows + rloc;
+    const bool live = m_raw < M;
+    const int64_t m = live ? m_raw : M - 1;            // idle rows recompute the last row and store nothing
+    const half* r = x + m * x_stride + tin * 32;
+    float v[32];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(r) + c);
+        const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(h[i]);
+            v[8 * c + 2 * i] = f.x, v[8 * c + 2 * i + 1] = f.y;
+        }
+    }
+    float2 P[16];
+    if (ROT) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) P[i] = make_float2(v[i], v[i + 16]);
+        two_stages(P);                                  // index bits 0-3
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) P[i] = make_float2(v[2 * i], v[2 * i + 1]);
+    }
+    if (ROT == 256) {
+        float* we = tbuf_w + tpad(t8 << 5) + tsw;
+        float* wo = tbuf_w + tpad(t8 << 5) - tsw;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            float* w = (i & 1) ? wo : we;
+            w[i] = P[i].x;
+            w[16 + i] = P[i].y;
+        }
+        __syncwarp(wmask);
+#pragma unroll
+        for (int rr = 0; rr < 16; ++rr) P[rr] = *reinterpret_cast<const float2*>(tbuf_w + tpad(2 * t8 + 16 * rr));
+        two_stages(P);                                  // index bits 4-7
+        __syncwarp(wmask);
+    } else if (ROT == 64) {
+        // third stage, index bits 4 and 5: bit 4 is the pair's half, bit 5 the lane's parity. The even lane holds x0, x1
+        // and computes outputs 0 and 1 of the block, the odd lane holds x2, x3 and computes outputs 2 and 3.
+        const bool even = (lane & 1) == 0;
+        const float sg = even ? 1.f : -1.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float ox = __shfl_xor_sync(wmask, P[i].x, 1), oy = __shfl_xor_sync(wmask, P[i].y, 1);
+            const float x0 = even ? P[i].x : ox, x1 = even ? P[i].y : oy, x2 = even ? ox : P[i].x, x3 = even ? oy : P[i].y;
+            const float sd = __fmaf_rn(x1, sg, x0);                                   // x0 + x1 (even) or x0 - x1 (odd)
+            const float rx = __fmaf_rn(x3, -sg, __fadd_rn(sd, x2));                   // (sd + x2) - x3   or (sd + x2) + x3
+            const float ry = __fadd_rn(__fmaf_rn(even ? x2 : sd, -1.f, even ? sd : x2), x3);   // (sd - x2) + x3 or (-sd + x2) + x3
+            P[i] = make_float2(__fmul_rn(0.5f, rx), __fmul_rn(0.5f, ry));
+        }
+    }
+    // round to half; the row maximum is over the rounded values (the NaN-propagating form flags threads that hold one)
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        P[i] = __half22float2(__floats2half2_rn(P[i].x, P[i].y));
+        amax = max3_abs_nan(amax, P[i].x, P[i].y);
+    }
+    const bool has_nan = amax != amax;
+    if (has_nan) {
+        amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fmaxf(fabsf(P[i].x), fabsf(P[i].y)));
+    }
+    if ((tpr & 7) == 0) {
+        amax = fmaxf(amax, __shfl_xor_sync(wmask, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(wmask, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(wmask, amax, 4));
+        if (t8 == 0) atomicMax(amax_s + rloc, __float_as_uint(amax));
+    } else {
+        atomicMax(amax_s + rloc, __float_as_uint(amax));
+    }
+    __syncthreads();
+    const float mx = __uint_as_float(amax_s[rloc]);
+    const float scale = __fdiv_rn(fmaxf(mx, 1e-30f), 127.f);
+    if (live && tin == 0) scales[m] = scale;
+    const float sh16 = rnd<half>(scale);
+    const float st = sh16 > 0.f ? sh16 : scale;          // a scale below half's range divides in float
+    const bool fast = sh16 > 0.f && mx <= 65504.f && !has_nan;
+    uint32_t c16[16];
+    if (fast) {
+        const float rcp = __frcp_rn(st);
+        const float2 rcp2 = make_float2(rcp, rcp), nst2 = make_float2(-st, -st), magic = make_float2(12582912.f, 12582912.f);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float2 q0 = __fmul2_rn(P[i], rcp2);
+            const float2 t = __ffma2_rn(__ffma2_rn(q0, nst2, P[i]), rcp2, q0);
+            const float2 th = __half22float2(__floats2half2_rn(t.x, t.y));
+            const float2 u = __fadd2_rn(th, magic);
+            const int n0 = (int)__float_as_uint(u.x) - 0x4B400000, n1 = (int)__float_as_uint(u.y) - 0x4B400000;
+            asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(c16[i]) : "r"(n1), "r"(n0));
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int qx = clamp_rint_i8(rnd<half>(__fdiv_rn(P[i].x, st)), -128.f), qy = clamp_rint_i8(rnd<half>(__fdiv_rn(P[i].y, st)), -128.f);
+            c16[i] = (uint32_t)(qx & 0xff) | ((uint32_t)(qy & 0xff) << 8);
+        }
+    }
+    int8_t* qr = q + m * (int64_t)K + tin * 32;
+    if (ROT == 256) {
+        uint16_t* cb = reinterpret_cast<uint16_t*>(tbuf);
+        const uint32_t order = tsw ? 0x3201u : 0x3210u;
+#pragma unroll
+        for (int rr = 0; rr < 16; ++rr) cb[t8 + 8 * rr] = (uint16_t)__byte_perm(c16[rr], 0u, order);
+        __syncwarp(wmask);
+        const uint4 lo = reinterpret_cast<const uint4*>(tbuf)[2 * t8], hi = reinterpret_cast<const uint4*>(tbuf)[2 * t8 + 1];
+        if (live) {
+            reinterpret_cast<uint4*>(qr)[0] = lo;
+            reinterpret_cast<uint4*>(qr)[1] = hi;
+        }
+    } else if (live) {
+        uint32_t w[8];
+        if (ROT == 64) {      // c16[i] = codes of elements (i, i + 16)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t a = __byte_perm(c16[4 * j], c16[4 * j + 1], 0x5140), b = __byte_perm(c16[4 * j + 2], c16[4 * j + 3], 0x5140);
+                w[j] = __byte_perm(a, b, 0x5410);          // bytes: codes of elements 4j .. 4j+3
+                w[4 + j] = __byte_perm(a, b, 0x7632);      // and of elements 16+4j .. 16+4j+3
+            }
+        } else {              // c16[i] = codes of elements (2i, 2i + 1)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w[i] = (c16[2 * i] & 0xffffu) | (c16[2 * i + 1] << 16);
+        }
+        reinterpret_cast<uint4*>(qr)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        reinterpret_cast<uint4*>(qr)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+}
+
 // ---- host side ------------------------------------------------------------------------------------------------
 struct LutState {
     std::mutex mu;
@@ -582,6 +736,43 @@ int ensure_lut(int which, cudaStream_t st) {
 }
 
 }  // namespace
+
+// gpu_sd_quant_rows through the register kernel above; false when the shape is not one it takes (the caller falls back).
+bool b200q::sd_quant_rows_fast(const void* x, int64_t x_stride, int8_t* q, float* scales, int M, int K, int rotate, cudaStream_t st,
+                               int* rc) {
+    if (K % 32 || K > 16384 || (rotate == 64 && K % 64) || (rotate == 256 && K % 256) || (rotate != 0 && rotate != 64 && rotate != 256))
+        return false;
+    if ((((uintptr_t)x | (uintptr_t)q) & 15) || (x_stride & 7)) return false;
+    const int tpr = K / 32;
+    int rows = 256 / tpr;
+    if (rows < 1) rows = 1;
+    if (rows * tpr < 32) rows = (32 + tpr - 1) / tpr;
+    const int threads = rows * tpr;
+    const uint32_t off_amax = rotate == 256 ? (uint32_t)((threads + 31) / 32) * kWarpWords * 4 : 0;
+    const size_t smem = off_amax + (size_t)rows * 4;
+    const unsigned grid = (unsigned)((M + rows - 1) / rows);
+    const half* xh = (const half*)x;
+    *rc = 0;
+    if (rotate == 256) {
+        static std::atomic<uint64_t> configured{0};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        const uint64_t bit = 1ull << (dev & 63);
+        if (smem > 48 * 1024 && !(configured.load(std::memory_order_acquire) & bit)) {
+            const cudaError_t e = cudaFuncSetAttribute(sd_quant_fast_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+            if (e != cudaSuccess) { *rc = (int)e; return true; }
+            configured.fetch_or(bit, std::memory_order_release);
+        }
+        sd_quant_fast_kernel<256><<<grid, threads, smem, st>>>(xh, x_stride, q, scales, M, K, tpr, rows, off_amax);
+    } else if (rotate == 64) {
+        sd_quant_fast_kernel<64><<<grid, threads, smem, st>>>(xh, x_stride, q, scales, M, K, tpr, rows, off_amax);
+    } else {
+        sd_quant_fast_kernel<0><<<grid, threads, smem, st>>>(xh, x_stride, q, scales, M, K, tpr, rows, off_amax);
+    }
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) *rc = (int)e;
+    return true;
+}
 
 // Reads and clears the quantizer's status word (a staging wait that ran out); used by gpu_kernels_status.
 int b200q::quant_status_read_clear(int* out) {

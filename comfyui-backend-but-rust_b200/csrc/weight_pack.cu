@@ -17,6 +17,7 @@
 #include <cuda_fp8.h>
 
 #include "common.cuh"
+#include "epilogue.cuh"
 #include "w6_decode.cuh"
 
 // quant_rows.cu
@@ -567,6 +568,10 @@ GPU_API int gpu_sd_quant_rows(const void* x, int64_t x_stride, int8_t* q, float*
                               void* stream) {
     if ((rotate != 0 && rotate != 64 && rotate != 256) || (rotate && K % rotate)) return -1;
     if (M <= 0 || K <= 0) return 0;
+    {   // rows of whole 32-value pieces: the quantizer's register kernel (transposition through shared memory for R256)
+        int rc = 0;
+        if (sd_quant_rows_fast(x, x_stride, q, scales, M, K, rotate, (cudaStream_t)stream, &rc)) return rc;
+    }
     // register kernel: whole 16-value pieces per thread, rotation groups inside a warp, aligned rows
     const int tpr = K / 16;
     if (K % 16 == 0 && tpr <= 512 && x_stride % 8 == 0 && (((uintptr_t)x & 15) == 0) && (((uintptr_t)q & 15) == 0)) {

@@ -23,6 +23,27 @@ def test_sd_quant_rows(pkg, oracle, dev, M, K, rot):
     assert_bits_equal(s, so, "scales")
 
 
+@pytest.mark.parametrize("rot", [0, 64, 256])
+def test_sd_quant_rows_row_lengths_and_special_values(pkg, ref, dev, rot):
+    """Every row length the register kernel takes for this rotation (K = 32 n, 64 n or 256 n up to 16384, longer rows and
+    ragged K on the shared-memory kernel), several rows per CTA, with infinities, NaN, zeros, half's largest and smallest
+    values sprinkled in: codes and scales equal the reference's kernel."""
+    step = {0: 32, 64: 64, 256: 256}[rot]
+    g = torch.Generator().manual_seed(rot + 5)
+    special = torch.tensor([0.0, 65504.0, -65504.0, 6e-8, -6e-8, 1e-4, float("inf"), float("-inf"), float("nan")]).half()
+    for K in list(range(step, 2561, step)) + [5120, 10240, 16384, 16384 + step]:
+        M = 37 if K <= 2560 else 5
+        x = (torch.randn(M, K + 8, generator=g) * 0.5).half()
+        idx = torch.randint(0, M * (K + 8), (M,), generator=g)
+        x.view(-1)[idx] = special[torch.randint(0, len(special), (M,), generator=g)]
+        x[1] = 0
+        xd = x.to(dev)[:, :K]                            # row stride K + 8
+        q, s = pkg.linear.sd_quant_rows(xd, rot)
+        qr, sr = ref.sd_quant_rows(xd, rot)
+        assert_bits_equal(s, sr, f"scales K={K}")
+        assert_bits_equal(q, qr, f"codes K={K}")
+
+
 def test_sd_quant_rows_tiny_scale_and_stride(pkg, oracle, dev):
     x = torch.zeros(3, 256).half()
     x[1] = 6e-8           # scale below half's range: the division stays in float (csrc/sd.cu:592-593)

@@ -35,3 +35,19 @@ def test_no_quotient_sits_on_a_rounding_boundary():
     assert odd_part.max() < 256          # odd part of the left side
     # odd part of the right side is odd(S) * M >= 257: the two can never be equal
     assert 1 * 257 > odd_part.max()
+
+
+def test_half_division_by_refined_reciprocal_for_every_significand_pair():
+    """The fp16 quantizer's division: q0 = a * rcp(st), t = fma(fma(-q0, st, a), rcp, q0), then half(t). For every pair of
+    11-bit significands (and exponents covering quotients from 2^-12 to 2^9) half(t) equals half(a / st)."""
+    A = np.arange(1024, 2048, dtype=np.float64)[:, None]
+    S = np.arange(1024, 2048, dtype=np.float64)[None, :]
+    rcp = (np.float32(1.0) / S.astype(np.float32)).astype(np.float32).astype(np.float64)
+    for e in range(-12, 10):
+        a = A * 2.0 ** e
+        q0 = (a.astype(np.float32) * rcp.astype(np.float32)).astype(np.float32).astype(np.float64)
+        r = (a - q0 * S).astype(np.float32).astype(np.float64)          # fma(-q0, st, a): the difference is exact in double
+        t = (q0 + r * rcp).astype(np.float32)                           # fma(r, rcp, q0)
+        ieee = (a.astype(np.float32) / S.astype(np.float32)).astype(np.float32)
+        assert np.array_equal(t.astype(np.float16), ieee.astype(np.float16)), e
+        assert np.array_equal(ieee.astype(np.float16), (a / S).astype(np.float16)), e
