@@ -5,8 +5,8 @@
 
 One step = one pass of the path over one batch of the ConvRot int8 MMDiT MLP pair (Qwen-Image-shaped block at
 1024x1024: M = 4352 tokens, 3072 -> 12288 with GELU-tanh, 12288 -> 3072 with the residual add):
-    quantize rows (rotate) -> int8 GEMM -> quantize rows (GELU-tanh prologue, rotate) -> int8 GEMM + residual epilogue
-(the reference's arrangement; BENCH_FUSED_GELU=1 moves the GELU into the first GEMM's epilogue instead)
+    quantize rows (rotate) -> int8 GEMM with the GELU-tanh epilogue -> quantize rows (rotate) -> int8 GEMM + residual epilogue
+(--unfused-gelu: the reference's arrangement, plain epilogue and the GELU in the next quantizer's prologue; same bits)
 Inputs are seeded synthetic tensors with the block's shapes and distributions (no checkpoint is available offline).
 
 Prints ONE JSON line. `value` is whole-job tera-ops/s (2*M*N*K per linear) with inputs resident in HBM; `e2e` is the
@@ -38,7 +38,7 @@ UNIT = "TOPS"
 WORKLOAD = "convrot_int8_mmdit_mlp_pair_M4352_K3072_N12288"
 INT8_NOMINAL_TOPS = 4500.0
 # the same `config` in both arms: what is computed, not how
-CONFIG = {"workload": WORKLOAD, "step": "quant(R256) -> gemm -> gelu+quant(R256) -> gemm+residual", "tokens_per_gpu": 4352}
+CONFIG = {"workload": WORKLOAD, "step": "quant(R256) -> gemm -> gelu -> quant(R256) -> gemm+residual", "tokens_per_gpu": 4352}
 
 
 # --mode kernel: one kernel of the step alone, on the step's own buffers (what profiles/ summarises)
@@ -106,6 +106,8 @@ def parse_args():
                     help="--mode kernel: the one kernel to launch --steps times (the command ncu captures are taken from)")
     ap.add_argument("--cpu-rows", type=int, default=4352, help="rows of the batch the CPU baseline computes")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--unfused-gelu", action="store_true",
+                    help="the reference's arrangement: plain GEMM epilogue, GELU-tanh in the next quantizer's prologue")
     ap.add_argument("--no-stack", action="store_true", help="skip the 60-block stack record")
     ap.add_argument("--stack-blocks", type=int, default=60)
     return ap.parse_args()
@@ -411,7 +413,7 @@ def main():
             return
         impl, fused = RefImpl(R), False
     else:
-        impl, fused = pkg.linear, os.environ.get("BENCH_FUSED_GELU", "0") == "1"
+        impl, fused = pkg.linear, not args.unfused_gelu
 
     if args.mode == "shapes":
         if rank == 0:

@@ -7,7 +7,8 @@
 
 #include "common.cuh"
 
-enum EpiMode { EPI_PLAIN = 0, EPI_RESID = 1, EPI_ACT = 2, EPI_ACC = 3 };
+// EPI_ACT computes the activation; EPI_ACT_LUT (tensor-core kernel, bf16 outputs) reads bf16(act(x)) from a table instead
+enum EpiMode { EPI_PLAIN = 0, EPI_RESID = 1, EPI_ACT = 2, EPI_ACC = 3, EPI_ACT_LUT = 4 };
 enum Act { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_SILU = 2, ACT_GELU_ERF = 3 };
 
 template <typename OutT, int EPI>

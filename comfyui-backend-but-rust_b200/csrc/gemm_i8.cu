@@ -44,7 +44,11 @@ constexpr int kThreads = 320;  // warp 0 producer, warp 1 MMA, warps 2-9 epilogu
 constexpr int kEpiWarps = 8;
 constexpr int kMaxStages = 8;
 constexpr int kSmemBytes = 232448;            // the per-CTA maximum (227 KB)
-constexpr int kStagingBytes = kEpiWarps * 4096;  // per epilogue warp: 32 rows x 128 B of output staging
+// Epilogue staging, 32 KB. 4-byte outputs: per warp 32 rows x 128 B. 2-byte outputs: per warp a 2 KB chunk buffer (32 rows x
+// 64 B), then per warp the staged per-column vectors (ws | bias [| rscale], 128 floats each), and, for the activation
+// epilogue, the shared-memory part of the activation table behind them (16 + 8 + 8 KB).
+constexpr int kStagingBytes = kEpiWarps * 4096;
+constexpr int kVecOffset = kEpiWarps * 2048;                 // 2-byte outputs: vectors start behind the chunk buffers
 constexpr int kTailBytes = 256;               // barriers, tensor-memory pointer, abort flag
 
 struct GemmParams {
@@ -142,9 +146,14 @@ template <> __device__ __forceinline__ void load8<half>(const half* p, float (&y
 //   t0 = float(acc) * xs;  v = out(fma(t0, ws, bias));  RESID: fma(v, rscale, resid);  ACT: act(v)
 // `vs`, when set, points at this warp's staged per-column vectors for these 8 columns in shared memory
 // (ws at vs[0..], bias at vs[VS..], rscale at vs[2 VS..], all as f32, zero beyond N; VS = columns a warp stages).
+// The part of the 65536-entry activation table an epilogue keeps in shared memory: bf16 bit patterns of 2^-10 <= |x| < 64
+// (16 exponents x 128 significands), positive half first; anything else is read from the whole table in global memory.
+constexpr uint32_t kActLutLo = 0x3A80u, kActLutHalf = 16u * 128u;
+constexpr int kActLutBytes = 2 * (int)kActLutHalf * 2;
+
 template <typename OutT, int EPI, int VS = 128>
 __device__ __forceinline__ void epilogue8(const GemmParams& p, const uint32_t* r, int row, int col, float xs_r, bool vec,
-                                          float (&y)[8], const float* vs = nullptr) {
+                                          float (&y)[8], const float* vs = nullptr, const uint16_t* lut_sm = nullptr) {
     float w8[8], b8[8], rs8[8], rr[8];
     const OutT* rsd = reinterpret_cast<const OutT*>(p.resid) + (int64_t)row * p.N + col;
     if (vs) {
@@ -188,14 +197,51 @@ __device__ __forceinline__ void epilogue8(const GemmParams& p, const uint32_t* r
         const float t0 = __fmul_rn(__int2float_rn((int)r[e]), xs_r);
         float v = rnd<OutT>(__fmaf_rn(t0, w8[e], b8[e]));
         if (EPI == EPI_RESID) v = __fmaf_rn(v, rs8[e], rr[e]);
-        else if (EPI == EPI_ACT) {
-            if (std::is_same<OutT, bf16>::value && p.act_lut)
-                v = __uint_as_float((uint32_t)__ldg(p.act_lut + (__float_as_uint(v) >> 16)) << 16);
-            else
-                v = p.act == ACT_GELU_TANH ? gelu_tanh_f(v) : p.act == ACT_SILU ? silu_f(v) : gelu_f(v);
+        else if (EPI == EPI_ACT_LUT) {
+            // bf16(act(v)) from the table: its hot part sits in shared memory, the rest is read from global memory
+            // (a predicated load; the shared-memory index is masked into range either way)
+            const uint32_t bits = __float_as_uint(v) >> 16;
+            const uint32_t u = bits - kActLutLo;
+            uint32_t t = lut_sm[(u & 0x7ffu) | ((u >> 4) & 0x800u)];                     // sign bit 15 -> the table's second half
+            if ((u & 0x7fffu) >= kActLutHalf) t = __ldg(p.act_lut + bits);
+            v = __uint_as_float(t << 16);
+        } else if (EPI == EPI_ACT) {
+            v = p.act == ACT_GELU_TANH ? gelu_tanh_f(v) : p.act == ACT_SILU ? silu_f(v) : gelu_f(v);
         }
         y[e] = v;
     }
+}
+
+// The table-driven activation epilogue on 8 consecutive columns of one row, for bf16 outputs through the staged path:
+// y = bf16(fma(float(acc) * xs, ws, bias)) is formed two at a time (one packed conversion), its 16 bits index the table
+// (hot part in shared memory, sign in the index's top bit), and the table's 16-bit entries are the output as they are:
+// no conversion back and forth. Values outside the shared-memory part (checked once per 8) are read from the whole table.
+template <int VS>
+__device__ __forceinline__ uint4 epilogue8_lut(const GemmParams& p, const uint32_t* r, float xs_r, const float* vs,
+                                               const uint16_t* lut_sm) {
+    float w8[8], b8[8];
+    load8<float>(vs, w8);
+    load8<float>(vs + VS, b8);
+    uint32_t bits[8], t[8], worst = 0;
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) {
+        const float v0 = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[e]), xs_r), w8[e], b8[e]);
+        const float v1 = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[e + 1]), xs_r), w8[e + 1], b8[e + 1]);
+        const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(&h);
+        bits[e] = w & 0xffffu, bits[e + 1] = w >> 16;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const uint32_t u = bits[e] - kActLutLo;
+        worst = max(worst, u & 0x7fffu);
+        t[e] = lut_sm[(u & 0x7ffu) | ((u >> 4) & 0x800u)];
+    }
+    if (worst >= kActLutHalf) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) t[e] = __ldg(p.act_lut + bits[e]);
+    }
+    return make_uint4(t[0] | (t[1] << 16), t[2] | (t[3] << 16), t[4] | (t[5] << 16), t[6] | (t[7] << 16));
 }
 
 // One 32-column chunk of one accumulator row, written straight to global memory (the path for outputs whose row
@@ -242,12 +288,16 @@ __device__ __forceinline__ void chunk_direct(const GemmParams& p, const uint32_t
 // 2-byte outputs: the chunk's 32 values of this lane's row, computed and packed (no shared-memory traffic yet)
 template <typename OutT, int EPI, int VS = 128>
 __device__ __forceinline__ void chunk_compute16(const GemmParams& p, const uint32_t (&r)[32], int row, int col0, float xs_r,
-                                                const float* vs, uint4 (&pk)[4]) {
+                                                const float* vs, uint4 (&pk)[4], const uint16_t* lut_sm = nullptr) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-        float y[8];
-        epilogue8<OutT, EPI, VS>(p, r + 8 * j, row, col0 + 8 * j, xs_r, p.vec_ok && col0 + 8 * j + 8 <= p.N, y, vs + 8 * j);
-        if constexpr (sizeof(OutT) == 2) pk[j] = pack8<OutT>(y);
+        if constexpr (EPI == EPI_ACT_LUT) {
+            pk[j] = epilogue8_lut<VS>(p, r + 8 * j, xs_r, vs + 8 * j, lut_sm);
+        } else {
+            float y[8];
+            epilogue8<OutT, EPI, VS>(p, r + 8 * j, row, col0 + 8 * j, xs_r, p.vec_ok && col0 + 8 * j + 8 <= p.N, y, vs + 8 * j, lut_sm);
+            if constexpr (sizeof(OutT) == 2) pk[j] = pack8<OutT>(y);
+        }
     }
 }
 __device__ __forceinline__ void chunk_write16(const uint4 (&pk)[4], uint8_t* stage, int lane) {
@@ -342,6 +392,15 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         tmem_alloc_pair(smem_u32(tmem_ptr_s), 512);
         tmem_relinquish_pair();
     }
+    if constexpr (EPI == EPI_ACT_LUT) {
+        // the activation table's hot part into shared memory (a gather from the whole table through L1 costs the epilogue
+        // one wavefront per distinct line and made it, not the tensor core, the limit)
+        if (warp >= 2) {
+            uint16_t* dst = reinterpret_cast<uint16_t*>(staging + kVecOffset + kEpiWarps * 1024);
+            for (uint32_t i = threadIdx.x - 64; i < 2 * kActLutHalf; i += kThreads - 64)
+                dst[i] = __ldg(p.act_lut + (i < kActLutHalf ? kActLutLo + i : 0x8000u + kActLutLo + (i - kActLutHalf)));
+        }
+    }
     tc_fence_before();
     __syncthreads();
     cluster_sync_all();   // the peer's barriers exist before anything signals them
@@ -431,9 +490,11 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const int quad = warp & 3;               // TMEM lane quarter this warp may read
         const int half = ew >> 2;                // which half of the 32-column chunks
         const int nchunks = BN / 32;
-        uint8_t* my_stage = staging + ew * 4096;
+        constexpr int kVecBytes = EPI == EPI_RESID ? 1536 : 1024;       // ws[128] | bias[128] | rscale[128] (residual form only)
+        uint8_t* my_stage = staging + ew * (kStageVec ? 2048 : 4096);
         const uint32_t my_stage_u32 = smem_u32(my_stage);
-        float* my_vec = reinterpret_cast<float*>(my_stage + 2048);   // ws[128] | bias[128] | rscale[128]
+        float* my_vec = reinterpret_cast<float*>(staging + kVecOffset + ew * kVecBytes);
+        const uint16_t* lut_sm = reinterpret_cast<const uint16_t*>(staging + kVecOffset + kEpiWarps * 1024);   // EPI_ACT_LUT only
         int buf = 0;
         uint32_t tphase = 0;
         for (int w = cluster_id; w < p.num_items; w += nclusters) {
@@ -472,7 +533,7 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 if (p.tma_store) {
                     if constexpr (kStageVec) {
                         uint4 pk[4];
-                        chunk_compute16<OutT, EPI>(p, r, rrow, col0, xs_r, my_vec + 32 * ((c - half) >> 1), pk);
+                        chunk_compute16<OutT, EPI>(p, r, rrow, col0, xs_r, my_vec + 32 * ((c - half) >> 1), pk, lut_sm);
                         if (lane == 0) bulk_wait_read<0>();   // the previous chunk's store has read the buffer
                         __syncwarp();
                         chunk_write16(pk, my_stage, lane);
@@ -690,6 +751,9 @@ int launch_pair_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tw, const
         case EPI_PLAIN: return launch_pair<OutT, EPI_PLAIN>(ta, tw, td, p, grid, st);
         case EPI_RESID: return launch_pair<OutT, EPI_RESID>(ta, tw, td, p, grid, st);
         case EPI_ACT: return launch_pair<OutT, EPI_ACT>(ta, tw, td, p, grid, st);
+        case EPI_ACT_LUT:
+            if constexpr (std::is_same<OutT, bf16>::value) return launch_pair<bf16, EPI_ACT_LUT>(ta, tw, td, p, grid, st);
+            return -200;
         default: return -200;
     }
 }
@@ -789,13 +853,15 @@ int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const f
     p.M = (int)M, p.N = (int)N, p.K = (int)K;
     p.act = act;
     p.act_lut = nullptr;
-    if (epi == EPI_ACT && out_dt == DT_BF16 && M * N >= (1 << 20)) {
-        if (int rc = act_lut_ptr(act, st, &p.act_lut)) return rc;
-    }
     const int esz = epi == EPI_ACC ? 4 : (out_dt == DT_F32 ? 4 : 2);
     auto al16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
     p.vec_ok = (N % 8 == 0) && al16(D) && al16(ws) && al16(bias) && al16(rscale) && al16(resid);
     p.tma_store = al16(D) && ((N * esz) % 16 == 0);
+    // large bf16 outputs take the activation from the table (the staged-output path keeps its hot part in shared memory)
+    if (epi == EPI_ACT && out_dt == DT_BF16 && M * N >= (1 << 20) && p.tma_store) {
+        if (int rc = act_lut_ptr(act, st, &p.act_lut)) return rc;
+        epi = EPI_ACT_LUT;
+    }
     p.ksub = K <= BK ? 1 : 2;
     p.k_iters = (int)((K + p.ksub * BK - 1) / (p.ksub * BK));
     const int bn = choose_bn(M, N, clusters);

@@ -411,9 +411,6 @@ int run_w6_gemm(int epi, const int8_t* A, const uint8_t* Wq6, const uint8_t* s_r
     p.M = (int)M, p.N = (int)N, p.K = (int)K;
     p.act = act;
     p.act_lut = nullptr;
-    if (epi == EPI_ACT && out_dt == DT_BF16 && M * N >= (1 << 20)) {
-        if (int rc = act_lut_ptr(act, st, &p.act_lut)) return rc;
-    }
     const int esz = epi == EPI_ACC ? 4 : (out_dt == DT_F32 ? 4 : 2);
     auto al16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
     p.vec_ok = (N % 8 == 0) && al16(D) && al16(ws) && al16(bias) && al16(rscale) && al16(resid);
