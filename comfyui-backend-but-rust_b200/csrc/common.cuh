@@ -317,13 +317,31 @@ constexpr uint32_t kDescHiSw128 = (uint32_t)(((uint64_t)(1024 >> 4) << 32 | (1ul
 __device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_addr) { return ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16); }
 // Pair MMA taking the descriptors as (low word, shared high word): the issuing thread's instruction count is
 // what bounds the tensor pipe, so nothing 64-bit is computed per instruction.
-__device__ __forceinline__ void umma_i8_pair_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "mov.b64 da, {%1, %5};\n\t"
-        "mov.b64 db, {%2, %5};\n\t"
-        "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiSw128)
-        : "memory");
+// KIND 0: int8 x int8 -> int32 (kind::i8); KIND 1: bf16 x bf16 -> f32 (kind::f16), 32 bytes of K per instruction either way.
+template <int KIND>
+__device__ __forceinline__ void umma_pair_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+    if constexpr (KIND == 0) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "mov.b64 da, {%1, %5};\n\t"
+            "mov.b64 db, {%2, %5};\n\t"
+            "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %3, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiSw128)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "mov.b64 da, {%1, %5};\n\t"
+            "mov.b64 db, {%2, %5};\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %3, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiSw128)
+            : "memory");
+    }
+}
+// Instruction descriptor for kind::f16 with bf16 operands and f32 accumulators: D f32 (bits 4-5 = 1), A and B bf16
+// (bits 7-9, 10-12 = 1), both K-major, N >> 3 in bits 17-22, M >> 4 in bits 24-28.
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }

@@ -39,6 +39,9 @@ namespace b200q {
 int act_lut_ptr(int act, cudaStream_t st, const uint16_t** out);
 // quant_rows.cu: the quantizer's status word (non-zero after a staging wait ran out), read and cleared
 int quant_status_read_clear(int* out);
+// quant_rows.cu: gpu_rotate_rows_f32's prologue + rotation with the rows written as two bf16 terms [M, K] each
+int rotate_rows_split(int prologue, const float* x, int64_t x_stride, int64_t up_offset, const float* norm_w, float eps, void* hi,
+                      void* lo, int M, int K, cudaStream_t st);
 // quant_rows.cu: the fp16 row quantizer on the register kernel; false when the shape is outside what it takes
 bool sd_quant_rows_fast(const void* x, int64_t x_stride, int8_t* q, float* scales, int M, int K, int rotate, cudaStream_t st, int* rc);
 bool skinny_gemm_applies(int64_t M, int64_t N, int64_t K);

@@ -151,7 +151,12 @@ template <> __device__ __forceinline__ void load8<half>(const half* p, float (&y
 constexpr uint32_t kActLutLo = 0x3A80u, kActLutHalf = 16u * 128u;
 constexpr int kActLutBytes = 2 * (int)kActLutHalf * 2;
 
-template <typename OutT, int EPI, int VS = 128>
+// Accumulator word -> float: int32 sums of the int8 kernel (KIND 0), or the f32 sums of the bf16 kernel (KIND 1) as they are.
+template <int KIND> __device__ __forceinline__ float acc_f(uint32_t r) {
+    return KIND == 0 ? __int2float_rn((int)r) : __uint_as_float(r);
+}
+
+template <typename OutT, int EPI, int VS = 128, int KIND = 0>
 __device__ __forceinline__ void epilogue8(const GemmParams& p, const uint32_t* r, int row, int col, float xs_r, bool vec,
                                           float (&y)[8], const float* vs = nullptr, const uint16_t* lut_sm = nullptr) {
     float w8[8], b8[8], rs8[8], rr[8];
@@ -172,7 +177,11 @@ __device__ __forceinline__ void epilogue8(const GemmParams& p, const uint32_t* r
         load8<float>(p.ws + col, w8);
         if (p.bias) load8<OutT>(reinterpret_cast<const OutT*>(p.bias) + col, b8);
         if (EPI == EPI_RESID) {
-            load8<OutT>(reinterpret_cast<const OutT*>(p.rscale) + col, rs8);
+            if (p.rscale) load8<OutT>(reinterpret_cast<const OutT*>(p.rscale) + col, rs8);
+            else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) rs8[e] = 1.f;
+            }
             load8<OutT>(rsd, rr);
         }
     } else {
@@ -183,7 +192,7 @@ __device__ __forceinline__ void epilogue8(const GemmParams& p, const uint32_t* r
             w8[e] = in ? p.ws[n] : 0.f;
             if (p.bias) b8[e] = in ? to_f<OutT>(reinterpret_cast<const OutT*>(p.bias)[n]) : 0.f;
             if (EPI == EPI_RESID) {
-                rs8[e] = in ? to_f<OutT>(reinterpret_cast<const OutT*>(p.rscale)[n]) : 0.f;
+                rs8[e] = !in ? 0.f : p.rscale ? to_f<OutT>(reinterpret_cast<const OutT*>(p.rscale)[n]) : 1.f;
                 rr[e] = in ? to_f<OutT>(rsd[e]) : 0.f;
             }
         }
@@ -194,7 +203,7 @@ __device__ __forceinline__ void epilogue8(const GemmParams& p, const uint32_t* r
     }
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-        const float t0 = __fmul_rn(__int2float_rn((int)r[e]), xs_r);
+        const float t0 = __fmul_rn(acc_f<KIND>(r[e]), xs_r);
         float v = rnd<OutT>(__fmaf_rn(t0, w8[e], b8[e]));
         if (EPI == EPI_RESID) v = __fmaf_rn(v, rs8[e], rr[e]);
         else if (EPI == EPI_ACT_LUT) {
@@ -246,7 +255,7 @@ __device__ __forceinline__ uint4 epilogue8_lut(const GemmParams& p, const uint32
 
 // One 32-column chunk of one accumulator row, written straight to global memory (the path for outputs whose row
 // pitch or base TMA cannot address, and for ragged N).
-template <typename OutT, int EPI>
+template <typename OutT, int EPI, int KIND = 0>
 __device__ __forceinline__ void chunk_direct(const GemmParams& p, const uint32_t (&r)[32], int row, int col0, float xs_r) {
     if (EPI == EPI_ACC) {
         int32_t* d = reinterpret_cast<int32_t*>(p.D) + (int64_t)row * p.N + col0;
@@ -266,7 +275,7 @@ __device__ __forceinline__ void chunk_direct(const GemmParams& p, const uint32_t
         if (col0 + j >= p.N) break;
         const bool vec = p.vec_ok && col0 + j + 8 <= p.N;
         float y[8];
-        epilogue8<OutT, EPI>(p, r + j, row, col0 + j, xs_r, vec, y);
+        epilogue8<OutT, EPI, 128, KIND>(p, r + j, row, col0 + j, xs_r, vec, y);
         if (vec) {
             if constexpr (sizeof(OutT) == 2) {
                 *reinterpret_cast<uint4*>(d + j) = pack8<OutT>(y);
@@ -286,7 +295,7 @@ __device__ __forceinline__ void chunk_direct(const GemmParams& p, const uint32_t
 // (2-byte outputs) or 128-byte (4-byte outputs) swizzle expects: row r at r * pitch, its 16-byte piece j at
 // piece j ^ f(r). Eight consecutive lanes then hit eight different bank groups.
 // 2-byte outputs: the chunk's 32 values of this lane's row, computed and packed (no shared-memory traffic yet)
-template <typename OutT, int EPI, int VS = 128>
+template <typename OutT, int EPI, int VS = 128, int KIND = 0>
 __device__ __forceinline__ void chunk_compute16(const GemmParams& p, const uint32_t (&r)[32], int row, int col0, float xs_r,
                                                 const float* vs, uint4 (&pk)[4], const uint16_t* lut_sm = nullptr) {
 #pragma unroll
@@ -295,7 +304,7 @@ __device__ __forceinline__ void chunk_compute16(const GemmParams& p, const uint3
             pk[j] = epilogue8_lut<VS>(p, r + 8 * j, xs_r, vs + 8 * j, lut_sm);
         } else {
             float y[8];
-            epilogue8<OutT, EPI, VS>(p, r + 8 * j, row, col0 + 8 * j, xs_r, p.vec_ok && col0 + 8 * j + 8 <= p.N, y, vs + 8 * j, lut_sm);
+            epilogue8<OutT, EPI, VS, KIND>(p, r + 8 * j, row, col0 + 8 * j, xs_r, p.vec_ok && col0 + 8 * j + 8 <= p.N, y, vs + 8 * j, lut_sm);
             if constexpr (sizeof(OutT) == 2) pk[j] = pack8<OutT>(y);
         }
     }
@@ -307,7 +316,7 @@ __device__ __forceinline__ void chunk_write16(const uint4 (&pk)[4], uint8_t* sta
     for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(rowp + ((j ^ sw) << 4)) = pk[j];
 }
 
-template <typename OutT, int EPI>
+template <typename OutT, int EPI, int KIND = 0>
 __device__ __forceinline__ void chunk_to_smem(const GemmParams& p, const uint32_t (&r)[32], int row, int col0, float xs_r,
                                               uint8_t* stage, int lane) {
     constexpr int kEsz = EPI == EPI_ACC ? 4 : (int)sizeof(OutT);
@@ -323,7 +332,7 @@ __device__ __forceinline__ void chunk_to_smem(const GemmParams& p, const uint32_
 #pragma unroll
                 for (int e = 0; e < 8; ++e) y[e] = __uint_as_float(r[8 * j + e]);  // raw int32 bits
             } else {
-                epilogue8<OutT, EPI>(p, r + 8 * j, row, col0 + 8 * j, xs_r, p.vec_ok && col0 + 8 * j + 8 <= p.N, y);
+                epilogue8<OutT, EPI, 128, KIND>(p, r + 8 * j, row, col0 + 8 * j, xs_r, p.vec_ok && col0 + 8 * j + 8 <= p.N, y);
             }
             *reinterpret_cast<float4*>(rowp + (((2 * j) ^ sw) << 4)) = make_float4(y[0], y[1], y[2], y[3]);
             *reinterpret_cast<float4*>(rowp + (((2 * j + 1) ^ sw) << 4)) = make_float4(y[4], y[5], y[6], y[7]);
@@ -343,7 +352,7 @@ template <int N> __device__ __forceinline__ void bulk_wait_read() {
 }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
-template <typename OutT, int EPI>
+template <typename OutT, int EPI, int KIND = 0>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                     const __grid_constant__ CUtensorMap tmap_d, const GemmParams p) {
@@ -460,16 +469,16 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         if (!mbar_wait(bar_f, phase, abort_s, ST_TIMEOUT_FULL)) { ok = false; break; }
                     }
                     {
-                        umma_i8_pair_lo(d_tmem, a_lo, b_lo, idesc, kb);
-                        umma_i8_pair_lo(d_tmem, a_lo + 2, b_lo + 2, idesc, 1);   // +32 bytes inside the swizzle row
-                        umma_i8_pair_lo(d_tmem, a_lo + 4, b_lo + 4, idesc, 1);
-                        umma_i8_pair_lo(d_tmem, a_lo + 6, b_lo + 6, idesc, 1);
+                        umma_pair_lo<KIND>(d_tmem, a_lo, b_lo, idesc, kb);
+                        umma_pair_lo<KIND>(d_tmem, a_lo + 2, b_lo + 2, idesc, 1);   // +32 bytes inside the swizzle row
+                        umma_pair_lo<KIND>(d_tmem, a_lo + 4, b_lo + 4, idesc, 1);
+                        umma_pair_lo<KIND>(d_tmem, a_lo + 6, b_lo + 6, idesc, 1);
                         if (KS == 2) {
                             const uint32_t a2 = a_lo + a_sub, b2 = b_lo + b_sub;
-                            umma_i8_pair_lo(d_tmem, a2, b2, idesc, 1);
-                            umma_i8_pair_lo(d_tmem, a2 + 2, b2 + 2, idesc, 1);
-                            umma_i8_pair_lo(d_tmem, a2 + 4, b2 + 4, idesc, 1);
-                            umma_i8_pair_lo(d_tmem, a2 + 6, b2 + 6, idesc, 1);
+                            umma_pair_lo<KIND>(d_tmem, a2, b2, idesc, 1);
+                            umma_pair_lo<KIND>(d_tmem, a2 + 2, b2 + 2, idesc, 1);
+                            umma_pair_lo<KIND>(d_tmem, a2 + 4, b2 + 4, idesc, 1);
+                            umma_pair_lo<KIND>(d_tmem, a2 + 6, b2 + 6, idesc, 1);
                         }
                     }
                     umma_commit_pair(bar_e);   // the stage is free in both CTAs once these MMAs have read it
@@ -506,7 +515,7 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const int row = row0 + lane;
             const bool row_ok = row < p.M;
             const int rrow = row_ok ? row : p.M - 1;     // rows past M compute on the last row; their output is clipped
-            const float xs_r = EPI != EPI_ACC ? p.xs[rrow] : 0.f;
+            const float xs_r = EPI == EPI_ACC ? 0.f : p.xs ? p.xs[rrow] : 1.f;
             const bool staged = kStageVec && p.tma_store;
             if (staged) {
                 // this warp's columns of ws / bias / rscale, fetched while the mainloop still runs
@@ -518,7 +527,7 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     my_vec[32 * k + lane] = in ? p.ws[n] : 0.f;
                     my_vec[128 + 32 * k + lane] = (in && p.bias) ? to_f<OutT>(reinterpret_cast<const OutT*>(p.bias)[n]) : 0.f;
                     if (EPI == EPI_RESID)
-                        my_vec[256 + 32 * k + lane] = in ? to_f<OutT>(reinterpret_cast<const OutT*>(p.rscale)[n]) : 0.f;
+                        my_vec[256 + 32 * k + lane] = !in ? 0.f : p.rscale ? to_f<OutT>(reinterpret_cast<const OutT*>(p.rscale)[n]) : 1.f;
                 }
                 __syncwarp();
             }
@@ -533,14 +542,14 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 if (p.tma_store) {
                     if constexpr (kStageVec) {
                         uint4 pk[4];
-                        chunk_compute16<OutT, EPI>(p, r, rrow, col0, xs_r, my_vec + 32 * ((c - half) >> 1), pk, lut_sm);
+                        chunk_compute16<OutT, EPI, 128, KIND>(p, r, rrow, col0, xs_r, my_vec + 32 * ((c - half) >> 1), pk, lut_sm);
                         if (lane == 0) bulk_wait_read<0>();   // the previous chunk's store has read the buffer
                         __syncwarp();
                         chunk_write16(pk, my_stage, lane);
                     } else {
                         if (lane == 0) bulk_wait_read<0>();
                         __syncwarp();
-                        chunk_to_smem<OutT, EPI>(p, r, rrow, col0, xs_r, my_stage, lane);
+                        chunk_to_smem<OutT, EPI, KIND>(p, r, rrow, col0, xs_r, my_stage, lane);
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
@@ -549,7 +558,7 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         bulk_commit();
                     }
                 } else if (row_ok) {
-                    chunk_direct<OutT, EPI>(p, r, row, col0, xs_r);
+                    chunk_direct<OutT, EPI, KIND>(p, r, row, col0, xs_r);
                 }
             };
             if (wi.kind == ITEM_WHOLE) {
@@ -727,10 +736,10 @@ int device_sm_count(int dev) {
     return c;
 }
 
-template <typename OutT, int EPI>
+template <typename OutT, int EPI, int KIND = 0>
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& td, const GemmParams& p, int grid,
                 cudaStream_t st) {
-    auto kern = gemm_i8_pair_kernel<OutT, EPI>;
+    auto kern = gemm_i8_pair_kernel<OutT, EPI, KIND>;
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -914,6 +923,61 @@ int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const f
     return rc;
 }
 
+// ---- weight-only int8 linear (the text encoders' path) ---------------------------------------------------------------
+// int8 codes are exact in bf16, so W goes to the tensor cores as bf16 without loss; the f32 activation goes as two bf16
+// terms (hi + lo = 16 significant bits), one GEMM pass each into f32 accumulators: close to an fp32 product at tensor-core
+// speed. The kernel is the int8 one with kind::f16 MMAs (bf16 operands are addressed as rows of 2 K bytes).
+__global__ void __launch_bounds__(256) widen_i8_bf16_kernel(const int8_t* __restrict__ q, bf16* __restrict__ out, int64_t n16) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n16) return;
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(q) + i);
+    const int8_t* b = reinterpret_cast<const int8_t*>(&v);
+    __nv_bfloat162 o[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = __floats2bfloat162_rn((float)b[2 * e], (float)b[2 * e + 1]);
+    reinterpret_cast<uint4*>(out)[2 * i] = *reinterpret_cast<const uint4*>(&o[0]);
+    reinterpret_cast<uint4*>(out)[2 * i + 1] = *reinterpret_cast<const uint4*>(&o[4]);
+}
+
+// D[M,N] (f32) = [resid +] (A[M,K] . W[N,K]^T) * ws[n], A and W bf16 row-major, K % 8 == 0, 16-byte aligned.
+int run_gemm_bf16(bool add, const void* A, const void* W, const float* ws, float* D, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
+    if (M == 0 || N == 0 || K == 0) return 0;
+    if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX / 2) return -200;
+    if ((K % 8) != 0 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((uintptr_t)D & 15)) return -202;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int clusters = device_sm_count(dev) / 2;
+    if (const int lim = g_cluster_limit.load(std::memory_order_relaxed); lim > 0 && lim < clusters) clusters = lim;
+    const int64_t Kb = 2 * K;                                   // bytes per row
+    GemmParams p{};
+    p.xs = nullptr, p.ws = ws, p.bias = nullptr, p.rscale = nullptr, p.resid = add ? D : nullptr, p.D = D;
+    p.M = (int)M, p.N = (int)N, p.K = (int)Kb;
+    auto al16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
+    p.vec_ok = (N % 8 == 0) && al16(ws);
+    p.tma_store = (N * 4) % 16 == 0;
+    p.ksub = Kb <= BK ? 1 : 2;
+    p.k_iters = (int)((Kb + p.ksub * BK - 1) / (p.ksub * BK));
+    const int bn = choose_bn(M, N, clusters);
+    p.bn = bn;
+    p.idesc = umma_idesc_bf16(2 * BM, bn);
+    const int stage_bytes = p.ksub * (BM * BK + (bn / 2) * BK);
+    const int stages = (kSmemBytes - 1024 - kTailBytes - kStagingBytes) / stage_bytes;
+    p.stages = stages > kMaxStages ? kMaxStages : stages;
+    p.tiles_m = (int)((M + 2 * BM - 1) / (2 * BM));
+    p.tiles_n = (int)((N + bn - 1) / bn);
+    p.num_tiles = p.tiles_m * p.tiles_n;
+    p.whole_tiles = p.num_tiles, p.splits = 0, p.kps = p.k_iters, p.num_items = p.num_tiles;
+    CUtensorMap ta, tw, td;
+    if (!make_operand_tmap(&ta, A, M, Kb, BM) || !make_operand_tmap(&tw, W, N, Kb, bn / 2)) return -203;
+    if (p.tma_store) {
+        if (!make_output_tmap(&td, D, M, N, 4)) return -203;
+    } else {
+        td = ta;
+    }
+    const int grid = 2 * (p.num_items < clusters ? p.num_items : clusters);
+    return add ? launch_pair<float, EPI_RESID, 1>(ta, tw, td, p, grid, st) : launch_pair<float, EPI_PLAIN, 1>(ta, tw, td, p, grid, st);
+}
+
 #include "gemm_w6.inl"
 
 }  // namespace
@@ -944,6 +1008,33 @@ GPU_API int gpu_w6a8_gemm_act(const int8_t* A, const uint8_t* Wq6, const uint8_t
 GPU_API int gpu_w6a8_gemm_acc_i32(const int8_t* A, const uint8_t* Wq6, const uint8_t* s_rel, int32_t* D, int64_t M,
                                   int64_t N, int64_t K, int G, void* stream) {
     return run_w6_gemm(EPI_ACC, A, Wq6, s_rel, nullptr, nullptr, nullptr, nullptr, nullptr, D, M, N, K, G, 0, (cudaStream_t)stream);
+}
+
+// New: the weight-only int8 linear of the text encoders in one call. The reference rotates the f32 activation rows
+// (gpu_rotate_rows_f32, csrc/kernels.cu:316-327), dequantizes the whole int8 weight to f32 (gpu_dequant_i8, :330-343) and runs
+// an fp32 GEMM with beta 0 or 1 (src/te.rs:493-511). Here: out[M,N] = beta * out + R256(prologue(x)) . (Wq * ws[n])^T with the
+// product on the bf16 tensor cores: Wq widens to bf16 exactly, the rotated rows go as hi + lo bf16 terms (two passes, f32
+// accumulation), so the result is within about 2^-16 relative of the fp32 product's terms.
+//   prologue   PRO_PLAIN, PRO_RMS (norm_w, eps) or PRO_SWIGLU (up_offset) as gpu_rotate_rows_f32 takes them
+//   a_scratch  >= 4 * M * K bytes (the reference's rotated-rows buffer has that size), w_scratch >= 2 * N * K bytes
+//              (half of the reference's dequantized-weight buffer); both 16-byte aligned
+//   beta       0 or 1 (-207 otherwise); K % 256 == 0 (-1); N * 4 bytes a multiple of 16 for the fast store path
+GPU_API int gpu_wo8_linear(int prologue, const float* x, int64_t x_stride, int64_t up_offset, const float* norm_w, float eps,
+                           const int8_t* Wq, const float* ws, float* out, float beta, void* a_scratch, void* w_scratch, int M,
+                           int N, int K, void* stream) {
+    if ((K % 256) != 0) return -1;
+    if (beta != 0.f && beta != 1.f) return -207;
+    if (M <= 0 || N <= 0) return 0;
+    if ((((uintptr_t)a_scratch | (uintptr_t)w_scratch | (uintptr_t)Wq) & 15) || !a_scratch || !w_scratch) return -202;
+    cudaStream_t st = (cudaStream_t)stream;
+    uint8_t* hi = reinterpret_cast<uint8_t*>(a_scratch);
+    uint8_t* lo = hi + (size_t)M * K * 2;
+    if (int rc = rotate_rows_split(prologue, x, x_stride, up_offset, norm_w, eps, hi, lo, M, K, st)) return rc;
+    const int64_t n16 = (int64_t)N * K / 16;
+    widen_i8_bf16_kernel<<<(unsigned)((n16 + 255) / 256), 256, 0, st>>>(Wq, reinterpret_cast<bf16*>(w_scratch), n16);
+    KCHECK();
+    if (int rc = run_gemm_bf16(beta == 1.f, hi, w_scratch, ws, out, M, N, K, st)) return rc;
+    return run_gemm_bf16(true, lo, w_scratch, ws, out, M, N, K, st);
 }
 
 // D[M,N] = (A[M,K] . W[N,K]^T) * xs[m] * ws[n] + bias[n]; replaces the reference's csrc/gemm.cu:123-129.

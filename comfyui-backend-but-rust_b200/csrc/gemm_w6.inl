@@ -161,10 +161,10 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 #pragma unroll
                     for (int h = 0; h < MH; ++h) {
                         const uint32_t dh = d_tmem + h * 128, ah = a_lo + h * (a_box >> 4);
-                        umma_i8_pair_lo(dh, ah, b_lo, idesc, kb);
-                        umma_i8_pair_lo(dh, ah + 2, b_lo + 2, idesc, 1);
-                        umma_i8_pair_lo(dh, ah + 4, b_lo + 4, idesc, 1);
-                        umma_i8_pair_lo(dh, ah + 6, b_lo + 6, idesc, 1);
+                        umma_pair_lo<0>(dh, ah, b_lo, idesc, kb);
+                        umma_pair_lo<0>(dh, ah + 2, b_lo + 2, idesc, 1);
+                        umma_pair_lo<0>(dh, ah + 4, b_lo + 4, idesc, 1);
+                        umma_pair_lo<0>(dh, ah + 6, b_lo + 6, idesc, 1);
                     }
                     umma_commit_pair(bar_bempty + 8 * sb);
                     umma_commit_pair(bar_aempty + 8 * sa);

@@ -83,6 +83,9 @@ struct QuantArgs {
     // shared-memory plan (byte offsets from the dynamic shared memory base), filled in by launch_quant
     int staged;             // rows arrive through the staging buffer (bulk copies) instead of direct loads
     uint32_t off_amax, off_norm, off_stage, off_bar;
+    // when set (with out_f unset): the rotated fp32 rows leave as two bf16 rows, hi = bf16(v) and lo = bf16(v - hi)
+    bf16* out_hi;
+    bf16* out_lo;
 };
 
 template <int PRO> __host__ __device__ constexpr bool is_ln() { return PRO == PRO_LAYERNORM || PRO == PRO_LN_MOD || PRO == PRO_LN_AFFINE; }
@@ -459,6 +462,20 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 384 ? 2 : 1) quant_rows_kernel(c
             for (int i = 0; i < 16; ++i) P[i] = make_float2(v[2 * i], v[2 * i + 1]);   // natural order
         }
 
+        if (p.out_hi) {  // the weight-only linear's activation side: rotated rows split into two bf16 terms
+            if (live) {
+                const int64_t o = m * (int64_t)p.K + (grp << 8) + 2 * t8;
+#pragma unroll
+                for (int r = 0; r < 16; ++r) {
+                    const float2 v2 = tsw ? make_float2(P[r].y, P[r].x) : P[r];
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(v2.x, v2.y);
+                    const float2 hf = __bfloat1622float2(h);
+                    *reinterpret_cast<__nv_bfloat162*>(p.out_hi + o + 16 * r) = h;
+                    *reinterpret_cast<__nv_bfloat162*>(p.out_lo + o + 16 * r) = __floats2bfloat162_rn(__fsub_rn(v2.x, hf.x), __fsub_rn(v2.y, hf.y));
+                }
+            }
+            continue;
+        }
         if (p.out_f) {   // gpu_rotate_rows_f32: always rotated, so P holds (2 t8, 2 t8 + 1) + 16 r
             if (live) {
                 float* o = p.out_f + m * (int64_t)p.K + (grp << 8) + 2 * t8;
@@ -879,7 +896,7 @@ int launch_quant(QuantArgs& p, cudaStream_t st) {
     const uintptr_t mis = (uintptr_t)p.x | (uintptr_t)(p.x_stride * sizeof(T)) |
                           (PRO == PRO_GATE ? (uintptr_t)p.g | (uintptr_t)(p.g_stride * sizeof(T)) : 0) |
                           (has_aux<PRO>() && PRO != PRO_GATE ? (uintptr_t)(p.up_offset * sizeof(T)) : 0) | (uintptr_t)p.q |
-                          (uintptr_t)p.out_f;
+                          (uintptr_t)p.out_f | (uintptr_t)p.out_hi | (uintptr_t)p.out_lo;
     if (mis & 15) return -5;
     int lut = -1;
     if (sizeof(T) == 2 && (int64_t)p.M * p.K >= (1 << 20)) {
@@ -977,6 +994,22 @@ GPU_API int gpu_rotate_rows_f32(int prologue, const float* x, int64_t x_stride, 
         case PRO_PLAIN: return launch_quant<float, PRO_PLAIN>(p, (cudaStream_t)stream);
         case PRO_RMS: return launch_quant<float, PRO_RMS>(p, (cudaStream_t)stream);
         case PRO_SWIGLU: return launch_quant<float, PRO_SWIGLU>(p, (cudaStream_t)stream);
+        default: return -3;
+    }
+}
+
+// The same with the rotated rows written as two bf16 terms (hi + lo carries 16 significant bits of every value): the
+// A operand of the weight-only int8 linear on the bf16 tensor-core kernel.
+int b200q::rotate_rows_split(int prologue, const float* x, int64_t x_stride, int64_t up_offset, const float* norm_w, float eps,
+                             void* hi, void* lo, int M, int K, cudaStream_t st) {
+    if ((K % 256) != 0) return -1;
+    QuantArgs p{x, x_stride, nullptr, 0, up_offset, nullptr, nullptr, nullptr, M, K, 1, 0, 0, 0, -1, nullptr, nullptr,
+                norm_w, nullptr, eps, nullptr, nullptr};
+    p.out_hi = reinterpret_cast<bf16*>(hi), p.out_lo = reinterpret_cast<bf16*>(lo);
+    switch (prologue) {
+        case PRO_PLAIN: return launch_quant<float, PRO_PLAIN>(p, st);
+        case PRO_RMS: return launch_quant<float, PRO_RMS>(p, st);
+        case PRO_SWIGLU: return launch_quant<float, PRO_SWIGLU>(p, st);
         default: return -3;
     }
 }

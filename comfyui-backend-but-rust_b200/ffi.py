@@ -43,6 +43,7 @@ SIGNATURES = {
     "gpu_quant_rows_amax": [i32, i32, P, i64, P, i64, i64, P, i32, i32, i32, P],
     "gpu_quant_rows_scaled": [i32, i32, P, i64, P, i64, i64, P, P, P, i32, i32, i32, P],
     "gpu_int8_epilogue": [P, P, P, P, P, P, P, i64, i64, i32, i32, P],
+    "gpu_wo8_linear": [i32, P, i64, i64, P, f32, P, P, P, f32, P, P, i32, i32, i32, P],
     "gpu_bias_residual_add": [P, P, P, P, i64, i64, i64, i64, i32, P],
     "gpu_int8_gemm_set_cluster_limit": [i32],
     "gpu_w6_decode": [P, P, P, i64, i32, i32, P],

@@ -122,6 +122,23 @@ def rotate_rows_f32(x: torch.Tensor, prologue: int = ffi.PRO_PLAIN, *, K: Option
     return out
 
 
+def wo8_linear(x: torch.Tensor, Wq: torch.Tensor, ws: torch.Tensor, prologue: int = ffi.PRO_PLAIN, *, K: Optional[int] = None,
+               up_offset: int = 0, norm_w: Optional[torch.Tensor] = None, eps: float = 0.0, out: Optional[torch.Tensor] = None,
+               beta: float = 0.0, scratch: Optional[tuple] = None):
+    """gpu_wo8_linear: the text encoders' weight-only int8 linear, out = beta * out + R256(prologue(x)) @ (Wq * ws)^T in f32.
+    `scratch` = (a_scratch >= 4 M K bytes, w_scratch >= 2 N K bytes), allocated here when not given."""
+    _cuda(x)
+    M = x.shape[0]
+    K = K if K is not None else x.shape[1]
+    N = Wq.shape[0]
+    out = out if out is not None else torch.empty((M, N), dtype=torch.float32, device=x.device)
+    a_s, w_s = scratch if scratch is not None else (torch.empty(4 * M * K, dtype=torch.uint8, device=x.device),
+                                                    torch.empty(2 * N * K, dtype=torch.uint8, device=x.device))
+    ok(_lib().gpu_wo8_linear(prologue, _ptr(x), x.stride(0), up_offset, _ptr(norm_w), eps, _ptr(Wq), _ptr(ws), _ptr(out), beta,
+                             _ptr(a_s), _ptr(w_s), M, N, K, _stream()), "gpu_wo8_linear")
+    return out
+
+
 def sd_quant_rows(x: torch.Tensor, rotate: int = 0):
     """gpu_sd_quant_rows: fp16 rows (activations, or weights at load) -> (q int8, scales f32)."""
     _cuda(x)

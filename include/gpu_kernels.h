@@ -142,6 +142,17 @@ int gpu_quant_rows_scaled(int dtype, int prologue, const void* x, int64_t x_stri
 int gpu_int8_epilogue(const int32_t* acc, const float* xs, const float* ws, const void* bias, const void* rscale,
                       const void* resid, void* D, int64_t M, int64_t N, int out_dt, int act, void* stream);
 
+/* New: the weight-only int8 linear of the text encoders in one call. The reference runs gpu_rotate_rows_f32
+ * (csrc/kernels.cu:316-327), dequantizes the whole weight with gpu_dequant_i8 (:330-343) and calls an fp32 GEMM with beta 0
+ * or 1 (src/te.rs:493-511); this computes out[M,N] = beta * out + R256(prologue(x)) . (Wq * ws[n])^T on the bf16 tensor
+ * cores: Wq [N,K] int8 widens to bf16 exactly, the rotated f32 rows go as two bf16 terms (hi + lo) in two accumulating
+ * passes, f32 accumulators. prologue PLAIN, RMS (norm_w, eps) or SWIGLU (up_offset) as for gpu_rotate_rows_f32 (-3).
+ * a_scratch >= 4*M*K bytes, w_scratch >= 2*N*K bytes, 16-byte aligned (-202); beta 0 or 1 (-207); K % 256 == 0 (-1).
+ * Result: within 1e-5 of the largest output of the fp32 flow (tests state the bound). */
+int gpu_wo8_linear(int prologue, const float* x, int64_t x_stride, int64_t up_offset, const float* norm_w, float eps,
+                   const int8_t* Wq, const float* ws, float* out, float beta, void* a_scratch, void* w_scratch, int M, int N,
+                   int K, void* stream);
+
 /* New (tensor parallelism): the tail of a row-parallel linear whose dequantized partial outputs were summed across
  * devices: out[:, n0:n0+Nc] = T(T(y + bias[n0:n0+Nc]) + resid[:, n0:n0+Nc]); y [M, Nc] contiguous, resid / out [M, ld]
  * (out may alias resid), bias and resid nullable, all in the activation dtype dt. Nc, n0, ld multiples of 8 and
