@@ -81,10 +81,26 @@ def _setup_hbm(name, b, torch, dev, wl, I):
         b.hs = (torch.rand(1, generator=g, device=dev) * 0.01, torch.rand(N, generator=g, device=dev) * 1e-3, rnd(N).bfloat16())
         b.hd = torch.empty((1, N), dtype=torch.bfloat16, device=dev)
         return N * K + K + 4 + 4 * N + 2 * N + 2 * N
+    if name in ("wo8_linear", "wo8_fp32_flow"):                  # a text-encoder MLP-up linear: 512 tokens, 2560 -> 19456
+        M, K, N = 512, 2560, 19456
+        b.tx = rnd(M, K)
+        b.tw = I.convrot_requant(rnd(N, K) * 0.03, 0)
+        b.tout = torch.empty((M, N), dtype=torch.float32, device=dev)
+        b.tscr = (torch.empty(4 * M * K, dtype=torch.uint8, device=dev), torch.empty(2 * N * K, dtype=torch.uint8, device=dev))
+        return None
     raise KeyError(name)
 
 
+def _fp32_flow(b, I):
+    """The reference's arrangement of the weight-only linear: rotate, dequantize the whole weight to f32, fp32 GEMM (a library
+    GEMM stands in for its cuBLASLt call: a baseline beside gpu_wo8_linear, not part of the product path)."""
+    import torch
+    torch.matmul(I.rotate_rows_f32(b.tx), I.dequant_i8(*b.tw).t(), out=b.tout)
+
+
 HBM_KERNELS = {
+    "wo8_linear": lambda b, I: I.wo8_linear(b.tx, b.tw[0], b.tw[1], out=b.tout, scratch=b.tscr),
+    "wo8_fp32_flow": _fp32_flow,
     "pack_f32": lambda b, I: I.convrot_requant(b.hw, 0),
     "pack_bf16": lambda b, I: I.convrot_requant(b.hw, 0),
     "sd_quant": lambda b, I: I.sd_quant_rows(b.hx, 256),
@@ -109,6 +125,7 @@ def parse_args():
     ap.add_argument("--unfused-gelu", action="store_true",
                     help="the reference's arrangement: plain GEMM epilogue, GELU-tanh in the next quantizer's prologue")
     ap.add_argument("--no-stack", action="store_true", help="skip the 60-block stack record")
+    ap.add_argument("--settle-s", type=float, default=SETTLE_S, help="seconds of untimed back-to-back load before the timed steps")
     ap.add_argument("--stack-blocks", type=int, default=60)
     return ap.parse_args()
 
@@ -470,17 +487,18 @@ def main():
         blk.step()
     torch.cuda.synchronize()
     t_settle, settle_steps = time.perf_counter(), 0
-    while time.perf_counter() - t_settle < SETTLE_S:
+    while time.perf_counter() - t_settle < args.settle_s:
         for _ in range(100):
             blk.step()
         torch.cuda.synchronize()
         settle_steps += 100
     ms = time_steps(torch, blk.step, args.steps, 0, barrier)
-    tail_ms = time_steps(torch, blk.step, max(args.steps, 300), 0)        # keeps the load up while the sampler takes its last samples
+    tail_n = max(args.steps, 300) if args.settle_s > 0 else args.steps
+    tail_ms = time_steps(torch, blk.step, tail_n, 0)                      # keeps the load up while the sampler takes its last samples
     clocks = sampler.stop() if rank == 0 else None
     if rank == 0:
-        clocks["source"] = (f"sampled over {settle_steps} untimed settling steps ({SETTLE_S} s), the {args.steps} timed steps "
-                            f"and {max(args.steps, 300)} more steps right after them ({tail_ms / max(args.steps, 300):.4f} ms per step)")
+        clocks["source"] = (f"sampled over {settle_steps} untimed settling steps ({args.settle_s} s), the {args.steps} timed steps "
+                            f"and {tail_n} more steps right after them ({tail_ms / tail_n:.4f} ms per step)")
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -604,7 +622,7 @@ def main():
             "config": dict(CONFIG),
             "run": {"sharding": "tokens (replicated weights), no data-path collective", "fused_gelu_epilogue": fused,
                     "l2": "working set per step ~300 MB exceeds the 126 MB L2",
-                    "settle": f"{settle_steps} untimed steps ({SETTLE_S} s) directly before the timed ones: value is the power-capped, sustained rate"},
+                    "settle": f"{settle_steps} untimed steps ({args.settle_s} s) directly before the timed ones: value is the power-capped, sustained rate"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
