@@ -5,8 +5,10 @@
 
 One step = one pass of the path over one batch of the ConvRot int8 MMDiT MLP pair (Qwen-Image-shaped block at
 1024x1024: M = 4352 tokens, 3072 -> 12288 with GELU-tanh, 12288 -> 3072 with the residual add):
-    quantize rows (rotate) -> int8 GEMM with the GELU-tanh epilogue -> quantize rows (rotate) -> int8 GEMM + residual epilogue
-(--unfused-gelu: the reference's arrangement, plain epilogue and the GELU in the next quantizer's prologue; same bits)
+    quantize rows (rotate) -> int8 GEMM whose epilogue applies GELU-tanh and the next quantizer's rotation -> the
+    quantizer's second pass (row maximum, scale, codes) -> int8 GEMM + residual epilogue
+(--act-epilogue: GELU in the epilogue, the whole quantizer after it; --unfused-gelu: the reference's arrangement, plain
+epilogue and the GELU in the next quantizer's prologue; all three give the same bits)
 Inputs are seeded synthetic tensors with the block's shapes and distributions (no checkpoint is available offline).
 
 Prints ONE JSON line. `value` is whole-job tera-ops/s (2*M*N*K per linear) with inputs resident in HBM; `e2e` is the
@@ -47,6 +49,10 @@ KERNELS = {
     "quant_gelu": lambda b, I: I.quant_rows(b.h, 11, 1, q=b.a2, scales=b.xs2),           # the same with the GELU-tanh prologue
     "quant_in": lambda b, I: I.quant_rows(b.x, 0, 1, q=b.a1, scales=b.xs1),              # M=4352 K=3072
     "gemm_up": lambda b, I: I.int8_gemm(b.a1, b.w1, b.xs1, b.s1, b.b1, out=b.h),         # M=4352 K=3072 N=12288
+    "gemm_up_act": lambda b, I: I.int8_gemm(b.a1, b.w1, b.xs1, b.s1, b.b1, act=1, out=b.h),
+    # the activation and the rotation in the epilogue, and the quantizer pass that is left after it
+    "gemm_up_rot": lambda b, I: I.int8_gemm_act_rot(b.a1, b.w1, b.xs1, b.s1, b.b1, act=1, out=b.h, amax_part=b.parts),
+    "quant_rotated": lambda b, I: I.quant_rows_rotated(b.h, b.parts, q=b.a2, scales=b.xs2),
     "gemm_down": lambda b, I: I.int8_gemm(b.a2, b.w2, b.xs2, b.s2, b.b2, rscale=b.ones, resid=b.x, out=b.out),
     # the up-projection with its weight in W6 storage (fitted group scales / s_rel = 1), unpacked inside the GEMM
     "w6a8_up": lambda b, I: I.w6a8_gemm(b.a1, b.w6[0], b.w6[1], b.xs1, b.w6[2], b.b1, out=b.h),
@@ -124,6 +130,9 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--unfused-gelu", action="store_true",
                     help="the reference's arrangement: plain GEMM epilogue, GELU-tanh in the next quantizer's prologue")
+    ap.add_argument("--act-epilogue", action="store_true",
+                    help="GELU-tanh in the up-projection's epilogue but the rotation in the quantizer (gpu_int8_gemm_act, then "
+                         "gpu_quant_rows) instead of both in the epilogue (gpu_int8_gemm_act_rot, then gpu_quant_rows_rotated)")
     ap.add_argument("--no-stack", action="store_true", help="skip the 60-block stack record")
     ap.add_argument("--settle-s", type=float, default=SETTLE_S, help="seconds of untimed back-to-back load before the timed steps")
     ap.add_argument("--stack-blocks", type=int, default=60)
@@ -195,8 +204,8 @@ class Block:
     """Device state of one MLP pair and the four kernel launches of a step, through `impl` (the product's
     host layer, or the binding of the reference's CUDA kernels: both expose the same calls)."""
 
-    def __init__(self, impl, torch, dev, up, down, x, w1, w2, b1, b2, fused_gelu: bool):
-        self.impl, self.torch, self.fused_gelu = impl, torch, fused_gelu
+    def __init__(self, impl, torch, dev, up, down, x, w1, w2, b1, b2, fused_gelu: bool, rot_epilogue: bool = False):
+        self.impl, self.torch, self.fused_gelu, self.rot_epilogue = impl, torch, fused_gelu, rot_epilogue
         self.up, self.down = up, down
         self.x = x.to(dev)
         # quantize-at-load: f32 weights -> R256 -> int8 + per-channel scale (seed 0 = nearest)
@@ -208,6 +217,7 @@ class Block:
         self.a1 = torch.empty((M, up.K), dtype=torch.int8, device=dev)
         self.xs1 = torch.empty((M,), dtype=torch.float32, device=dev)
         self.h = torch.empty((M, up.N), dtype=torch.bfloat16, device=dev)
+        self.parts = torch.empty((M, up.N // 64), dtype=torch.float32, device=dev)
         self.a2 = torch.empty((M, down.K), dtype=torch.int8, device=dev)
         self.xs2 = torch.empty((M,), dtype=torch.float32, device=dev)
         self.out = torch.empty((M, down.N), dtype=torch.bfloat16, device=dev)
@@ -218,7 +228,10 @@ class Block:
         x = self.x if x is None else x
         out = self.out if out is None else out
         I.quant_rows(x, 0, 1, q=self.a1, scales=self.xs1)
-        if self.fused_gelu:
+        if self.rot_epilogue:
+            I.int8_gemm_act_rot(self.a1, self.w1, self.xs1, self.s1, self.b1, act=1, out=self.h, amax_part=self.parts)
+            I.quant_rows_rotated(self.h, self.parts, q=self.a2, scales=self.xs2)
+        elif self.fused_gelu:
             I.int8_gemm(self.a1, self.w1, self.xs1, self.s1, self.b1, act=1, out=self.h)
             I.quant_rows(self.h, 0, 1, q=self.a2, scales=self.xs2)
         else:   # the reference's arrangement: plain epilogue, GELU in the next quantizer's prologue
@@ -439,8 +452,11 @@ def main():
 
     # token-sharded replicas: every rank owns one batch of the block (weights replicated), no data-path collective
     up, down, x, w1, w2, b1, b2 = host_inputs(wl, rank)
-    blk = Block(impl, torch, dev, up, down, x, w1, w2, b1, b2, fused)
+    rot = fused and not args.act_epilogue and args.impl != "reference-gpu"
+    blk = Block(impl, torch, dev, up, down, x, w1, w2, b1, b2, fused, rot)
     if args.mode == "kernel":
+        # the rotated rows and their partial maxima in h / parts for the second pass; the GELU output for the others
+        blk.rot_epilogue = args.kernel == "quant_rotated"
         blk.step()                                   # fills every buffer the single kernels read
         if args.kernel.startswith("w6a8"):
             blk.w6 = tuple(t.to(dev) for t in wl.w6_pack(w1, True))
@@ -600,27 +616,35 @@ def main():
 
     if rank != 0:
         return
-    # roofline of the dominant kernel: the up-projection GEMM alone, CUDA events over back-to-back launches
+    # roofline of the dominant kernel: the up-projection GEMM alone, as the step runs it, CUDA events over back-to-back launches
     def gemm_up():
-        impl.int8_gemm(blk.a1, blk.w1, blk.xs1, blk.s1, blk.b1, act=1 if fused else 0, out=blk.h)
+        if rot:
+            impl.int8_gemm_act_rot(blk.a1, blk.w1, blk.xs1, blk.s1, blk.b1, act=1, out=blk.h, amax_part=blk.parts)
+        else:
+            impl.int8_gemm(blk.a1, blk.w1, blk.xs1, blk.s1, blk.b1, act=1 if fused else 0, out=blk.h)
     k_ms = time_steps(torch, gemm_up, 20, 3) / 20
     plain_ms = time_steps(torch, lambda: impl.int8_gemm(blk.a1, blk.w1, blk.xs1, blk.s1, blk.b1, out=blk.h), 20, 3) / 20
+    act_ms = time_steps(torch, lambda: impl.int8_gemm(blk.a1, blk.w1, blk.xs1, blk.s1, blk.b1, act=1, out=blk.h), 20, 3) / 20 if fused else None
     bf16_burst, bf16_sust, hbm, src = measured_peaks()
     achieved = up.ops / (k_ms * 1e-3) / 1e12
     peak = 2.0 * bf16_burst                      # dense int8 runs at twice the dense bf16 rate on this part
-    roofline = {"bound": "tensor", "kernel": "gemm_i8_pair_kernel (mlp_up, M=4352 K=3072 N=12288, "
-                                             + ("GELU-tanh epilogue as in the step)" if fused else "plain epilogue)"), "achieved": achieved,
+    form = ("GELU-tanh and the next quantizer's R256 rotation in the epilogue, as in the step: the epilogue's table look-ups "
+            "and the tile loads share the SM's shared-memory bandwidth, so this kernel is slower than the plain one and the "
+            "quantizer after it 2.3x faster)" if rot else "GELU-tanh epilogue as in the step)" if fused else "plain epilogue)")
+    sub = lambda t: {"us_per_launch": t * 1e3, "achieved": up.ops / (t * 1e-3) / 1e12, "frac": up.ops / (t * 1e-3) / 1e12 / peak}
+    roofline = {"bound": "tensor", "kernel": "gemm_i8_pair_kernel (mlp_up, M=4352 K=3072 N=12288, " + form, "achieved": achieved,
                 "peak": peak, "unit": "TOPS", "frac": achieved / peak,
                 "peak_source": f"2 x {src} dense bf16 burst ({bf16_burst} TFLOP/s); no int8 figure is measured on this pool",
                 "frac_of_nominal_4500": achieved / INT8_NOMINAL_TOPS, "us_per_launch": k_ms * 1e3,
                 "traffic": profiled_dram_bytes(),
-                "plain_epilogue": {"us_per_launch": plain_ms * 1e3, "achieved": up.ops / (plain_ms * 1e-3) / 1e12,
-                                   "frac": up.ops / (plain_ms * 1e-3) / 1e12 / peak}}
+                "plain_epilogue": sub(plain_ms)}
+    if act_ms is not None:
+        roofline["act_epilogue"] = sub(act_ms)
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
             "data": "synthetic",
             "config": dict(CONFIG),
-            "run": {"sharding": "tokens (replicated weights), no data-path collective", "fused_gelu_epilogue": fused,
+            "run": {"sharding": "tokens (replicated weights), no data-path collective", "fused_gelu_epilogue": fused, "rotating_epilogue": rot,
                     "l2": "working set per step ~300 MB exceeds the 126 MB L2",
                     "settle": f"{settle_steps} untimed steps ({args.settle_s} s) directly before the timed ones: value is the power-capped, sustained rate"},
             "clocks": clocks,

@@ -7,8 +7,9 @@
 
 #include "common.cuh"
 
-// EPI_ACT computes the activation; EPI_ACT_LUT (tensor-core kernel, bf16 outputs) reads bf16(act(x)) from a table instead
-enum EpiMode { EPI_PLAIN = 0, EPI_RESID = 1, EPI_ACT = 2, EPI_ACC = 3, EPI_ACT_LUT = 4 };
+// EPI_ACT computes the activation; EPI_ACT_LUT (tensor-core kernel, bf16 outputs) reads bf16(act(x)) from a table instead;
+// EPI_ACT_ROT does that and rotates each 256-column group of the row (R256) before the store
+enum EpiMode { EPI_PLAIN = 0, EPI_RESID = 1, EPI_ACT = 2, EPI_ACC = 3, EPI_ACT_LUT = 4, EPI_ACT_ROT = 5 };
 enum Act { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_SILU = 2, ACT_GELU_ERF = 3 };
 
 template <typename OutT, int EPI>

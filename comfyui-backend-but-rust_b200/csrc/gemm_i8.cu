@@ -42,6 +42,8 @@ constexpr int BK = 128;        // int8 elements (= bytes) of K per TMA box: one 
 constexpr int UMMA_K = 32;     // K of one tcgen05.mma kind::i8
 constexpr int kThreads = 320;  // warp 0 producer, warp 1 MMA, warps 2-9 epilogue
 constexpr int kEpiWarps = 8;
+constexpr int kRotEpiWarps = 8;                      // epilogue warps of the rotating epilogue (two per tensor-memory lane quarter)
+constexpr int kRotThreads = 64 + 32 * kRotEpiWarps;
 constexpr int kMaxStages = 8;
 constexpr int kSmemBytes = 232448;            // the per-CTA maximum (227 KB)
 // Epilogue staging, 32 KB. 4-byte outputs: per warp 32 rows x 128 B. 2-byte outputs: per warp a 2 KB chunk buffer (32 rows x
@@ -49,7 +51,7 @@ constexpr int kSmemBytes = 232448;            // the per-CTA maximum (227 KB)
 // epilogue, the shared-memory part of the activation table behind them (16 + 8 + 8 KB).
 constexpr int kStagingBytes = kEpiWarps * 4096;
 constexpr int kVecOffset = kEpiWarps * 2048;                 // 2-byte outputs: vectors start behind the chunk buffers
-constexpr int kTailBytes = 256;               // barriers, tensor-memory pointer, abort flag
+constexpr int kTailBytes = 512;               // barriers, tensor-memory pointer, abort flag, the rotating epilogue's flags
 
 struct GemmParams {
     const float* xs;     // [M]
@@ -77,6 +79,8 @@ struct GemmParams {
     uint32_t idesc;      // instruction descriptor for M = 256, N = bn
     const uint16_t* act_lut;   // EPI_ACT with bf16 outputs: bf16(act(x)) for every bf16 x (a tanhf or erff per element
                                // made the epilogue, not the tensor core, the limit: 836 against 2740 TOPS), or null
+    float* amax_part;          // EPI_ACT_ROT: [M, N / 64] partial row maxima of |rotated value| (four per tile, see the
+                               // epilogue), sign bit set when the part held a NaN
 };
 
 // Tile order: bands of 8 row tiles, column tile fastest-varying across the band's rows, so that the clusters
@@ -148,7 +152,13 @@ template <> __device__ __forceinline__ void load8<half>(const half* p, float (&y
 // (ws at vs[0..], bias at vs[VS..], rscale at vs[2 VS..], all as f32, zero beyond N; VS = columns a warp stages).
 // The part of the 65536-entry activation table an epilogue keeps in shared memory: bf16 bit patterns of 2^-10 <= |x| < 64
 // (16 exponents x 128 significands), positive half first; anything else is read from the whole table in global memory.
+// Inside a half the entry of pattern b sits at b & 0x7ff (the window 0x3A80..0x427F wraps once), so the index needs no
+// subtraction: (b & 0x7ff) | (sign << 11).
 constexpr uint32_t kActLutLo = 0x3A80u, kActLutHalf = 16u * 128u;
+__host__ __device__ constexpr uint32_t act_lut_pattern(uint32_t i) {   // bf16 pattern whose entry sits at index i of the shared part
+    return ((i & 0x800u) << 4) | ((i & 0x7ffu) >= (kActLutLo & 0x7ffu) ? 0x3800u : 0x4000u) | (i & 0x7ffu);
+}
+__device__ __forceinline__ uint32_t act_lut_index(uint32_t b) { return (b & 0x7ffu) | ((b >> 4) & 0x800u); }
 constexpr int kActLutBytes = 2 * (int)kActLutHalf * 2;
 
 // Accumulator word -> float: int32 sums of the int8 kernel (KIND 0), or the f32 sums of the bf16 kernel (KIND 1) as they are.
@@ -210,9 +220,8 @@ __device__ __forceinline__ void epilogue8(const GemmParams& p, const uint32_t* r
             // bf16(act(v)) from the table: its hot part sits in shared memory, the rest is read from global memory
             // (a predicated load; the shared-memory index is masked into range either way)
             const uint32_t bits = __float_as_uint(v) >> 16;
-            const uint32_t u = bits - kActLutLo;
-            uint32_t t = lut_sm[(u & 0x7ffu) | ((u >> 4) & 0x800u)];                     // sign bit 15 -> the table's second half
-            if ((u & 0x7fffu) >= kActLutHalf) t = __ldg(p.act_lut + bits);
+            uint32_t t = lut_sm[act_lut_index(bits)];                                   // sign bit 15 -> the table's second half
+            if (((bits & 0x7fffu) - kActLutLo) >= kActLutHalf) t = __ldg(p.act_lut + bits);
             v = __uint_as_float(t << 16);
         } else if (EPI == EPI_ACT) {
             v = p.act == ACT_GELU_TANH ? gelu_tanh_f(v) : p.act == ACT_SILU ? silu_f(v) : gelu_f(v);
@@ -225,32 +234,109 @@ __device__ __forceinline__ void epilogue8(const GemmParams& p, const uint32_t* r
 // y = bf16(fma(float(acc) * xs, ws, bias)) is formed two at a time (one packed conversion), its 16 bits index the table
 // (hot part in shared memory, sign in the index's top bit), and the table's 16-bit entries are the output as they are:
 // no conversion back and forth. Values outside the shared-memory part (checked once per 8) are read from the whole table.
+// Out of line on purpose: inlined, its eight loads were issued (predicated off) by every group of eight and cost the
+// epilogue a tenth of its instructions.
+__device__ __noinline__ uint4 act_lut_whole8(const uint16_t* __restrict__ lut, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
+    const uint32_t w[4] = {w0, w1, w2, w3};
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = (uint32_t)__ldg(lut + (w[i] & 0xffffu)) | ((uint32_t)__ldg(lut + (w[i] >> 16)) << 16);
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+// t[e] = table entry (16 bits) for column e. Returns false when some entry came from the whole table (values outside the
+// shared-memory part: the caller may want to look at their size).
+template <int VS>
+__device__ __forceinline__ bool epilogue8_lut_bits(const GemmParams& p, const uint32_t* r, float xs_r, const float* vs,
+                                                   const uint16_t* lut_sm, uint32_t (&t)[8]) {
+    float w8[8], b8[8], v[8];
+    load8<float>(vs, w8);
+    load8<float>(vs + VS, b8);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[e]), xs_r), w8[e], b8[e]);
+    // inside the shared-memory part when 2^-10 <= |v| < 63.75 for all eight (rounding to bf16 then stays below 64); a NaN
+    // fails the comparison
+    float lo = fabsf(v[0]), hi = lo;
+#pragma unroll
+    for (int e = 1; e < 7; e += 2) {
+        asm("min.f32 %0, %1, %2, %3;" : "=f"(lo) : "f"(lo), "f"(fabsf(v[e])), "f"(fabsf(v[e + 1])));
+        asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(hi) : "f"(hi), "f"(fabsf(v[e])), "f"(fabsf(v[e + 1])));
+    }
+    lo = fminf(lo, fabsf(v[7]));
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(hi) : "f"(hi), "f"(fabsf(v[7])));
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t*>(&h);
+        t[2 * i] = lut_sm[act_lut_index(w[i])];
+        t[2 * i + 1] = lut_sm[act_lut_index(w[i] >> 16)];
+    }
+    const bool inside = lo >= 0.0009765625f && hi < 63.75f;
+    if (__all_sync(0xffffffffu, inside)) return true;
+    const uint4 o = act_lut_whole8(p.act_lut, w[0], w[1], w[2], w[3]);
+    t[0] = o.x & 0xffffu, t[1] = o.x >> 16, t[2] = o.y & 0xffffu, t[3] = o.y >> 16;
+    t[4] = o.z & 0xffffu, t[5] = o.z >> 16, t[6] = o.w & 0xffffu, t[7] = o.w >> 16;
+    return false;
+}
 template <int VS>
 __device__ __forceinline__ uint4 epilogue8_lut(const GemmParams& p, const uint32_t* r, float xs_r, const float* vs,
                                                const uint16_t* lut_sm) {
-    float w8[8], b8[8];
-    load8<float>(vs, w8);
-    load8<float>(vs + VS, b8);
-    uint32_t bits[8], t[8], worst = 0;
-#pragma unroll
-    for (int e = 0; e < 8; e += 2) {
-        const float v0 = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[e]), xs_r), w8[e], b8[e]);
-        const float v1 = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[e + 1]), xs_r), w8[e + 1], b8[e + 1]);
-        const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
-        const uint32_t w = *reinterpret_cast<const uint32_t*>(&h);
-        bits[e] = w & 0xffffu, bits[e + 1] = w >> 16;
-    }
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-        const uint32_t u = bits[e] - kActLutLo;
-        worst = max(worst, u & 0x7fffu);
-        t[e] = lut_sm[(u & 0x7ffu) | ((u >> 4) & 0x800u)];
-    }
-    if (worst >= kActLutHalf) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) t[e] = __ldg(p.act_lut + bits[e]);
-    }
+    uint32_t t[8];
+    epilogue8_lut_bits<VS>(p, r, xs_r, vs, lut_sm, t);
     return make_uint4(t[0] | (t[1] << 16), t[2] | (t[3] << 16), t[4] | (t[5] << 16), t[6] | (t[7] << 16));
+}
+
+// Radix-4 butterfly of the regular Hadamard block on f32 bit patterns, outputs in the reference's association
+// (csrc/common.cuh:99-126): r0 = .5*(((x0+x1)+x2)-x3)  r1 = .5*(((x0+x1)-x2)+x3)  r2 = .5*(((x0-x1)+x2)+x3)
+// r3 = .5*(((-x0+x1)+x2)+x3); -x0+x1 is the exact negation of x0-x1.
+__device__ __forceinline__ void h4u(uint32_t& u0, uint32_t& u1, uint32_t& u2, uint32_t& u3) {
+    const float x0 = __uint_as_float(u0), x1 = __uint_as_float(u1), x2 = __uint_as_float(u2), x3 = __uint_as_float(u3);
+    const float s = __fadd_rn(x0, x1), d = __fsub_rn(x0, x1);
+    u0 = __float_as_uint(__fmul_rn(0.5f, __fsub_rn(__fadd_rn(s, x2), x3)));
+    u1 = __float_as_uint(__fmul_rn(0.5f, __fadd_rn(__fsub_rn(s, x2), x3)));
+    u2 = __float_as_uint(__fmul_rn(0.5f, __fadd_rn(__fadd_rn(d, x2), x3)));
+    u3 = __float_as_uint(__fmul_rn(0.5f, __fadd_rn(__fsub_rn(x2, d), x3)));
+}
+// The same without the halving. With inputs scaled by a power of two instead, every intermediate is the reference's times
+// a power of two: rounding commutes with such a scaling as long as nothing overflows (the caller bounds the inputs) and
+// nothing is rounded in the subnormal range (sums of bf16 values are multiples of 2^-133, and so are their sixteenths' sums
+// of 2^-137: subnormal results are exact).
+__device__ __forceinline__ void h4n(uint32_t& u0, uint32_t& u1, uint32_t& u2, uint32_t& u3) {
+    const float x0 = __uint_as_float(u0), x1 = __uint_as_float(u1), x2 = __uint_as_float(u2), x3 = __uint_as_float(u3);
+    const float s = __fadd_rn(x0, x1), d = __fsub_rn(x0, x1);
+    u0 = __float_as_uint(__fsub_rn(__fadd_rn(s, x2), x3));
+    u1 = __float_as_uint(__fadd_rn(__fsub_rn(s, x2), x3));
+    u2 = __float_as_uint(__fadd_rn(__fadd_rn(d, x2), x3));
+    u3 = __float_as_uint(__fadd_rn(__fsub_rn(x2, d), x3));
+}
+// Stages of strides 1, 4 and 16 over 64 values held as two halves of 32
+template <bool HALVE>
+__device__ __forceinline__ void three_stages64(uint32_t (&ra)[32], uint32_t (&rb)[32]) {
+    auto bf = [](uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) {
+        if (HALVE) h4u(a, b, c, d);
+        else h4n(a, b, c, d);
+    };
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+        bf(ra[i], ra[i + 1], ra[i + 2], ra[i + 3]);
+        bf(rb[i], rb[i + 1], rb[i + 2], rb[i + 3]);
+    }
+#pragma unroll
+    for (int b = 0; b < 32; b += 16) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            bf(ra[b + i], ra[b + i + 4], ra[b + i + 8], ra[b + i + 12]);
+            bf(rb[b + i], rb[b + i + 4], rb[b + i + 8], rb[b + i + 12]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) bf(ra[i], ra[i + 16], rb[i], rb[i + 16]);
+}
+// max(m, |a|, |b|) that is NaN as soon as one input is
+__device__ __forceinline__ float max3_abs_nan_u(float m, uint32_t a, uint32_t b) {
+    float o;
+    asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(o) : "f"(m), "f"(fabsf(__uint_as_float(a))), "f"(fabsf(__uint_as_float(b))));
+    return o;
 }
 
 // One 32-column chunk of one accumulator row, written straight to global memory (the path for outputs whose row
@@ -352,8 +438,217 @@ template <int N> __device__ __forceinline__ void bulk_wait_read() {
 }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
+// ---- the rotating epilogue (EPI_ACT_ROT) --------------------------------------------------------------------------------
+// Activation, then the R256 rotation of the tile's 256 columns (one rotation group per row), written as bf16 with the
+// row's maximum over this warp's share beside it: what the quantizer's second pass needs. Tile width 256, bf16 and whole
+// tiles only (the host side sees to it). The two warps of a lane quarter split the work, and tensor memory is their
+// scratch (the accumulator is rewritten in place, as f32). Warp h of the two:
+//   A  columns [128 h, 128 h + 128), eight at a time: dequantize, activation from the table, back to tensor memory;
+//   B  the same columns as two 64-column blocks: stages of strides 1, 4 and 16 (64 values in registers), back again;
+//      barrier between the two warps;
+//   C  the last stage (columns j, j + 64, j + 128, j + 192) for the offsets j in [32 h, 32 h + 32), sixteen at a time: row
+//      maximum, rounding to bf16, and out through shared memory with TMA stores of 16-column boxes.
+// This epilogue, not the tensor core, bounds the kernel, and its warps wait for latency and instruction fetch, not for
+// issue slots: the loops are kept rolled (unrolled, "no instruction" was the largest stall), tensor-memory loads of step A
+// run one step ahead, and the next tile's per-column vectors and row scale are fetched a tile ahead. Plain 16-byte stores
+// from the registers (a row per lane) were slower than the staged TMA stores, and so were sixteen warps instead of eight.
+__device__ __forceinline__ void rotate_block64(uint32_t (&a)[32], uint32_t (&b)[32], bool exact) {
+    // Three stages (strides 1, 4, 16) of one 64-column block, left as half the reference's values: without the per-stage
+    // halvings and one multiplication by 1/16 at the end, or, next to huge values (where the unhalved sums could overflow
+    // although the reference's do not), exactly as the reference computes them, then halved (exact: see h4n).
+    if (!exact) {
+        three_stages64<false>(a, b);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            a[i] = __float_as_uint(__fmul_rn(__uint_as_float(a[i]), 0.0625f));
+            b[i] = __float_as_uint(__fmul_rn(__uint_as_float(b[i]), 0.0625f));
+        }
+    } else {
+        three_stages64<true>(a, b);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            a[i] = __float_as_uint(__fmul_rn(__uint_as_float(a[i]), 0.5f));
+            b[i] = __float_as_uint(__fmul_rn(__uint_as_float(b[i]), 0.5f));
+        }
+    }
+}
+
+__device__ __forceinline__ void epilogue_rot(const GemmParams& p, const CUtensorMap* tmap_d16, uint8_t* staging, uint8_t* tail,
+                                             uint32_t bar_tfull, uint32_t bar_tempty, uint32_t tmem_base, volatile int* abort_s,
+                                             int rank, int cluster_id, int nclusters, int warp, int lane) {
+    const int ew = warp - 2;
+    const int quad = warp & 3;               // TMEM lane quarter this warp may read
+    const int half = ew >> 2;
+    uint8_t* my_stage = staging + ew * 2048;                                              // two buffers of 32 rows x 32 bytes
+    const uint32_t my_stage_u32 = smem_u32(my_stage);
+    float* my_vec = reinterpret_cast<float*>(staging + kVecOffset + ew * 1024);          // ws[128] | bias[128]
+    const uint16_t* lut_sm = reinterpret_cast<const uint16_t*>(staging + kVecOffset + kEpiWarps * 1024);
+    volatile int* pair_ok = reinterpret_cast<volatile int*>(tail + 176);                  // [tile parity][quarter][half]
+    const bf16* bias = reinterpret_cast<const bf16*>(p.bias);
+    int buf = 0;
+    uint32_t tphase = 0;
+
+    // this warp's columns of ws / bias and this lane's row scale, for the tile `w`
+    float nx_ws[4], nx_b[4], nx_xs = 1.f;
+    auto fetch = [&](int w) {
+        int tm, tn;
+        tile_coords(w, p.tiles_m, p.tiles_n, tm, tn);
+        const int row = tm * (2 * BM) + rank * BM + quad * 32 + lane;
+        nx_xs = p.xs ? __ldg(p.xs + (row < p.M ? row : p.M - 1)) : 1.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int n = tn * 256 + (4 * half + k) * 32 + lane;
+            nx_ws[k] = __ldg(p.ws + n);
+            nx_b[k] = bias ? __bfloat162float(bias[n]) : 0.f;
+        }
+    };
+    if (cluster_id < p.num_items) fetch(cluster_id);
+
+    for (int w = cluster_id; w < p.num_items; w += nclusters) {
+        int tm, tn;
+        tile_coords(w, p.tiles_m, p.tiles_n, tm, tn);
+        const int n0 = tn * 256;
+        const int row0 = tm * (2 * BM) + rank * BM + quad * 32;
+        const int row = row0 + lane;
+        const float xs_r = nx_xs;
+        __syncwarp();
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            my_vec[32 * k + lane] = nx_ws[k];
+            my_vec[128 + 32 * k + lane] = nx_b[k];
+        }
+        __syncwarp();
+        if (w + nclusters < p.num_items) fetch(w + nclusters);      // in flight while this tile is processed
+
+        const bool got = mbar_wait_warp_relaxed(bar_tfull + 8 * buf, tphase, abort_s, ST_TIMEOUT_TMEM_FULL);
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + buf * 256 + ((uint32_t)(quad * 32) << 16);
+        bool big = false;   // a value of 2^120 or more (or an infinity, a NaN) among this warp's: exact halvings
+        if (got) {
+            const uint32_t ta = taddr + 128 * half;
+            // A: dequantize + activation, eight columns a step, the next step's load in flight
+            bool wide = false;
+            uint32_t r0[8], r1[8];
+            auto convert = [&](const uint32_t (&r)[8], int g) {
+                uint32_t t[8];
+                if (!epilogue8_lut_bits<128>(p, r, xs_r, my_vec + 8 * g, lut_sm, t)) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) wide |= (t[e] & 0x7fffu) >= 0x7B80u;
+                }
+#pragma unroll
+                for (int e = 0; e < 8; ++e) t[e] <<= 16;
+                tmem_st8(ta + 8 * g, t);
+            };
+            tmem_ld8(ta, r0);
+#pragma unroll 1
+            for (int g = 0; g < 16; g += 2) {
+                tmem_ld_wait();
+                tmem_ld8(ta + 8 * (g + 1), r1);
+                convert(r0, g);
+                tmem_ld_wait();
+                if (g + 2 < 16) tmem_ld8(ta + 8 * (g + 2), r0);
+                convert(r1, g + 1);
+            }
+            big = __any_sync(0xffffffffu, wide);
+            tmem_st_wait();
+            // B: three stages per 64-column block
+#pragma unroll 1
+            for (int blk = 0; blk < 2; ++blk) {
+                uint32_t a[32], b[32];
+                tmem_ld32(ta + 64 * blk, a);
+                tmem_ld32(ta + 64 * blk + 32, b);
+                tmem_ld_wait();
+                rotate_block64(a, b, big);
+                tmem_st32(ta + 64 * blk, a);
+                tmem_st32(ta + 64 * blk + 32, b);
+            }
+            tmem_st_wait();
+        }
+        // The partner's blocks are needed next. A warp whose wait ran out still meets its partner here, and both leave
+        // together: the decision is read from flags written before the barrier (two sets, by tile parity: a warp is at
+        // most one barrier ahead of its partner).
+        if (lane == 0) pair_ok[(buf * 4 + quad) * 2 + half] = got ? (big ? 3 : 1) : 0;
+        tc_fence_before();
+        named_bar_sync(1 + quad, 64);
+        tc_fence_after();
+        const int f0 = pair_ok[(buf * 4 + quad) * 2], f1 = pair_ok[(buf * 4 + quad) * 2 + 1];
+        if (!f0 || !f1) break;
+        const bool exact = ((f0 | f1) & 2) != 0;     // either warp met huge values: the last stage as the reference has it
+
+        // C: the last stage, sixteen offsets a step
+        const bool row_ok = row < p.M;
+#pragma unroll 1
+        for (int t = 0; t < 2; ++t) {
+            const int j0 = 32 * half + 16 * t;
+            uint32_t q[4][16];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) tmem_ld16(taddr + 64 * k + j0, q[k]);
+            tmem_ld_wait();
+            if (t == 1) {
+                // The accumulator is free as soon as both warps have read it. No cluster-scope release: nothing but tensor
+                // memory, ordered by the tcgen05 fences, is handed over.
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_remote(mapa_shared(bar_tempty + 8 * buf, 0));
+            }
+            if (!exact) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) h4n(q[0][i], q[1][i], q[2][i], q[3][i]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) q[k][i] = __float_as_uint(__fmul_rn(__uint_as_float(q[k][i]), 2.f));
+                    h4u(q[0][i], q[1][i], q[2][i], q[3][i]);
+                }
+            }
+            float m = 0.f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+#pragma unroll
+                for (int i = 0; i < 16; i += 2) m = max3_abs_nan_u(m, q[k][i], q[k][i + 1]);
+            }
+            bool has_nan = false;
+            if (m != m) {   // the reference's fmaxf drops a NaN: the maximum again without it, and a flag
+                has_nan = true;
+                m = 0.f;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(__uint_as_float(q[k][i])));
+                }
+            }
+            if (row_ok)
+                p.amax_part[(int64_t)row * (p.N >> 6) + 4 * tn + 2 * half + t] = has_nan ? __uint_as_float(__float_as_uint(m) | 0x80000000u) : m;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                uint32_t o[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(q[k][2 * i]), __uint_as_float(q[k][2 * i + 1]));
+                    o[i] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+                if (lane == 0) bulk_wait_read<1>();   // the store before the last has read this buffer
+                __syncwarp();
+                uint8_t* rowp = my_stage + (k & 1) * 1024 + lane * 32;
+                *reinterpret_cast<uint4*>(rowp) = make_uint4(o[0], o[1], o[2], o[3]);
+                *reinterpret_cast<uint4*>(rowp + 16) = make_uint4(o[4], o[5], o[6], o[7]);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_2d(tmap_d16, my_stage_u32 + (k & 1) * 1024, n0 + 64 * k + j0, row0);
+                    bulk_commit();
+                }
+            }
+        }
+        buf ^= 1;
+        if (buf == 0) tphase ^= 1u;
+    }
+    if (lane == 0) bulk_wait_all();   // staged rows have left shared memory before the CTA exits
+}
+
 template <typename OutT, int EPI, int KIND = 0>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(EPI == EPI_ACT_ROT ? kRotThreads : kThreads, 1)
 gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                     const __grid_constant__ CUtensorMap tmap_d, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -389,7 +684,7 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar_tfull + 8 * i, 1);
-            mbar_init(bar_tempty + 8 * i, 2 * kEpiWarps);
+            mbar_init(bar_tempty + 8 * i, 2 * (EPI == EPI_ACT_ROT ? kRotEpiWarps : kEpiWarps));
         }
         *abort_s = 0;
         fence_mbar_init();
@@ -401,13 +696,13 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         tmem_alloc_pair(smem_u32(tmem_ptr_s), 512);
         tmem_relinquish_pair();
     }
-    if constexpr (EPI == EPI_ACT_LUT) {
+    if constexpr (EPI == EPI_ACT_LUT || EPI == EPI_ACT_ROT) {
         // the activation table's hot part into shared memory (a gather from the whole table through L1 costs the epilogue
         // one wavefront per distinct line and made it, not the tensor core, the limit)
         if (warp >= 2) {
             uint16_t* dst = reinterpret_cast<uint16_t*>(staging + kVecOffset + kEpiWarps * 1024);
-            for (uint32_t i = threadIdx.x - 64; i < 2 * kActLutHalf; i += kThreads - 64)
-                dst[i] = __ldg(p.act_lut + (i < kActLutHalf ? kActLutLo + i : 0x8000u + kActLutLo + (i - kActLutHalf)));
+            for (uint32_t i = threadIdx.x - 64; i < 2 * kActLutHalf; i += blockDim.x - 64)
+                dst[i] = __ldg(p.act_lut + act_lut_pattern(i));
         }
     }
     tc_fence_before();
@@ -493,6 +788,10 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
     } else {
         // ---------------- epilogue (both CTAs, 8 warps) ----------------
+        if constexpr (EPI == EPI_ACT_ROT) {
+            epilogue_rot(p, &tmap_d, staging, tail, bar_tfull, bar_tempty, tmem_base, abort_s, (int)rank, cluster_id, nclusters, warp,
+                         lane);
+        } else {
         constexpr int kEsz = EPI == EPI_ACC ? 4 : (int)sizeof(OutT);
         constexpr bool kStageVec = kEsz == 2;            // 2-byte outputs: 2 KB chunk + 1.5 KB of per-column vectors
         const int ew = warp - 2;
@@ -613,6 +912,7 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             if (buf == 0) tphase ^= 1u;
         }
         if (p.tma_store && lane == 0) bulk_wait_all();   // staged rows have left shared memory before the CTA exits
+        }
     }
 
     // ---------------- teardown ----------------
@@ -712,6 +1012,22 @@ bool make_output_tmap(CUtensorMap* tm, void* ptr, int64_t M, int64_t N, int esz)
     g_tmaps.put(k, *tm);
     return true;
 }
+// The rotating epilogue's map: bf16 output, boxes of 16 columns x 32 rows (32-byte rows, no swizzle)
+bool make_output_tmap16(CUtensorMap* tm, void* ptr, int64_t M, int64_t N) {
+    const TmapKey k{ptr, N, M, N * 2, 16, 32, 3};
+    if (const CUtensorMap* hit = g_tmaps.find(k)) { *tm = *hit; return true; }
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)(N * 2)};
+    const cuuint32_t box[2] = {16, 32};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    g_tmaps.put(k, *tm);
+    return true;
+}
 bool encode_output_tmap(CUtensorMap* tm, void* ptr, int64_t M, int64_t N, int esz) {
     EncodeTiledFn enc = encode_fn();
     if (!enc) return false;
@@ -749,7 +1065,7 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap&
         if (e != cudaSuccess) return (int)e;
         configured.fetch_or(bit, std::memory_order_release);
     }
-    kern<<<grid, kThreads, kSmemBytes, st>>>(ta, tw, td, p);
+    kern<<<grid, EPI == EPI_ACT_ROT ? kRotThreads : kThreads, kSmemBytes, st>>>(ta, tw, td, p);
     KCHECK();
     return 0;
 }
@@ -762,6 +1078,9 @@ int launch_pair_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tw, const
         case EPI_ACT: return launch_pair<OutT, EPI_ACT>(ta, tw, td, p, grid, st);
         case EPI_ACT_LUT:
             if constexpr (std::is_same<OutT, bf16>::value) return launch_pair<bf16, EPI_ACT_LUT>(ta, tw, td, p, grid, st);
+            return -200;
+        case EPI_ACT_ROT:
+            if constexpr (std::is_same<OutT, bf16>::value) return launch_pair<bf16, EPI_ACT_ROT>(ta, tw, td, p, grid, st);
             return -200;
         default: return -200;
     }
@@ -835,7 +1154,7 @@ int choose_bn(int64_t M, int64_t N, int clusters) {
 
 int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const float* ws, const void* bias,
              const void* rscale, const void* resid, void* D, int64_t M, int64_t N, int64_t K, int out_dt, int act,
-             cudaStream_t st) {
+             cudaStream_t st, float* amax_part = nullptr) {
     if (M == 0 || N == 0) return 0;
     if (K == 0) return epi == EPI_RESID ? -201 : 0;  // the reference declines K == 0 for the residual form only
     if (epi == EPI_RESID && (!rscale || !resid)) return -201;
@@ -846,12 +1165,17 @@ int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const f
     if ((K % 8) != 0) return epi == EPI_RESID ? -201 : -200;
     int dev = 0;
     cudaGetDevice(&dev);
+    const bool rot = epi == EPI_ACT_ROT;
+    // the rotating epilogue exists on the tensor-core kernel only: bf16 rows of whole 256-column rotation groups
+    if (rot && (out_dt != DT_BF16 || (N % 256) != 0 || (K % 16) != 0 || (((uintptr_t)A | (uintptr_t)W | (uintptr_t)D) & 15) ||
+                !amax_part || act < 1 || act > 3))
+        return -208;
     // TMA needs 16-byte aligned bases and row pitch; what it cannot address takes the CUDA-core kernel
     if ((K % 16) != 0 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) {
         SkinnyParams sp{A, W, xs, ws, bias, rscale, resid, D, (int)M, (int)N, (int)K, act};
         return launch_generic_gemm(epi, sp, out_dt, st);
     }
-    if (skinny_gemm_applies(M, N, K)) {
+    if (!rot && skinny_gemm_applies(M, N, K)) {
         SkinnyParams sp{A, W, xs, ws, bias, rscale, resid, D, (int)M, (int)N, (int)K, act};
         return launch_skinny_gemm(epi, sp, out_dt, device_sm_count(dev), st);
     }
@@ -862,6 +1186,7 @@ int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const f
     p.M = (int)M, p.N = (int)N, p.K = (int)K;
     p.act = act;
     p.act_lut = nullptr;
+    p.amax_part = amax_part;
     const int esz = epi == EPI_ACC ? 4 : (out_dt == DT_F32 ? 4 : 2);
     auto al16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
     p.vec_ok = (N % 8 == 0) && al16(D) && al16(ws) && al16(bias) && al16(rscale) && al16(resid);
@@ -871,9 +1196,11 @@ int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const f
         if (int rc = act_lut_ptr(act, st, &p.act_lut)) return rc;
         epi = EPI_ACT_LUT;
     }
+    if (rot)
+        if (int rc = act_lut_ptr(act, st, &p.act_lut)) return rc;
     p.ksub = K <= BK ? 1 : 2;
     p.k_iters = (int)((K + p.ksub * BK - 1) / (p.ksub * BK));
-    const int bn = choose_bn(M, N, clusters);
+    const int bn = rot ? 256 : choose_bn(M, N, clusters);
     p.bn = bn;
     p.idesc = umma_idesc_i8(2 * BM, bn);
     const int stage_bytes = p.ksub * (BM * BK + (bn / 2) * BK);
@@ -884,7 +1211,9 @@ int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const f
     p.num_tiles = p.tiles_m * p.tiles_n;
     CUtensorMap ta, tw, td;
     if (!make_operand_tmap(&ta, A, M, K, BM) || !make_operand_tmap(&tw, W, N, K, bn / 2)) return -203;
-    if (p.tma_store) {
+    if (rot) {
+        if (!make_output_tmap16(&td, D, M, N)) return -203;
+    } else if (p.tma_store) {
         if (!make_output_tmap(&td, D, M, N, esz)) return -203;
     } else {
         td = ta;  // unused
@@ -899,7 +1228,7 @@ int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const f
     p.whole_tiles = p.num_tiles, p.splits = 0, p.kps = p.k_iters, p.num_items = p.num_tiles;
     p.scratch = nullptr, p.partials = nullptr;
     const int rem = p.num_tiles % clusters;
-    if (rem > 0 && p.num_tiles < clusters && 2 * rem <= clusters && p.k_iters >= 16) {
+    if (!rot && rem > 0 && p.num_tiles < clusters && 2 * rem <= clusters && p.k_iters >= 16) {
         int splits = clusters / rem;
         if (splits > p.k_iters / 8) splits = p.k_iters / 8;
         if (splits > 16) splits = 16;
@@ -1057,6 +1386,19 @@ GPU_API int gpu_int8_gemm_act(const int8_t* A, const int8_t* W, const float* xs,
     if (act == ACT_NONE) return gpu_int8_gemm(A, W, xs, ws, bias, D, M, N, K, out_dt, stream);
     if (act < 0 || act > 3) return -204;
     return run_gemm(EPI_ACT, A, W, xs, ws, bias, nullptr, nullptr, D, M, N, K, out_dt, act, (cudaStream_t)stream);
+}
+
+// New: gpu_int8_gemm_act whose epilogue also rotates. The reference runs the MLP's second half as GEMM -> quantizer with the
+// GELU prologue and the R256 rotation -> GEMM (src/qwen21.rs:378-417; csrc/kernels.cu:121-130,184-258), and the quantizer's
+// rotation is what that kernel spends its time on. Here the up-projection's epilogue, which holds one whole rotation group
+// of each row (256 columns) in tensor memory, applies the activation and the rotation while the tensor cores run the next
+// tile, and leaves   D[m, :] = bf16(R256(act(bf16(acc * xs * ws + bias))))   (bf16 only) together with
+// amax_part[m, N / 64]: partial maxima of the unrounded rotated values, four per tile (sign bit: a NaN was among them).
+// gpu_quant_rows_rotated turns the two into the codes and scales gpu_quant_rows(prologue = the activation, rotate = 1)
+// gives on the plain GEMM's output, bit for bit. N % 256 == 0, K % 16 == 0, 16-byte aligned operands, act 1..3 (-208 otherwise).
+GPU_API int gpu_int8_gemm_act_rot(const int8_t* A, const int8_t* W, const float* xs, const float* ws, const void* bias, void* D,
+                                  float* amax_part, int64_t M, int64_t N, int64_t K, int act, void* stream) {
+    return run_gemm(EPI_ACT_ROT, A, W, xs, ws, bias, nullptr, nullptr, D, M, N, K, DT_BF16, act, (cudaStream_t)stream, amax_part);
 }
 
 // New, for tests: the raw int32 accumulators D[m,n] = sum_k A[m,k]*W[n,k], which the fused forms never expose.

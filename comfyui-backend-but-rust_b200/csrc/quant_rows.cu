@@ -180,24 +180,27 @@ __device__ __forceinline__ float max3_abs_nan(float a, float b, float c) {
 // (tests/test_quant_division.py enumerates every pair of significands).
 // The magic-number rint + saturating pack equal clamp(rint(.)) for finite values; the caller keeps rows that hold a NaN
 // or an infinity off this path.
+// (the fast path on two values already rounded to bf16, packed in one word)
+__device__ __forceinline__ uint32_t quant2_bf16_bits(uint32_t au, float rcp) {
+    const float2 a = make_float2(__uint_as_float(au << 16), __uint_as_float(au & 0xffff0000u));
+    const float2 t = __fmul2_rn(a, make_float2(rcp, rcp));
+    const __nv_bfloat162 tb = __floats2bfloat162_rn(t.x, t.y);
+    const uint32_t tu = *reinterpret_cast<const uint32_t*>(&tb);
+    // rint by adding 1.5 * 2^23 (round to nearest even at unit spacing, |t| <= 128): the integer sits in the low bits.
+    // The float -> integer conversion instructions share a narrow pipe with the bf16 conversions above, and that
+    // pipe, not HBM, bounded this kernel; the addition runs on the FP32 pipe instead.
+    const float2 u = __fadd2_rn(make_float2(__uint_as_float(tu << 16), __uint_as_float(tu & 0xffff0000u)),
+                                make_float2(12582912.f, 12582912.f));
+    const int n0 = (int)__float_as_uint(u.x) - 0x4B400000, n1 = (int)__float_as_uint(u.y) - 0x4B400000;
+    uint32_t packed;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(packed) : "r"(n1), "r"(n0));
+    return packed;   // byte 0 = code of the low half, byte 1 = code of the high half
+}
 template <typename T>
 __device__ __forceinline__ uint32_t quant2(float2 v, float st, float rcp, bool fast) {
     if (sizeof(T) == 2 && fast) {
         const __nv_bfloat162 ab = __floats2bfloat162_rn(v.x, v.y);
-        const uint32_t au = *reinterpret_cast<const uint32_t*>(&ab);
-        const float2 a = make_float2(__uint_as_float(au << 16), __uint_as_float(au & 0xffff0000u));
-        const float2 t = __fmul2_rn(a, make_float2(rcp, rcp));
-        const __nv_bfloat162 tb = __floats2bfloat162_rn(t.x, t.y);
-        const uint32_t tu = *reinterpret_cast<const uint32_t*>(&tb);
-        // rint by adding 1.5 * 2^23 (round to nearest even at unit spacing, |t| <= 128): the integer sits in the low bits.
-        // The float -> integer conversion instructions share a narrow pipe with the bf16 conversions above, and that
-        // pipe, not HBM, bounded this kernel; the addition runs on the FP32 pipe instead.
-        const float2 u = __fadd2_rn(make_float2(__uint_as_float(tu << 16), __uint_as_float(tu & 0xffff0000u)),
-                                    make_float2(12582912.f, 12582912.f));
-        const int n0 = (int)__float_as_uint(u.x) - 0x4B400000, n1 = (int)__float_as_uint(u.y) - 0x4B400000;
-        uint32_t packed;
-        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(packed) : "r"(n1), "r"(n0));
-        return packed;   // byte 0 = code of v.x, byte 1 = code of v.y
+        return quant2_bf16_bits(*reinterpret_cast<const uint32_t*>(&ab), rcp);
     }
     const int qx = clamp_rint_i8(rnd<T>(__fdiv_rn(rnd<T>(v.x), st)), -128.f);
     const int qy = clamp_rint_i8(rnd<T>(__fdiv_rn(rnd<T>(v.y), st)), -128.f);
@@ -1035,4 +1038,75 @@ GPU_API int gpu_quant_rows_scaled(int dtype, int prologue, const void* x, int64_
     if (dtype == DT_BF16) return dispatch_prologue<bf16>(prologue, p, (cudaStream_t)stream);
     if (dtype == DT_F32) return dispatch_prologue<float>(prologue, p, (cudaStream_t)stream);
     return -4;
+}
+
+// ---- second pass after a rotating GEMM epilogue -------------------------------------------------------------------------
+// gpu_int8_gemm_act_rot leaves the rows rotated and rounded to bf16, and per row N / 64 partial maxima of the unrounded
+// rotated values (sign bit: a NaN among them). What is left of the quantizer is the row maximum, the scale and one pass
+// over the row: 2 bytes read and 1 written per element. A row is shared by `wpr` warps (each re-reads the row's few
+// partial maxima); a lane converts 16 consecutive values per step.
+namespace {
+__global__ void __launch_bounds__(256) quant_rotated_kernel(const bf16* __restrict__ xr, const float* __restrict__ parts,
+                                                            int8_t* __restrict__ q, float* __restrict__ scales, int M, int K,
+                                                            int P, int wpr) {
+    const int lane = threadIdx.x & 31;
+    const int64_t gw = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t m = gw / wpr;
+    const int seg = (int)(gw - m * wpr);
+    if (m >= M) return;
+    float amax = 0.f;
+    uint32_t flag = 0;
+    for (int i = lane; i < P; i += 32) {
+        const uint32_t u = __float_as_uint(__ldg(parts + m * P + i));
+        flag |= u & 0x80000000u;
+        amax = fmaxf(amax, __uint_as_float(u & 0x7fffffffu));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        flag |= __shfl_xor_sync(0xffffffffu, flag, o);
+    }
+    const float scale = fmaxf(fminf(amax, finite_max<bf16>()) * (1.f / 127.f), 1.0e-30f);
+    if (seg == 0 && lane == 0) scales[m] = scale;
+    const float st = rnd<bf16>(scale);
+    // rows holding an infinity or a NaN keep the IEEE division and the exact clamp
+    const bool fast = amax <= FLT_MAX && flag == 0;
+    const float rcp = fast ? __frcp_rn(st) : 0.f;
+    const int per = K / wpr;
+    const bf16* src = xr + m * (int64_t)K + (int64_t)seg * per;
+    int8_t* dst = q + m * (int64_t)K + (int64_t)seg * per;
+#pragma unroll 2
+    for (int e = lane * 16; e < per; e += 512) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(src + e)), b = __ldg(reinterpret_cast<const uint4*>(src + e + 8));
+        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        uint32_t c[8];
+        if (fast) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) c[i] = quant2_bf16_bits(w[i], rcp);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                c[i] = quant2<bf16>(make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u)), st, 0.f, false);
+        }
+        *reinterpret_cast<uint4*>(dst + e) = make_uint4((c[0] & 0xffffu) | (c[1] << 16), (c[2] & 0xffffu) | (c[3] << 16),
+                                                        (c[4] & 0xffffu) | (c[5] << 16), (c[6] & 0xffffu) | (c[7] << 16));
+    }
+}
+}  // namespace
+
+// New: the quantizer's second pass on rows a rotating GEMM epilogue left (gpu_int8_gemm_act_rot): xr [M, K] bf16, rotated;
+// amax_part [M, K / 64]; q [M, K] int8 and scales [M] as gpu_quant_rows(prologue = that activation, rotate = 1) gives them
+// on the plain GEMM's output. K % 256 == 0 (-1); xr and q 16-byte aligned (-5).
+GPU_API int gpu_quant_rows_rotated(const void* xr, const float* amax_part, int8_t* q, float* scales, int M, int K, void* stream) {
+    if (K <= 0 || (K % 256) != 0) return -1;
+    if (M <= 0) return 0;
+    if ((((uintptr_t)xr | (uintptr_t)q) & 15) != 0) return -5;
+    // enough warps for every SM to have many loads in flight: split long rows
+    const int wpr = K >= 8192 ? 4 : K >= 2048 ? 2 : 1;
+    const int64_t warps = (int64_t)M * wpr;
+    const unsigned grid = (unsigned)((warps + 7) / 8);
+    quant_rotated_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<const bf16*>(xr), amax_part, q, scales, M, K,
+                                                                 K / 64, wpr);
+    KCHECK();
+    return 0;
 }

@@ -34,6 +34,8 @@ SIGNATURES = {
     "gpu_int8_gemm": [P, P, P, P, P, P, i64, i64, i64, i32, P],
     "gpu_int8_gemm_residual": [P, P, P, P, P, P, P, P, i64, i64, i64, i32, P],
     "gpu_int8_gemm_act": [P, P, P, P, P, P, i64, i64, i64, i32, i32, P],
+    "gpu_int8_gemm_act_rot": [P, P, P, P, P, P, P, i64, i64, i64, i32, P],
+    "gpu_quant_rows_rotated": [P, P, P, P, i32, i32, P],
     "gpu_int8_gemm_noalloc": [P, P, P, P, P, P, i64, i64, i64, i32, P],
     "gpu_int8_gemm_acc_i32": [P, P, P, i64, i64, i64, P],
     "gpu_w6a8_gemm": [P, P, P, P, P, P, P, i64, i64, i64, i32, i32, P],

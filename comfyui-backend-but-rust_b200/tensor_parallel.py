@@ -103,6 +103,9 @@ def shard_pair(w1q, s1, b1, w2q, s2, b2, rank: int, world: int, hidden_of=None) 
     return PairWeights(w1, s1r, b1r, w2, s2, b2)
 
 
+_ACT_OF_PROLOGUE = {PRO_GELU_TANH: 1, 5: 2, 6: 3}     # quantizer prologues that are activations -> the GEMM epilogue's codes
+
+
 class TPPair:
     """One (column-parallel, row-parallel) pair with a residual around it: out = x + W2 act(W1 x).
 
@@ -144,13 +147,23 @@ class TPPair:
         a8 = comm.all_gather_rows(a8, self._buf("a8", (M, F), torch.int8, x_local) if P > 1 else None)
         xs = comm.all_gather_rows(xs, self._buf("xs", (M,), torch.float32, x_local) if P > 1 else None)
         n1 = w.w1.shape[0]
-        h = ops.int8_gemm(a8, w.w1, xs, w.s1, w.b1, out_dtype=dt, out=self._buf("h", (M, n1), dt, x_local))       # [M, N1 / P]
+        cuda = x_local.device.type == "cuda"
+        # Activation and rotation in the column-parallel GEMM's epilogue, the quantizer's second pass after it (same codes
+        # and scales as the plain GEMM followed by the quantizer with that prologue). Not in exact mode, whose row maxima
+        # are reduced across the ranks between the quantizer's two passes.
+        act = _ACT_OF_PROLOGUE.get(self.pro, 0)
+        fused = (cuda and act and self.rotate and not self.exact and self.hidden_cols is None and dt == torch.bfloat16
+                 and n1 % 256 == 0 and F % 16 == 0 and hasattr(ops, "int8_gemm_act_rot"))
+        if fused:
+            h, parts = ops.int8_gemm_act_rot(a8, w.w1, xs, w.s1, w.b1, act=act, out=self._buf("h", (M, n1), dt, x_local),
+                                             amax_part=self._buf("parts", (M, n1 // 64), torch.float32, x_local))
+        else:
+            h = ops.int8_gemm(a8, w.w1, xs, w.s1, w.b1, out_dtype=dt, out=self._buf("h", (M, n1), dt, x_local))   # [M, N1 / P]
         if self.hidden_cols is not None:
             h = h[:, self.hidden_cols]            # a view: the quantizers take the row stride
         kh, n2 = h.shape[1], w.w2.shape[0]
         if self.ones is None:
             self.ones = torch.ones(n2, dtype=dt, device=x_local.device)
-        cuda = x_local.device.type == "cuda"
         if out is None:
             out = self._buf("out_" + ("a" if self.hidden_cols is not None else "m"), (rows, n2), dt, x_local)
         if self.exact:
@@ -162,7 +175,7 @@ class TPPair:
             xs2_local = xs2[comm.rank * rows:(comm.rank + 1) * rows]
             return ops.int8_epilogue(acc, xs2_local, w.s2, w.b2, out_dtype=dt, rscale=self.ones, resid=x_local, out=out)
         qkw = dict(q=self._buf("a2", (M, kh), torch.int8, x_local), scales=self._buf("xs2", (M,), torch.float32, x_local)) if cuda else {}
-        a2, xs2 = ops.quant_rows(h, self.pro, self.rotate, **qkw)
+        a2, xs2 = ops.quant_rows_rotated(h, parts, **qkw) if fused else ops.quant_rows(h, self.pro, self.rotate, **qkw)
         C = self.chunks if (cuda and P > 1 and self.comm_stream is not None and n2 % (8 * self.chunks) == 0) else 1
         if C == 1:
             part = ops.int8_gemm(a2, w.w2, xs2, w.s2, None, out_dtype=dt, out=self._buf("part", (M, n2), dt, x_local))   # partial sums, all rows

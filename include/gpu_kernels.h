@@ -94,6 +94,20 @@ int gpu_int8_gemm_residual(const int8_t* A, const int8_t* W, const float* xs, co
 int gpu_int8_gemm_act(const int8_t* A, const int8_t* W, const float* xs, const float* ws, const void* bias, void* D,
                       int64_t M, int64_t N, int64_t K, int out_dt, int act, void* stream);
 
+/* New: the MLP's "GEMM -> quantizer with activation prologue and rotation" (src/qwen21.rs:378-417; the quantizer is
+ * csrc/kernels.cu:76-259 with PRO_GELU_TANH / PRO_SILU / PRO_GELU and rotate = 1) with the activation AND the R256 rotation
+ * moved into the GEMM's epilogue, which holds one rotation group (256 columns) of every row in tensor memory:
+ *   gpu_int8_gemm_act_rot   D[m, :] = bf16( R256( act( bf16( acc * xs[m] * ws[n] + bias[n] ) ) ) )   (bf16 only), and
+ *                           amax_part [M, N / 64] f32: partial row maxima of the unrounded rotated values (four per
+ *                           256-column group), sign bit set when a NaN was among them;
+ *   gpu_quant_rows_rotated  xr = that D, amax_part -> q [M, K] int8, scales [M] f32.
+ * The pair gives the codes and scales of gpu_int8_gemm followed by gpu_quant_rows(prologue = the activation, rotate = 1),
+ * bit for bit. N % 256 == 0, K % 16 == 0, operands 16-byte aligned, act 1..3 (-208 otherwise); second call: K % 256 == 0
+ * (-1), xr and q 16-byte aligned (-5). */
+int gpu_int8_gemm_act_rot(const int8_t* A, const int8_t* W, const float* xs, const float* ws, const void* bias, void* D,
+                          float* amax_part, int64_t M, int64_t N, int64_t K, int act, void* stream);
+int gpu_quant_rows_rotated(const void* xr, const float* amax_part, int8_t* q, float* scales, int M, int K, void* stream);
+
 /* No counterpart in the reference. gpu_int8_gemm for hosts that must not allocate device memory once they run (an
  * engine that manages the card inside a fixed budget of its own, a latency-critical thread): small-output, long-K
  * problems (at most 16 tiles of 256 x 256 outputs) are cut along K, and the scratch the slices meet in is a
