@@ -114,7 +114,8 @@ HBM_KERNELS = {
     "w6_decode": lambda b, I: I.w6_decode(b.h6[0], b.h6[1], 5120),
     "adaln": lambda b, I: I.int8_gemm(b.ha, b.hw, b.hs[0], b.hs[1], b.hs[2], out=b.hd),
 }
-QUANT_BYTES = {"quant_rot": 3 * 4352 * 12288, "quant_gelu": 3 * 4352 * 12288, "quant_in": 3 * 4352 * 3072}
+QUANT_BYTES = {"quant_rot": 3 * 4352 * 12288, "quant_gelu": 3 * 4352 * 12288, "quant_in": 3 * 4352 * 3072,
+               "quant_rotated": 3 * 4352 * 12288 + 4 * 4352 * (12288 // 64)}      # rows in, codes out, partial maxima in
 
 
 def parse_args():
