@@ -134,6 +134,8 @@ def parse_args():
     ap.add_argument("--act-epilogue", action="store_true",
                     help="GELU-tanh in the up-projection's epilogue but the rotation in the quantizer (gpu_int8_gemm_act, then "
                          "gpu_quant_rows) instead of both in the epilogue (gpu_int8_gemm_act_rot, then gpu_quant_rows_rotated)")
+    ap.add_argument("--gemm-clusters", type=int, default=0,
+                    help="upper bound on the CTA pairs a GEMM launch occupies (gpu_int8_gemm_set_cluster_limit; 0 = the library's choice)")
     ap.add_argument("--no-stack", action="store_true", help="skip the 60-block stack record")
     ap.add_argument("--settle-s", type=float, default=SETTLE_S, help="seconds of untimed back-to-back load before the timed steps")
     ap.add_argument("--stack-blocks", type=int, default=60)
@@ -214,6 +216,9 @@ class Block:
         self.w2, self.s2 = impl.convrot_requant(w2.to(dev), 0)
         self.b1, self.b2 = b1.to(dev), b2.to(dev)
         self.ones = torch.ones(down.N, dtype=torch.bfloat16, device=dev)          # rscale of the residual form
+        # ... and the gate of the chained leg: an ungated branch added 60 times over drives the residual stream out of the
+        # input's distribution (the models gate the branch by their modulation vector: rscale of src/qwen21.rs:416)
+        self.gate = torch.full((down.N,), 0.125, dtype=torch.bfloat16, device=dev)
         M = up.M
         self.a1 = torch.empty((M, up.K), dtype=torch.int8, device=dev)
         self.xs1 = torch.empty((M,), dtype=torch.float32, device=dev)
@@ -224,10 +229,11 @@ class Block:
         self.out = torch.empty((M, down.N), dtype=torch.bfloat16, device=dev)
         self.launches_per_step = 4
 
-    def step(self, x=None, out=None):
+    def step(self, x=None, out=None, rscale=None):
         I = self.impl
         x = self.x if x is None else x
         out = self.out if out is None else out
+        rscale = self.ones if rscale is None else rscale
         I.quant_rows(x, 0, 1, q=self.a1, scales=self.xs1)
         if self.rot_epilogue:
             I.int8_gemm_act_rot(self.a1, self.w1, self.xs1, self.s1, self.b1, act=1, out=self.h, amax_part=self.parts)
@@ -238,7 +244,7 @@ class Block:
         else:   # the reference's arrangement: plain epilogue, GELU in the next quantizer's prologue
             I.int8_gemm(self.a1, self.w1, self.xs1, self.s1, self.b1, out=self.h)
             I.quant_rows(self.h, 11, 1, q=self.a2, scales=self.xs2)
-        I.int8_gemm(self.a2, self.w2, self.xs2, self.s2, self.b2, rscale=self.ones, resid=x, out=out)
+        I.int8_gemm(self.a2, self.w2, self.xs2, self.s2, self.b2, rscale=rscale, resid=x, out=out)
 
     def ops(self) -> float:
         return self.up.ops + self.down.ops
@@ -454,6 +460,8 @@ def main():
     # token-sharded replicas: every rank owns one batch of the block (weights replicated), no data-path collective
     up, down, x, w1, w2, b1, b2 = host_inputs(wl, rank)
     rot = fused and not args.act_epilogue and args.impl != "reference-gpu"
+    if args.gemm_clusters and args.impl != "reference-gpu":
+        pkg.linear.set_gemm_cluster_limit(args.gemm_clusters)
     blk = Block(impl, torch, dev, up, down, x, w1, w2, b1, b2, fused, rot)
     if args.mode == "kernel":
         # the rotated rows and their partial maxima in h / parts for the second pass; the GELU output for the others
@@ -574,7 +582,8 @@ def main():
     e2e_value = blk.ops() * world * args.steps / (e2e_ms * 1e-3) / 1e12
     # The same path as the product drives it: a chain of CHAIN_BLOCKS blocks between one copy in and one copy out
     # (the reference uploads a step's input once and downloads once at its end, src/h3.rs:1361-1364). The blocks share
-    # this block's weights; every block still runs its four kernels on the previous block's output.
+    # this block's weights; every block still runs its four kernels on the previous block's output, its MLP branch gated by
+    # 1/8 so that the residual stream stays in the input's distribution over the 60 blocks.
     def chain_run(n):
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         xa, xb = torch.empty_like(blk.x), torch.empty_like(blk.out)
@@ -584,7 +593,7 @@ def main():
             xa.copy_(x_host, non_blocking=True)
             cur, nxt = xa, xb
             for _b in range(CHAIN_BLOCKS):
-                blk.step(cur, nxt)
+                blk.step(cur, nxt, blk.gate)
                 cur, nxt = nxt, cur
             out_host.copy_(cur, non_blocking=True)
         t1.record()
