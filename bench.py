@@ -627,6 +627,7 @@ def main():
     if rank != 0:
         return
     # roofline of the dominant kernel: the up-projection GEMM alone, as the step runs it, CUDA events over back-to-back launches
+    blk.step()                                   # the timed step's own operands again (the chained leg left its last block's)
     def gemm_up():
         if rot:
             impl.int8_gemm_act_rot(blk.a1, blk.w1, blk.xs1, blk.s1, blk.b1, act=1, out=blk.h, amax_part=blk.parts)
