@@ -145,6 +145,22 @@ template <> __device__ __forceinline__ void load8<half>(const half* p, float (&y
     }
 }
 
+// 8 two-byte values held in a register quad -> floats (no address is taken: the quad stays in registers)
+template <typename OutT> __device__ __forceinline__ void unpack8(const uint4 u, float (&y)[8]) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if constexpr (std::is_same<OutT, bf16>::value) {
+            y[2 * i] = __uint_as_float(w[i] << 16), y[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        } else if constexpr (std::is_same<OutT, half>::value) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            y[2 * i] = f.x, y[2 * i + 1] = f.y;
+        } else {
+            y[2 * i] = 0.f, y[2 * i + 1] = 0.f;
+        }
+    }
+}
+
 // The epilogue arithmetic on 8 consecutive columns of one row (accumulators r[0..7] -> y[0..7], not yet rounded
 // to the output type for the last step; the store rounds).
 //   t0 = float(acc) * xs;  v = out(fma(t0, ws, bias));  RESID: fma(v, rscale, resid);  ACT: act(v)
@@ -173,7 +189,8 @@ template <int KIND> __device__ __forceinline__ float acc_f(uint32_t r) {
 
 template <typename OutT, int EPI, int VS = 128, int KIND = 0>
 __device__ __forceinline__ void epilogue8(const GemmParams& p, const uint32_t* r, int row, int col, float xs_r, bool vec,
-                                          float (&y)[8], const float* vs = nullptr, const uint16_t* lut_sm = nullptr) {
+                                          float (&y)[8], const float* vs = nullptr, const uint16_t* lut_sm = nullptr,
+                                          bool have_resid8 = false, const uint4 resid8 = uint4{0, 0, 0, 0}) {
     float w8[8], b8[8], rs8[8], rr[8];
     const OutT* rsd = reinterpret_cast<const OutT*>(p.resid) + (int64_t)row * p.N + col;
     if (vs) {
@@ -181,7 +198,8 @@ __device__ __forceinline__ void epilogue8(const GemmParams& p, const uint32_t* r
         load8<float>(vs + VS, b8);
         if (EPI == EPI_RESID) {
             load8<float>(vs + 2 * VS, rs8);
-            if (vec) load8<OutT>(rsd, rr);
+            if (have_resid8) unpack8<OutT>(resid8, rr);      // fetched by the caller, 8 two-byte values
+            else if (vec) load8<OutT>(rsd, rr);
             else {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) rr[e] = col + e < p.N ? to_f<OutT>(rsd[e]) : 0.f;
@@ -398,6 +416,17 @@ __device__ __forceinline__ void chunk_compute16(const GemmParams& p, const uint3
             epilogue8<OutT, EPI, VS, KIND>(p, r + 8 * j, row, col0 + 8 * j, xs_r, p.vec_ok && col0 + 8 * j + 8 <= p.N, y, vs + 8 * j, lut_sm);
             if constexpr (sizeof(OutT) == 2) pk[j] = pack8<OutT>(y);
         }
+    }
+}
+// The residual form of the same with the residual's four 16-byte pieces of this row already fetched by the caller
+template <typename OutT, int VS = 128, int KIND = 0>
+__device__ __forceinline__ void chunk_compute16_resid(const GemmParams& p, const uint32_t (&r)[32], int row, int col0, float xs_r,
+                                                      const float* vs, uint4 (&pk)[4], const uint4 (&rq)[4]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float y[8];
+        epilogue8<OutT, EPI_RESID, VS, KIND>(p, r + 8 * j, row, col0 + 8 * j, xs_r, true, y, vs + 8 * j, nullptr, true, rq[j]);
+        if constexpr (sizeof(OutT) == 2) pk[j] = pack8<OutT>(y);
     }
 }
 __device__ __forceinline__ void chunk_write16(const uint4 (&pk)[4], uint8_t* stage, int lane) {
@@ -868,7 +897,59 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     chunk_direct<OutT, EPI, KIND>(p, r, row, col0, xs_r);
                 }
             };
-            if (wi.kind == ITEM_WHOLE) {
+            constexpr bool kResidStaged = EPI == EPI_RESID && kStageVec;
+            if (kResidStaged && wi.kind == ITEM_WHOLE) {
+                // Residual form. Fetched one by one in front of their eight columns, the residual's 16-byte pieces put four
+                // memory latencies per chunk on the drain of a cluster's last tile (this form was 13 us slower than the
+                // plain one on the down-projection). Here a chunk's four pieces are requested together, one chunk ahead
+                // of their use; the pieces take the place of the second accumulator register set.
+                if constexpr (kResidStaged) {
+                    auto pieces = [&](uint4 (&rq)[4], int c) {
+                        const uint4* rsd = reinterpret_cast<const uint4*>(reinterpret_cast<const OutT*>(p.resid) + (int64_t)rrow * p.N + n0 + c * 32);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) rq[j] = rsd[j];
+                    };
+                    auto finish = [&](const uint32_t (&r)[32], const uint4 (&rq)[4], int c) {
+                        uint4 pk[4];
+                        chunk_compute16_resid<OutT, 128, KIND>(p, r, rrow, n0 + c * 32, xs_r, my_vec + 32 * ((c - half) >> 1), pk, rq);
+                        if (lane == 0) bulk_wait_read<0>();   // the previous chunk's store has read the buffer
+                        __syncwarp();
+                        chunk_write16(pk, my_stage, lane);
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d(&tmap_d, my_stage_u32, n0 + c * 32, row0);
+                            bulk_commit();
+                        }
+                    };
+                    if (staged && p.vec_ok && n0 + BN <= p.N) {
+                        uint4 qa[4], qb[4];
+                        int c = half;
+                        if (c < nchunks) pieces(qa, c);
+#pragma unroll 1
+                        for (; c < nchunks; c += 4) {
+                            tmem_ld32(taddr + c * 32, ra);
+                            if (c + 2 < nchunks) pieces(qb, c + 2);
+                            tmem_ld_wait();
+                            finish(ra, qa, c);
+                            if (c + 2 < nchunks) {
+                                tmem_ld32(taddr + (c + 2) * 32, ra);
+                                if (c + 4 < nchunks) pieces(qa, c + 4);
+                                tmem_ld_wait();
+                                finish(ra, qb, c + 2);
+                            }
+                        }
+                    } else {      // direct stores, unaligned vectors, a tile that reaches past N
+#pragma unroll 1
+                        for (int c = half; c < nchunks; c += 2) {
+                            if (n0 + c * 32 >= p.N) break;
+                            tmem_ld32(taddr + c * 32, ra);
+                            tmem_ld_wait();
+                            emit(ra, c);
+                        }
+                    }
+                }
+            } else if (!kResidStaged && wi.kind == ITEM_WHOLE) {
                 int c = half;
                 if (c < nchunks) tmem_ld32(taddr + c * 32, ra);
 #pragma unroll 1
