@@ -54,6 +54,7 @@ KERNELS = {
     "gemm_up_rot": lambda b, I: I.int8_gemm_act_rot(b.a1, b.w1, b.xs1, b.s1, b.b1, act=1, out=b.h, amax_part=b.parts),
     "quant_rotated": lambda b, I: I.quant_rows_rotated(b.h, b.parts, q=b.a2, scales=b.xs2),
     "gemm_down": lambda b, I: I.int8_gemm(b.a2, b.w2, b.xs2, b.s2, b.b2, rscale=b.ones, resid=b.x, out=b.out),
+    "gemm_down_plain": lambda b, I: I.int8_gemm(b.a2, b.w2, b.xs2, b.s2, b.b2, out=b.out),      # the same without the residual
     # the up-projection with its weight in W6 storage (fitted group scales / s_rel = 1), unpacked inside the GEMM
     "w6a8_up": lambda b, I: I.w6a8_gemm(b.a1, b.w6[0], b.w6[1], b.xs1, b.w6[2], b.b1, out=b.h),
     "w6a8_up_unit": lambda b, I: I.w6a8_gemm(b.a1, b.w6u[0], b.w6u[1], b.xs1, b.w6u[2], b.b1, out=b.h),

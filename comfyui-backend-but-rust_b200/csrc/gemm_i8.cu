@@ -477,15 +477,16 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 // row's maximum over this warp's share beside it: what the quantizer's second pass needs. Tile width 256, bf16 and whole
 // tiles only (the host side sees to it). The two warps of a lane quarter split the work, and tensor memory is their
 // scratch (the accumulator is rewritten in place, as f32). Warp h of the two:
-//   A  columns [128 h, 128 h + 128), eight at a time: dequantize, activation from the table, back to tensor memory;
-//   B  the same columns as two 64-column blocks: stages of strides 1, 4 and 16 (64 values in registers), back again;
-//      barrier between the two warps;
-//   C  the last stage (columns j, j + 64, j + 128, j + 192) for the offsets j in [32 h, 32 h + 32), sixteen at a time: row
-//      maximum, rounding to bf16, and out through shared memory with TMA stores of 16-column boxes.
-// This epilogue, not the tensor core, bounds the kernel, and its warps wait for latency and instruction fetch, not for
-// issue slots: the loops are kept rolled (unrolled, "no instruction" was the largest stall), tensor-memory loads of step A
-// run one step ahead, and the next tile's per-column vectors and row scale are fetched a tile ahead. Plain 16-byte stores
-// from the registers (a row per lane) were slower than the staged TMA stores, and so were sixteen warps instead of eight.
+//   1  columns [128 h, 128 h + 128) as two 64-column blocks: dequantize, activation from the table, the stages of strides
+//      1, 4 and 16 (64 values in registers), back to tensor memory; barrier between the two warps;
+//   2  the last stage (columns j, j + 64, j + 128, j + 192) for the offsets j in [32 h, 32 h + 32), sixteen at a time: row
+//      maximum, rounding to bf16, and out through shared memory with TMA stores of 16-column boxes, two per fence.
+// This epilogue, not the tensor core, bounds the kernel (builds with one part of it left out each: the tensor-memory stores,
+// the staged stores and the butterflies cost about as much each, the table look-ups a third of that), and its warps wait
+// for latency and instruction fetch, not for issue slots: the loops are kept rolled (fully unrolled, "no instruction" was
+// the largest stall), and the next tile's per-column vectors and row scale are fetched a tile ahead. Plain 16-byte stores
+// from the registers (a row per lane) were slower than the staged TMA stores, and so were sixteen warps instead of eight
+// and a pass of its own for the table look-ups (eight columns a step through tensor memory).
 __device__ __forceinline__ void rotate_block64(uint32_t (&a)[32], uint32_t (&b)[32], bool exact) {
     // Three stages (strides 1, 4, 16) of one 64-column block, left as half the reference's values: without the per-stage
     // halvings and one multiplication by 1/16 at the end, or, next to huge values (where the unhalved sums could overflow
@@ -560,39 +561,36 @@ __device__ __forceinline__ void epilogue_rot(const GemmParams& p, const CUtensor
         bool big = false;   // a value of 2^120 or more (or an infinity, a NaN) among this warp's: exact halvings
         if (got) {
             const uint32_t ta = taddr + 128 * half;
-            // A: dequantize + activation, eight columns a step, the next step's load in flight
-            bool wide = false;
-            uint32_t r0[8], r1[8];
-            auto convert = [&](const uint32_t (&r)[8], int g) {
-                uint32_t t[8];
-                if (!epilogue8_lut_bits<128>(p, r, xs_r, my_vec + 8 * g, lut_sm, t)) {
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) wide |= (t[e] & 0x7fffu) >= 0x7B80u;
-                }
-#pragma unroll
-                for (int e = 0; e < 8; ++e) t[e] <<= 16;
-                tmem_st8(ta + 8 * g, t);
-            };
-            tmem_ld8(ta, r0);
-#pragma unroll 1
-            for (int g = 0; g < 16; g += 2) {
-                tmem_ld_wait();
-                tmem_ld8(ta + 8 * (g + 1), r1);
-                convert(r0, g);
-                tmem_ld_wait();
-                if (g + 2 < 16) tmem_ld8(ta + 8 * (g + 2), r0);
-                convert(r1, g + 1);
-            }
-            big = __any_sync(0xffffffffu, wide);
-            tmem_st_wait();
-            // B: three stages per 64-column block
+            // A + B per 64-column block: dequantize, activation from the table, three stages, back to tensor memory
+            // (loading the next half block ahead of its use through a third register set was slower: 1.23 against 1.21
+            // times the plain kernel)
 #pragma unroll 1
             for (int blk = 0; blk < 2; ++blk) {
                 uint32_t a[32], b[32];
                 tmem_ld32(ta + 64 * blk, a);
                 tmem_ld32(ta + 64 * blk + 32, b);
                 tmem_ld_wait();
-                rotate_block64(a, b, big);
+                bool wide = false;
+                const float* vs = my_vec + 64 * blk;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint32_t t[8];
+                    if (!epilogue8_lut_bits<128>(p, a + 8 * j, xs_r, vs + 8 * j, lut_sm, t)) {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) wide |= (t[e] & 0x7fffu) >= 0x7B80u;
+                    }
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) a[8 * j + e] = t[e] << 16;
+                    if (!epilogue8_lut_bits<128>(p, b + 8 * j, xs_r, vs + 32 + 8 * j, lut_sm, t)) {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) wide |= (t[e] & 0x7fffu) >= 0x7B80u;
+                    }
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) b[8 * j + e] = t[e] << 16;
+                }
+                const bool ex = __any_sync(0xffffffffu, wide);
+                big |= ex;
+                rotate_block64(a, b, ex);
                 tmem_st32(ta + 64 * blk, a);
                 tmem_st32(ta + 64 * blk + 32, b);
             }
@@ -654,26 +652,34 @@ __device__ __forceinline__ void epilogue_rot(const GemmParams& p, const CUtensor
             }
             if (row_ok)
                 p.amax_part[(int64_t)row * (p.N >> 6) + 4 * tn + 2 * half + t] = has_nan ? __uint_as_float(__float_as_uint(m) | 0x80000000u) : m;
+            // out through the two staging buffers, two 16-column pieces per fence and store group
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                uint32_t o[8];
+            for (int kp = 0; kp < 4; kp += 2) {
+                uint32_t o[2][8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(q[k][2 * i]), __uint_as_float(q[k][2 * i + 1]));
-                    o[i] = *reinterpret_cast<const uint32_t*>(&h);
+                for (int u = 0; u < 2; ++u) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(q[kp + u][2 * i]), __uint_as_float(q[kp + u][2 * i + 1]));
+                        o[u][i] = *reinterpret_cast<const uint32_t*>(&h);
+                    }
                 }
-                if (lane == 0) bulk_wait_read<1>();   // the store before the last has read this buffer
+                if (lane == 0) bulk_wait_read<0>();   // the previous group's stores have read both buffers
                 __syncwarp();
                 // 32-byte rows with the 32-byte swizzle (the 16-byte half is flipped in every other group of four rows):
                 // without it rows r and r + 4 meet in the same banks
-                uint8_t* rowp = my_stage + (k & 1) * 1024 + lane * 32;
                 const int flip = ((lane >> 2) & 1) << 4;
-                *reinterpret_cast<uint4*>(rowp + flip) = make_uint4(o[0], o[1], o[2], o[3]);
-                *reinterpret_cast<uint4*>(rowp + (16 ^ flip)) = make_uint4(o[4], o[5], o[6], o[7]);
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    uint8_t* rowp = my_stage + u * 1024 + lane * 32;
+                    *reinterpret_cast<uint4*>(rowp + flip) = make_uint4(o[u][0], o[u][1], o[u][2], o[u][3]);
+                    *reinterpret_cast<uint4*>(rowp + (16 ^ flip)) = make_uint4(o[u][4], o[u][5], o[u][6], o[u][7]);
+                }
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
-                    tma_store_2d(tmap_d16, my_stage_u32 + (k & 1) * 1024, n0 + 64 * k + j0, row0);
+                    tma_store_2d(tmap_d16, my_stage_u32, n0 + 64 * kp + j0, row0);
+                    tma_store_2d(tmap_d16, my_stage_u32 + 1024, n0 + 64 * (kp + 1) + j0, row0);
                     bulk_commit();
                 }
             }
