@@ -405,12 +405,14 @@ def run_reference_cpu(args, rank):
                       "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
 
 
-def profiled_dram_bytes():
+def profiled_dram_bytes(rotating: bool = False):
     """DRAM bytes (read + write) of one launch of the dominant kernel, from the record line of the committed ncu summary
-    profiles/gemm_i8_pair_mlp_up.md ("dram_bytes_per_launch: <read> + <write>"); None when the summary is absent."""
+    of the kernel form the step runs ("dram_bytes_per_launch: <read> + <write>" in profiles/gemm_i8_pair_mlp_up.md or
+    profiles/gemm_i8_pair_rotating_epilogue_mlp_up.md); None when the summary is absent."""
     import re
+    name = "gemm_i8_pair_rotating_epilogue_mlp_up.md" if rotating else "gemm_i8_pair_mlp_up.md"
     try:
-        text = open(os.path.join(ROOT, "profiles", "gemm_i8_pair_mlp_up.md")).read()
+        text = open(os.path.join(ROOT, "profiles", name)).read()
     except OSError:
         return None
     m = re.search(r"dram_bytes_per_launch:\s*([0-9.eE+]+)\s*\+\s*([0-9.eE+]+)", text)
@@ -648,7 +650,7 @@ def main():
                 "peak": peak, "unit": "TOPS", "frac": achieved / peak,
                 "peak_source": f"2 x {src} dense bf16 burst ({bf16_burst} TFLOP/s); no int8 figure is measured on this pool",
                 "frac_of_nominal_4500": achieved / INT8_NOMINAL_TOPS, "us_per_launch": k_ms * 1e3,
-                "traffic": profiled_dram_bytes(),
+                "traffic": profiled_dram_bytes(rot),
                 "plain_epilogue": sub(plain_ms)}
     if act_ms is not None:
         roofline["act_epilogue"] = sub(act_ms)

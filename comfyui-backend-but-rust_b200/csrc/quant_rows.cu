@@ -1054,6 +1054,16 @@ __global__ void __launch_bounds__(256) quant_rotated_kernel(const bf16* __restri
     const int64_t m = gw / wpr;
     const int seg = (int)(gw - m * wpr);
     if (m >= M) return;
+    const int per = K / wpr;
+    const bf16* src = xr + m * (int64_t)K + (int64_t)seg * per;
+    int8_t* dst = q + m * (int64_t)K + (int64_t)seg * per;
+    // the first two steps' values are requested before the row's maximum is known: the partial maxima and the rows then
+    // arrive together instead of one after the other
+    uint4 a0, b0, a1, b1;
+    a0 = b0 = a1 = b1 = make_uint4(0, 0, 0, 0);
+    const int e0 = lane * 16;
+    if (e0 < per) a0 = __ldg(reinterpret_cast<const uint4*>(src + e0)), b0 = __ldg(reinterpret_cast<const uint4*>(src + e0 + 8));
+    if (e0 + 512 < per) a1 = __ldg(reinterpret_cast<const uint4*>(src + e0 + 512)), b1 = __ldg(reinterpret_cast<const uint4*>(src + e0 + 520));
     float amax = 0.f;
     uint32_t flag = 0;
     for (int i = lane; i < P; i += 32) {
@@ -1072,12 +1082,7 @@ __global__ void __launch_bounds__(256) quant_rotated_kernel(const bf16* __restri
     // rows holding an infinity or a NaN keep the IEEE division and the exact clamp
     const bool fast = amax <= FLT_MAX && flag == 0;
     const float rcp = fast ? __frcp_rn(st) : 0.f;
-    const int per = K / wpr;
-    const bf16* src = xr + m * (int64_t)K + (int64_t)seg * per;
-    int8_t* dst = q + m * (int64_t)K + (int64_t)seg * per;
-#pragma unroll 2
-    for (int e = lane * 16; e < per; e += 512) {
-        const uint4 a = __ldg(reinterpret_cast<const uint4*>(src + e)), b = __ldg(reinterpret_cast<const uint4*>(src + e + 8));
+    auto convert = [&](const uint4 a, const uint4 b, int e) {
         const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
         uint32_t c[8];
         if (fast) {
@@ -1090,6 +1095,18 @@ __global__ void __launch_bounds__(256) quant_rotated_kernel(const bf16* __restri
         }
         *reinterpret_cast<uint4*>(dst + e) = make_uint4((c[0] & 0xffffu) | (c[1] << 16), (c[2] & 0xffffu) | (c[3] << 16),
                                                         (c[4] & 0xffffu) | (c[5] << 16), (c[6] & 0xffffu) | (c[7] << 16));
+    };
+    // two steps in flight: a step's values are replaced by those of the step after next before it is converted
+#pragma unroll 1
+    for (int e = e0; e < per; e += 1024) {
+        uint4 a = a0, b = b0;
+        if (e + 1024 < per) a0 = __ldg(reinterpret_cast<const uint4*>(src + e + 1024)), b0 = __ldg(reinterpret_cast<const uint4*>(src + e + 1032));
+        convert(a, b, e);
+        if (e + 512 < per) {
+            a = a1, b = b1;
+            if (e + 1536 < per) a1 = __ldg(reinterpret_cast<const uint4*>(src + e + 1536)), b1 = __ldg(reinterpret_cast<const uint4*>(src + e + 1544));
+            convert(a, b, e + 512);
+        }
     }
 }
 }  // namespace
