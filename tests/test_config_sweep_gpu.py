@@ -4,8 +4,8 @@ kernels (oracle/_ref/libref.so, built from the reference tree) on the same devic
 Per linear: the activation quantizer's codes and scales, the packed / quantized weight, the GEMM output with bias
 (and the residual form where the configuration has one) must be bit-identical; the int32 accumulators are checked
 against an integer product (torch._int_mm, a library routine used here as a checker only); where the configuration has
-a GELU epilogue, "activation epilogue then PLAIN quantizer" must give the codes of the reference's "plain GEMM then
-GELU-tanh prologue quantizer". W6A8 linears are compared with the reference's decode followed by its int8 GEMM.
+a GELU epilogue, "activation epilogue then PLAIN quantizer" and "activation + rotation epilogue then the quantizer's second
+pass" must both give the codes of the reference's "plain GEMM then GELU-tanh prologue quantizer". W6A8 linears are compared with the reference's decode followed by its int8 GEMM.
 The first configuration additionally runs against the CPU oracle in full."""
 from __future__ import annotations
 
@@ -130,6 +130,13 @@ def test_linear_bit_exact_against_the_reference_kernels(pkg, ref, dev, index):
         assert_bits_equal(q2, q2r, "codes after the GELU epilogue")
         if sp.weight_format == "w6":
             assert_bits_equal(L.w6a8_gemm(a8, packed, s_rel, xs, ws, bias, out_dtype=dt, act=1), ya, "W6A8 GEMM with the GELU epilogue")
+        if sp.rotate and N % 256 == 0:
+            # activation and rotation in the GEMM's epilogue, the quantizer's second pass after it
+            rows, parts = L.int8_gemm_act_rot(a8, wq, xs, ws, bias, act=1)
+            q4, s4 = L.quant_rows_rotated(rows, parts)
+            assert_bits_equal(s4, s2r, "scales after the rotating epilogue")
+            assert_bits_equal(q4, q2r, "codes after the rotating epilogue")
+            del rows, parts, q4
         q3, s3 = L.quant_rows(y, 11, 1 if sp.rotate else 0)                                    # and the prologue form itself
         assert_bits_equal(q3, q2r, "codes of the GELU-tanh prologue")
         assert_bits_equal(s3, s2r, "scales of the GELU-tanh prologue")
