@@ -654,6 +654,11 @@ def main():
                 "plain_epilogue": sub(plain_ms)}
     if act_ms is not None:
         roofline["act_epilogue"] = sub(act_ms)
+    if clocks and clocks.get("sm_mhz"):
+        # time x the SM clock sampled under the sustained load: separates the kernel from the power-capped clock (the
+        # roofline launches run in short bursts, so their own clock lies between this one and the maximum)
+        roofline["kcycles_at_sampled_clock"] = {"sm_mhz": clocks["sm_mhz"], "as_in_step": k_ms * clocks["sm_mhz"],
+                                                "plain_epilogue": plain_ms * clocks["sm_mhz"]}
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
             "data": "synthetic",
