@@ -470,7 +470,6 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 template <int N> __device__ __forceinline__ void bulk_wait_read() {
     asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // ---- the rotating epilogue (EPI_ACT_ROT) --------------------------------------------------------------------------------
 // Activation, then the R256 rotation of the tile's 256 columns (one rotation group per row), written as bf16 with the
@@ -687,7 +686,8 @@ __device__ __forceinline__ void epilogue_rot(const GemmParams& p, const CUtensor
         buf ^= 1;
         if (buf == 0) tphase ^= 1u;
     }
-    if (lane == 0) bulk_wait_all();   // staged rows have left shared memory before the CTA exits
+    if (lane == 0) bulk_wait_read<0>();   // staged rows have left shared memory before the CTA exits (the writes
+                                          // themselves are complete when the grid is)
 }
 
 template <typename OutT, int EPI, int KIND = 0>
@@ -1006,7 +1006,8 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             buf ^= 1;
             if (buf == 0) tphase ^= 1u;
         }
-        if (p.tma_store && lane == 0) bulk_wait_all();   // staged rows have left shared memory before the CTA exits
+        if (p.tma_store && lane == 0) bulk_wait_read<0>();   // staged rows have left shared memory before the CTA exits
+                                                             // (the writes themselves are complete when the grid is)
         }
     }
 

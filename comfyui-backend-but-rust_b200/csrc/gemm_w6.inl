@@ -335,7 +335,7 @@ gemm_w6a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             buf ^= 1;
             if (buf == 0) tphase ^= 1u;
         }
-        if (p.tma_store && lane == 0) bulk_wait_all();
+        if (p.tma_store && lane == 0) bulk_wait_read<0>();   // the staged rows have been read; the grid's end completes the writes
     }
 
     __syncwarp();
