@@ -224,7 +224,7 @@ class Block:
         self.a1 = torch.empty((M, up.K), dtype=torch.int8, device=dev)
         self.xs1 = torch.empty((M,), dtype=torch.float32, device=dev)
         self.h = torch.empty((M, up.N), dtype=torch.bfloat16, device=dev)
-        self.parts = torch.empty((M, up.N // 64), dtype=torch.float32, device=dev)
+        self.parts = torch.empty((up.N // 64, M), dtype=torch.float32, device=dev)
         self.a2 = torch.empty((M, down.K), dtype=torch.int8, device=dev)
         self.xs2 = torch.empty((M,), dtype=torch.float32, device=dev)
         self.out = torch.empty((M, down.N), dtype=torch.bfloat16, device=dev)

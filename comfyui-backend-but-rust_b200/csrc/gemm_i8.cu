@@ -79,7 +79,7 @@ struct GemmParams {
     uint32_t idesc;      // instruction descriptor for M = 256, N = bn
     const uint16_t* act_lut;   // EPI_ACT with bf16 outputs: bf16(act(x)) for every bf16 x (a tanhf or erff per element
                                // made the epilogue, not the tensor core, the limit: 836 against 2740 TOPS), or null
-    float* amax_part;          // EPI_ACT_ROT: [M, N / 64] partial row maxima of |rotated value| (four per tile, see the
+    float* amax_part;          // EPI_ACT_ROT: [N / 64, M] partial row maxima of |rotated value| (four per tile, see the
                                // epilogue), sign bit set when the part held a NaN
 };
 
@@ -649,8 +649,11 @@ __device__ __forceinline__ void epilogue_rot(const GemmParams& p, const CUtensor
                     for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(__uint_as_float(q[k][i])));
                 }
             }
+            // part-major, so that a warp's 32 rows make one 128-byte store (row-major, the 4-byte stores of a warp went to
+            // 32 different sectors, each of them written eight times over the launch: at 16896 rows, where the output
+            // streams through L2, that made the kernel 1.6 times the plain one instead of 1.2)
             if (row_ok)
-                p.amax_part[(int64_t)row * (p.N >> 6) + 4 * tn + 2 * half + t] = has_nan ? __uint_as_float(__float_as_uint(m) | 0x80000000u) : m;
+                p.amax_part[(int64_t)(4 * tn + 2 * half + t) * p.M + row] = has_nan ? __uint_as_float(__float_as_uint(m) | 0x80000000u) : m;
             // out through the two staging buffers, two 16-column pieces per fence and store group
 #pragma unroll
             for (int kp = 0; kp < 4; kp += 2) {
@@ -1491,7 +1494,7 @@ GPU_API int gpu_int8_gemm_act(const int8_t* A, const int8_t* W, const float* xs,
 // rotation is what that kernel spends its time on. Here the up-projection's epilogue, which holds one whole rotation group
 // of each row (256 columns) in tensor memory, applies the activation and the rotation while the tensor cores run the next
 // tile, and leaves   D[m, :] = bf16(R256(act(bf16(acc * xs * ws + bias))))   (bf16 only) together with
-// amax_part[m, N / 64]: partial maxima of the unrounded rotated values, four per tile (sign bit: a NaN was among them).
+// amax_part[N / 64, M]: partial maxima of the unrounded rotated values, four per tile (sign bit: a NaN was among them).
 // gpu_quant_rows_rotated turns the two into the codes and scales gpu_quant_rows(prologue = the activation, rotate = 1)
 // gives on the plain GEMM's output, bit for bit. N % 256 == 0, K % 16 == 0, 16-byte aligned operands, act 1..3 (-208 otherwise).
 GPU_API int gpu_int8_gemm_act_rot(const int8_t* A, const int8_t* W, const float* xs, const float* ws, const void* bias, void* D,

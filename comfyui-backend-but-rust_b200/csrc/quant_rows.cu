@@ -1042,40 +1042,45 @@ GPU_API int gpu_quant_rows_scaled(int dtype, int prologue, const void* x, int64_
 
 // ---- second pass after a rotating GEMM epilogue -------------------------------------------------------------------------
 // gpu_int8_gemm_act_rot leaves the rows rotated and rounded to bf16, and per row N / 64 partial maxima of the unrounded
-// rotated values (sign bit: a NaN among them). What is left of the quantizer is the row maximum, the scale and one pass
-// over the row: 2 bytes read and 1 written per element. A row is shared by `wpr` warps (each re-reads the row's few
-// partial maxima); a lane converts 16 consecutive values per step.
+// rotated values (sign bit: a NaN among them), stored part-major [N / 64, M]. What is left of the quantizer is the row
+// maximum, the scale and one pass over the row: 2 bytes read and 1 written per element. A CTA takes 8 consecutive rows
+// (whose partial maxima are 32 contiguous bytes per part), `wpr` warps per row; a lane converts 16 consecutive values per
+// step.
 namespace {
-__global__ void __launch_bounds__(256) quant_rotated_kernel(const bf16* __restrict__ xr, const float* __restrict__ parts,
+constexpr int kRotRows = 8;
+__global__ void __launch_bounds__(512) quant_rotated_kernel(const bf16* __restrict__ xr, const float* __restrict__ parts,
                                                             int8_t* __restrict__ q, float* __restrict__ scales, int M, int K,
                                                             int P, int wpr) {
-    const int lane = threadIdx.x & 31;
-    const int64_t gw = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int64_t m = gw / wpr;
-    const int seg = (int)(gw - m * wpr);
-    if (m >= M) return;
+    __shared__ unsigned s_amax[kRotRows], s_flag[kRotRows];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int rloc = warp / wpr, seg = warp - rloc * wpr;
+    const int64_t m0 = (int64_t)blockIdx.x * kRotRows, m = m0 + rloc;
+    const bool live = m < M;
     const int per = K / wpr;
     const bf16* src = xr + m * (int64_t)K + (int64_t)seg * per;
     int8_t* dst = q + m * (int64_t)K + (int64_t)seg * per;
+    if (threadIdx.x < kRotRows) s_amax[threadIdx.x] = 0u, s_flag[threadIdx.x] = 0u;
     // the first two steps' values are requested before the row's maximum is known: the partial maxima and the rows then
     // arrive together instead of one after the other
     uint4 a0, b0, a1, b1;
     a0 = b0 = a1 = b1 = make_uint4(0, 0, 0, 0);
     const int e0 = lane * 16;
-    if (e0 < per) a0 = __ldg(reinterpret_cast<const uint4*>(src + e0)), b0 = __ldg(reinterpret_cast<const uint4*>(src + e0 + 8));
-    if (e0 + 512 < per) a1 = __ldg(reinterpret_cast<const uint4*>(src + e0 + 512)), b1 = __ldg(reinterpret_cast<const uint4*>(src + e0 + 520));
-    float amax = 0.f;
-    uint32_t flag = 0;
-    for (int i = lane; i < P; i += 32) {
-        const uint32_t u = __float_as_uint(__ldg(parts + m * P + i));
-        flag |= u & 0x80000000u;
-        amax = fmaxf(amax, __uint_as_float(u & 0x7fffffffu));
+    if (live && e0 < per) a0 = __ldg(reinterpret_cast<const uint4*>(src + e0)), b0 = __ldg(reinterpret_cast<const uint4*>(src + e0 + 8));
+    if (live && e0 + 512 < per) a1 = __ldg(reinterpret_cast<const uint4*>(src + e0 + 512)), b1 = __ldg(reinterpret_cast<const uint4*>(src + e0 + 520));
+    __syncthreads();
+    // the 8 rows' partial maxima, 8 consecutive floats per part; non-negative floats order as integers
+    for (int i = threadIdx.x; i < P * kRotRows; i += blockDim.x) {
+        const int r = i & (kRotRows - 1);
+        if (m0 + r < M) {
+            const uint32_t u = __float_as_uint(__ldg(parts + (int64_t)(i >> 3) * M + m0 + r));
+            atomicMax(&s_amax[r], u & 0x7fffffffu);
+            if (u & 0x80000000u) s_flag[r] = 1u;
+        }
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        flag |= __shfl_xor_sync(0xffffffffu, flag, o);
-    }
+    __syncthreads();
+    if (!live) return;
+    const float amax = __uint_as_float(s_amax[rloc]);
+    const uint32_t flag = s_flag[rloc];
     const float scale = fmaxf(fminf(amax, finite_max<bf16>()) * (1.f / 127.f), 1.0e-30f);
     if (seg == 0 && lane == 0) scales[m] = scale;
     const float st = rnd<bf16>(scale);
@@ -1112,18 +1117,17 @@ __global__ void __launch_bounds__(256) quant_rotated_kernel(const bf16* __restri
 }  // namespace
 
 // New: the quantizer's second pass on rows a rotating GEMM epilogue left (gpu_int8_gemm_act_rot): xr [M, K] bf16, rotated;
-// amax_part [M, K / 64]; q [M, K] int8 and scales [M] as gpu_quant_rows(prologue = that activation, rotate = 1) gives them
+// amax_part [K / 64, M]; q [M, K] int8 and scales [M] as gpu_quant_rows(prologue = that activation, rotate = 1) gives them
 // on the plain GEMM's output. K % 256 == 0 (-1); xr and q 16-byte aligned (-5).
 GPU_API int gpu_quant_rows_rotated(const void* xr, const float* amax_part, int8_t* q, float* scales, int M, int K, void* stream) {
     if (K <= 0 || (K % 256) != 0) return -1;
     if (M <= 0) return 0;
     if ((((uintptr_t)xr | (uintptr_t)q) & 15) != 0) return -5;
-    // enough warps for every SM to have many loads in flight: split long rows
-    const int wpr = K >= 8192 ? 4 : K >= 2048 ? 2 : 1;
-    const int64_t warps = (int64_t)M * wpr;
-    const unsigned grid = (unsigned)((warps + 7) / 8);
-    quant_rotated_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<const bf16*>(xr), amax_part, q, scales, M, K,
-                                                                 K / 64, wpr);
+    // enough warps for every SM to have many loads in flight: two warps share a long row
+    const int wpr = K >= 4096 ? 2 : 1;
+    const unsigned grid = (unsigned)((M + kRotRows - 1) / kRotRows);
+    quant_rotated_kernel<<<grid, kRotRows * wpr * 32, 0, (cudaStream_t)stream>>>(reinterpret_cast<const bf16*>(xr), amax_part, q,
+                                                                                 scales, M, K, K / 64, wpr);
     KCHECK();
     return 0;
 }

@@ -260,13 +260,13 @@ def int8_gemm(A, W, xs, ws, bias=None, *, out_dtype=torch.bfloat16, act: int = 0
 
 
 def int8_gemm_act_rot(A, W, xs, ws, bias=None, *, act: int = 1, out=None, amax_part=None):
-    """gpu_int8_gemm_act_rot: bf16(R256(act(linear output))) [M, N] and the partial row maxima [M, N / 64] that
+    """gpu_int8_gemm_act_rot: bf16(R256(act(linear output))) [M, N] and the partial row maxima [N / 64, M] that
     quant_rows_rotated turns into codes and scales."""
     _cuda(A)
     M, K = A.shape
     N = W.shape[0]
     D = out if out is not None else torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
-    parts = amax_part if amax_part is not None else torch.empty((M, N // 64), dtype=torch.float32, device=A.device)
+    parts = amax_part if amax_part is not None else torch.empty((N // 64, M), dtype=torch.float32, device=A.device)
     ok(_lib().gpu_int8_gemm_act_rot(_ptr(A), _ptr(W), _ptr(xs), _ptr(ws), _ptr(bias), _ptr(D), _ptr(parts), M, N, K, act,
                                     _stream()), "gpu_int8_gemm_act_rot")
     return D, parts

@@ -119,7 +119,10 @@ class TPPair:
 
     def __init__(self, ops, comm: Comm, weights: PairWeights, *, rotate: int = 1, act_prologue: int = PRO_PLAIN,
                  hidden_cols: Optional[slice] = None, exact: bool = False, bufs: Optional[dict] = None, chunks: int = 1,
-                 comm_stream=None):
+                 comm_stream=None, act_form: str = "rot"):
+        # act_form: where the activation of an MLP pair runs. "rot": with the rotation in the first GEMM's epilogue;
+        # "epilogue": in the epilogue, the whole quantizer after it; "prologue": in the quantizer (the reference's arrangement)
+        self.act_form = act_form
         self.ops, self.comm, self.w = ops, comm, weights
         self.rotate, self.pro, self.hidden_cols, self.exact = rotate, act_prologue, hidden_cols, exact
         self.bufs = bufs if bufs is not None else {}
@@ -153,10 +156,13 @@ class TPPair:
         # are reduced across the ranks between the quantizer's two passes.
         act = _ACT_OF_PROLOGUE.get(self.pro, 0)
         fused = (cuda and act and self.rotate and not self.exact and self.hidden_cols is None and dt == torch.bfloat16
-                 and n1 % 256 == 0 and F % 16 == 0 and hasattr(ops, "int8_gemm_act_rot"))
+                 and n1 % 256 == 0 and F % 16 == 0 and hasattr(ops, "int8_gemm_act_rot") and self.act_form == "rot")
+        in_epilogue = cuda and act and not fused and not self.exact and self.hidden_cols is None and self.act_form == "epilogue"
         if fused:
             h, parts = ops.int8_gemm_act_rot(a8, w.w1, xs, w.s1, w.b1, act=act, out=self._buf("h", (M, n1), dt, x_local),
-                                             amax_part=self._buf("parts", (M, n1 // 64), torch.float32, x_local))
+                                             amax_part=self._buf("parts", (n1 // 64, M), torch.float32, x_local))
+        elif in_epilogue:
+            h = ops.int8_gemm(a8, w.w1, xs, w.s1, w.b1, out_dtype=dt, act=act, out=self._buf("h", (M, n1), dt, x_local))
         else:
             h = ops.int8_gemm(a8, w.w1, xs, w.s1, w.b1, out_dtype=dt, out=self._buf("h", (M, n1), dt, x_local))   # [M, N1 / P]
         if self.hidden_cols is not None:
@@ -175,7 +181,10 @@ class TPPair:
             xs2_local = xs2[comm.rank * rows:(comm.rank + 1) * rows]
             return ops.int8_epilogue(acc, xs2_local, w.s2, w.b2, out_dtype=dt, rscale=self.ones, resid=x_local, out=out)
         qkw = dict(q=self._buf("a2", (M, kh), torch.int8, x_local), scales=self._buf("xs2", (M,), torch.float32, x_local)) if cuda else {}
-        a2, xs2 = ops.quant_rows_rotated(h, parts, **qkw) if fused else ops.quant_rows(h, self.pro, self.rotate, **qkw)
+        if fused:
+            a2, xs2 = ops.quant_rows_rotated(h, parts, **qkw)
+        else:
+            a2, xs2 = ops.quant_rows(h, PRO_PLAIN if in_epilogue else self.pro, self.rotate, **qkw)
         C = self.chunks if (cuda and P > 1 and self.comm_stream is not None and n2 % (8 * self.chunks) == 0) else 1
         if C == 1:
             part = ops.int8_gemm(a2, w.w2, xs2, w.s2, None, out_dtype=dt, out=self._buf("part", (M, n2), dt, x_local))   # partial sums, all rows
@@ -208,13 +217,13 @@ class TPBlock:
     rank computes its slice of the modulation vector, which the block's own ranks would consume)."""
 
     def __init__(self, ops, comm: Comm, attn: PairWeights, mlp: PairWeights, exact: bool = False, bufs: Optional[dict] = None,
-                 chunks: int = 1, comm_stream=None, adaln=None):
+                 chunks: int = 1, comm_stream=None, adaln=None, act_form: str = "rot"):
         v_cols = attn.w2.shape[1]
         self.ops, self.adaln = ops, adaln
         self.bufs = bufs if bufs is not None else {}
         common = dict(exact=exact, bufs=self.bufs, chunks=chunks, comm_stream=comm_stream)
         self.attn = TPPair(ops, comm, attn, rotate=1, act_prologue=PRO_PLAIN, hidden_cols=slice(2 * v_cols, 3 * v_cols), **common)
-        self.mlp = TPPair(ops, comm, mlp, rotate=1, act_prologue=PRO_GELU_TANH, **common)
+        self.mlp = TPPair(ops, comm, mlp, rotate=1, act_prologue=PRO_GELU_TANH, act_form=act_form, **common)
 
     def forward(self, x_local: torch.Tensor, cond: Optional[torch.Tensor] = None) -> torch.Tensor:
         if self.adaln is not None and cond is not None:
@@ -253,7 +262,7 @@ def link_model_ms(world: int, exact: bool, M: int = STACK_M) -> float:
 
 
 def run_stack(mode: str, rank: int, world: int, local: int, *, blocks: int = 60, steps: int = 3, warmup: int = 1,
-              chunks: int = 3, gemm_clusters: int = 0, graph: bool = True) -> dict:
+              chunks: int = 3, gemm_clusters: int = 0, graph: bool = True, act_form: str = "rot") -> dict:
     """One of the three ways to run the 60-block linear stack (QKV, attention-out, MLP up / down with GELU-tanh, adaLN) on
     `world` GPUs, timed with CUDA events (maximum over ranks):
       token     tokens sharded over the ranks, weights replicated, no data-path collective
@@ -292,7 +301,8 @@ def run_stack(mode: str, rank: int, world: int, local: int, *, blocks: int = 60,
         mlp = shard_pair(wu, su, bu, wd, sd, bd, r, w)
         n_mod = 6 * F // w                                       # the modulation vector's slice of this rank
         adaln = (wa[r * n_mod:(r + 1) * n_mod].contiguous(), sa[r * n_mod:(r + 1) * n_mod].contiguous(), ba[r * n_mod:(r + 1) * n_mod].contiguous())
-        stack.append(TPBlock(ops, comm, attn, mlp, exact, bufs=bufs, chunks=chunks, comm_stream=comm_stream, adaln=adaln))
+        stack.append(TPBlock(ops, comm, attn, mlp, exact, bufs=bufs, chunks=chunks, comm_stream=comm_stream, adaln=adaln,
+                             act_form=act_form))
         del wqkv, wo, wu, wd, wa
     rows = M // world
     x = torch.randn(rows, F, generator=torch.Generator(device=dev).manual_seed(99 + rank), device=dev).bfloat16()

@@ -98,8 +98,8 @@ int gpu_int8_gemm_act(const int8_t* A, const int8_t* W, const float* xs, const f
  * csrc/kernels.cu:76-259 with PRO_GELU_TANH / PRO_SILU / PRO_GELU and rotate = 1) with the activation AND the R256 rotation
  * moved into the GEMM's epilogue, which holds one rotation group (256 columns) of every row in tensor memory:
  *   gpu_int8_gemm_act_rot   D[m, :] = bf16( R256( act( bf16( acc * xs[m] * ws[n] + bias[n] ) ) ) )   (bf16 only), and
- *                           amax_part [M, N / 64] f32: partial row maxima of the unrounded rotated values (four per
- *                           256-column group), sign bit set when a NaN was among them;
+ *                           amax_part [N / 64, M] f32 (part-major): partial row maxima of the unrounded rotated values
+ *                           (four per 256-column group), sign bit set when a NaN was among them;
  *   gpu_quant_rows_rotated  xr = that D, amax_part -> q [M, K] int8, scales [M] f32.
  * The pair gives the codes and scales of gpu_int8_gemm followed by gpu_quant_rows(prologue = the activation, rotate = 1),
  * bit for bit. N % 256 == 0, K % 16 == 0, operands 16-byte aligned, act 1..3 (-208 otherwise); second call: K % 256 == 0

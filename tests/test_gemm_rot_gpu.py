@@ -99,4 +99,4 @@ def test_rejects_what_the_epilogue_cannot_rotate(pkg, dev):
         pkg.linear.int8_gemm_act_rot(A, W, xs, ws, bias, act=0)
     xr = torch.zeros((4, 384), dtype=torch.bfloat16, device=dev)
     with pytest.raises(pkg.GpuKernelError, match="-1"):
-        pkg.linear.quant_rows_rotated(xr, torch.zeros((4, 6), device=dev))
+        pkg.linear.quant_rows_rotated(xr, torch.zeros((6, 4), device=dev))
