@@ -67,3 +67,28 @@ def test_pair_on_two_gpus(tmp_path):
     fast = torch.cat([torch.load(tmp_path / f"out_0_{r}.pt") for r in range(2)])
     assert torch.equal(exact.view(torch.int16), want.view(torch.int16)), "exact mode: bit-identical to one GPU"
     assert (fast.float() - want.float()).abs().max().item() < 0.05 * want.float().abs().max().item()
+
+
+def test_the_three_arrangements_of_the_mlp_pair_agree_bit_for_bit():
+    """One GPU: the pair with GELU-tanh and the rotation in the first GEMM's epilogue, with the GELU in the epilogue and the
+    whole quantizer after it, and with the GELU in the quantizer's prologue (the reference's arrangement,
+    src/qwen21.rs:378-417) must write the same output."""
+    sys.path.insert(0, ROOT)
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    tp = importlib.import_module("cbr_b200.tensor_parallel")
+    L = pkg.linear
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(0)
+    w1, b1, w2, b2, x = _inputs(dev)
+    w1q, s1 = L.convrot_requant(w1)
+    w2q, s2 = L.convrot_requant(w2)
+    comm = tp.Comm()                      # no process group: world size 1
+    outs = {}
+    for form in ("rot", "epilogue", "prologue"):
+        pair = tp.TPPair(L, comm, tp.shard_pair(w1q, s1, b1, w2q, s2, b2, 0, 1), rotate=1, act_prologue=11, act_form=form)
+        outs[form] = pair.forward(x).clone()
+    torch.cuda.synchronize()
+    assert L.kernel_status() == 0
+    assert torch.equal(outs["rot"].view(torch.int16), outs["prologue"].view(torch.int16))
+    assert torch.equal(outs["epilogue"].view(torch.int16), outs["prologue"].view(torch.int16))
