@@ -562,7 +562,8 @@ __device__ __forceinline__ void epilogue_rot(const GemmParams& p, const CUtensor
             const uint32_t ta = taddr + 128 * half;
             // A + B per 64-column block: dequantize, activation from the table, three stages, back to tensor memory
             // (loading the next half block ahead of its use through a third register set was slower: 1.23 against 1.21
-            // times the plain kernel)
+            // times the plain kernel; so was keeping this warp's own half of every block in registers and sending only
+            // the partner's half through tensor memory: 1.28, the last stage then has to be unrolled over its two steps)
 #pragma unroll 1
             for (int blk = 0; blk < 2; ++blk) {
                 uint32_t a[32], b[32];
