@@ -42,6 +42,7 @@ constexpr int BK = 128;        // int8 elements (= bytes) of K per TMA box: one 
 constexpr int UMMA_K = 32;     // K of one tcgen05.mma kind::i8
 constexpr int kThreads = 320;  // warp 0 producer, warp 1 MMA, warps 2-9 epilogue
 constexpr int kEpiWarps = 8;
+constexpr double kSmallProblemOps = 2.0e9;           // below this many int8 operations a GEMM takes the one-CTA-per-tile kernel
 constexpr int kRotEpiWarps = 8;                      // epilogue warps of the rotating epilogue (two per tensor-memory lane quarter)
 constexpr int kRotThreads = 64 + 32 * kRotEpiWarps;
 constexpr int kMaxStages = 8;
@@ -1032,6 +1033,114 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
 }
 
+// ---- small problems: one CTA per 128 x bn tile --------------------------------------------------------------------------
+// A launch of the persistent CTA-pair kernel costs about 12 us before its size matters (cluster launch with the full shared
+// memory, two cluster barriers, 512 tensor-memory columns, a ring of 64 KB stages): for problems of a few hundred Mop (the
+// cross-attention K/V projections of the SDXL U-Net: 154 rows) that is the whole time. This kernel is the same dataflow
+// without the pair: one CTA per tile, tcgen05.mma.cta_group::1 (M = 128, N = bn <= 128, K = 32), a ring of 128-byte K boxes
+// of A (128 rows) and W (bn rows), one accumulator of bn tensor-memory columns, four epilogue warps (one per lane quarter)
+// that store straight to D with the arithmetic of the large kernel. Warp 0 loads, warp 1 issues the MMAs.
+constexpr int kSmallThreads = 192;
+constexpr int kSmallMaxStages = 8;
+template <typename OutT, int EPI>
+__global__ void __launch_bounds__(kSmallThreads, 1)
+gemm_i8_small_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t* sm = smem_raw + (base - raw_addr);
+    const int S = p.stages, BN = p.bn;
+    const uint32_t a_bytes = BM * BK, b_bytes = (uint32_t)BN * BK;
+    const uint32_t sA = base, sB = sA + S * a_bytes;
+    uint8_t* tail = sm + S * (a_bytes + b_bytes);
+    const uint32_t bar_full = smem_u32(tail), bar_empty = bar_full + 8 * kSmallMaxStages, bar_tfull = bar_empty + 8 * kSmallMaxStages;
+    uint32_t* tmem_ptr_s = reinterpret_cast<uint32_t*>(tail + 8 * (2 * kSmallMaxStages + 1));
+    volatile int* abort_s = reinterpret_cast<volatile int*>(tmem_ptr_s + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t tmem_cols = BN <= 32 ? 32u : BN <= 64 ? 64u : 128u;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < S; ++i) {
+            mbar_init(bar_full + 8 * i, 1);
+            mbar_init(bar_empty + 8 * i, 1);
+        }
+        mbar_init(bar_tfull, 1);
+        *abort_s = 0;
+        fence_mbar_init();
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_w);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_ptr_s), tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_s;
+    const int tm = blockIdx.x % p.tiles_m, tn = blockIdx.x / p.tiles_m;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int kb = 0; kb < p.k_iters; ++kb) {
+                if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_s, ST_TIMEOUT_EMPTY)) break;
+                mbar_arrive_expect_tx(bar_full + 8 * stage, a_bytes + b_bytes);
+                tma_load_2d(sA + stage * a_bytes, &tmap_a, kb * BK, tm * BM, bar_full + 8 * stage);
+                tma_load_2d(sB + stage * b_bytes, &tmap_w, kb * BK, tn * BN, bar_full + 8 * stage);
+                if (++stage == S) stage = 0, phase ^= 1u;
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = p.idesc;
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int kb = 0; kb < p.k_iters; ++kb) {
+                if (!mbar_wait(bar_full + 8 * stage, phase, abort_s, ST_TIMEOUT_FULL)) { ok = false; break; }
+                tc_fence_after();
+                const uint64_t da = umma_desc_sw128(sA + stage * a_bytes), db = umma_desc_sw128(sB + stage * b_bytes);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) umma_i8(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);   // +32 bytes per step
+                umma_commit(bar_empty + 8 * stage);
+                if (++stage == S) stage = 0, phase ^= 1u;
+            }
+            if (ok) umma_commit(bar_tfull);
+        }
+    } else {
+        const int quad = warp & 3;               // TMEM lane quarter this warp may read (warps 2..5 cover all four)
+        const int row = tm * BM + quad * 32 + lane;
+        const bool row_ok = row < p.M;
+        const float xs_r = EPI == EPI_ACC ? 0.f : (p.xs && row_ok) ? p.xs[row] : 1.f;
+        if (mbar_wait_warp_relaxed(bar_tfull, 0, abort_s, ST_TIMEOUT_TMEM_FULL)) {
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+            uint32_t r[32];
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                const int col0 = tn * BN + c * 32;
+                if (col0 >= p.N) break;
+                tmem_ld32(taddr + c * 32, r);
+                tmem_ld_wait();
+                if (row_ok) chunk_direct<OutT, EPI, 0>(p, r, row, col0, xs_r);
+            }
+        }
+    }
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_s != 0) {
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);      // leave time for copies and MMAs still in flight, then report
+        if (threadIdx.x == 0) atomicCAS(&g_kernel_status, 0, *abort_s);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, tmem_cols);
+    }
+}
+
 // ---- host side ------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -1186,6 +1295,33 @@ int launch_pair_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tw, const
     }
 }
 
+template <typename OutT, int EPI>
+int launch_small(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, int grid, size_t smem, cudaStream_t st) {
+    auto kern = gemm_i8_small_kernel<OutT, EPI>;
+    static std::atomic<uint64_t> configured{0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const uint64_t bit = 1ull << (dev & 63);
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        configured.fetch_or(bit, std::memory_order_release);
+    }
+    kern<<<grid, kSmallThreads, smem, st>>>(ta, tw, p);
+    KCHECK();
+    return 0;
+}
+template <typename OutT>
+int launch_small_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, int grid, size_t smem,
+                     cudaStream_t st) {
+    switch (epi) {
+        case EPI_PLAIN: return launch_small<OutT, EPI_PLAIN>(ta, tw, p, grid, smem, st);
+        case EPI_RESID: return launch_small<OutT, EPI_RESID>(ta, tw, p, grid, smem, st);
+        case EPI_ACT: return launch_small<OutT, EPI_ACT>(ta, tw, p, grid, smem, st);
+        default: return -200;
+    }
+}
+
 // Scratch of the K-split forms (split few-tile problems, streamed tail): per device and stream, one buffer allocated on
 // first need and kept (a stream-ordered allocation per call cost more host time than the split saves). Counters and sums
 // are zero between launches: the buffer is cleared on the caller's stream before its first use, every kernel leaves it at
@@ -1289,6 +1425,44 @@ int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const f
     p.act = act;
     p.act_lut = nullptr;
     p.amax_part = amax_part;
+    // Small problems (the pair kernel's launch alone would be most of their time): one CTA per 128 x bn tile, the tile
+    // width chosen so that about a hundred CTAs or more share the work.
+    // (a few tiles with a long K stay with the pair kernel, which cuts them along K over all SMs)
+    int small_bn = 128;
+    const int small_tm = (int)((M + BM - 1) / BM);
+    while (small_bn > 32 && (int64_t)small_tm * ((N + small_bn - 1) / small_bn) < 96) small_bn >>= 1;
+    const int64_t small_tiles = (int64_t)small_tm * ((N + small_bn - 1) / small_bn);
+    const double ops = 2.0 * (double)M * (double)N * (double)K;
+    // measured on the SDXL shapes: below 2 Gop always (154 x 2048 x 640: 10.2 against 13.5 us in kernel); up to 8 Gop when
+    // the tiles fit the SMs in little more than one wave (2048 x 1280 x 1280, 160 tiles: 14.9 against 16.5 us; 8192 x 640 x
+    // 640, 320 tiles: 21.7 against 18.8, so not there)
+    const bool small = !rot && ((ops < kSmallProblemOps && (K <= 4096 || small_tiles >= 64)) ||
+                                (ops < 4.0 * kSmallProblemOps && K <= 4096 && small_tiles * 5 <= (int64_t)device_sm_count(dev) * 6));
+    if (small) {
+        const int tiles_m = small_tm;
+        const int bn = small_bn;
+        auto al16s = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
+        p.vec_ok = (N % 8 == 0) && al16s(D) && al16s(ws) && al16s(bias) && al16s(rscale) && al16s(resid);
+        p.tma_store = 0;
+        p.bn = bn, p.ksub = 1;
+        p.k_iters = (int)((K + BK - 1) / BK);
+        p.tiles_m = tiles_m, p.tiles_n = (int)((N + bn - 1) / bn), p.num_tiles = p.tiles_m * p.tiles_n;
+        // ring depth: the whole K if it fits; half the SM's shared memory when there are more tiles than SMs, so that two
+        // CTAs share an SM
+        const int stage_bytes = BM * BK + bn * BK;
+        const int budget = (p.num_tiles > device_sm_count(dev) ? kSmemBytes / 2 : kSmemBytes) - 1024 - 256;
+        p.stages = budget / stage_bytes;
+        if (p.stages > kSmallMaxStages) p.stages = kSmallMaxStages;
+        if (p.stages > p.k_iters) p.stages = p.k_iters;
+        p.idesc = umma_idesc_i8(BM, bn);
+        CUtensorMap ta, tw;
+        if (!make_operand_tmap(&ta, A, M, K, BM) || !make_operand_tmap(&tw, W, N, K, bn)) return -203;
+        const size_t smem = 1024 + (size_t)p.stages * (BM * BK + bn * BK) + 256;
+        if (epi == EPI_ACC) return launch_small<float, EPI_ACC>(ta, tw, p, p.num_tiles, smem, st);
+        if (out_dt == DT_F32) return launch_small_epi<float>(epi, ta, tw, p, p.num_tiles, smem, st);
+        if (out_dt == DT_F16) return launch_small_epi<half>(epi, ta, tw, p, p.num_tiles, smem, st);
+        return launch_small_epi<bf16>(epi, ta, tw, p, p.num_tiles, smem, st);
+    }
     const int esz = epi == EPI_ACC ? 4 : (out_dt == DT_F32 ? 4 : 2);
     auto al16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
     p.vec_ok = (N % 8 == 0) && al16(D) && al16(ws) && al16(bias) && al16(rscale) && al16(resid);
