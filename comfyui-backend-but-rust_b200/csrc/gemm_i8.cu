@@ -42,6 +42,7 @@ constexpr int BK = 128;        // int8 elements (= bytes) of K per TMA box: one 
 constexpr int UMMA_K = 32;     // K of one tcgen05.mma kind::i8
 constexpr int kThreads = 320;  // warp 0 producer, warp 1 MMA, warps 2-9 epilogue
 constexpr int kEpiWarps = 8;
+constexpr int64_t kResidentOperandBytes = 32ll << 20;   // an A this small stays in L2 while W and D stream past it
 constexpr double kSmallProblemOps = 2.0e9;           // below this many int8 operations a GEMM takes the one-CTA-per-tile kernel
 constexpr int kRotEpiWarps = 8;                      // epilogue warps of the rotating epilogue (two per tensor-memory lane quarter)
 constexpr int kRotThreads = 64 + 32 * kRotEpiWarps;
@@ -63,6 +64,7 @@ struct GemmParams {
     void* D;             // [M,N] out dtype, or int32 for EPI_ACC
     int M, N, K;
     int tiles_m, tiles_n, num_tiles, k_iters;
+    int group_m;         // row tiles per band of the tile order (0 = the default of 8)
     int act;
     int vec_ok;          // per-column vectors and rows of D / resid can be read and written 16 bytes at a time
     int tma_store;       // D is written through shared memory with TMA stores
@@ -84,14 +86,15 @@ struct GemmParams {
                                // epilogue), sign bit set when the part held a NaN
 };
 
-// Tile order: bands of 8 row tiles, column tile fastest-varying across the band's rows, so that the clusters
-// running at one time share a few A row-panels and W column-panels in L2.
-__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
-    constexpr int GROUP_M = 8;
-    const int per_group = GROUP_M * tiles_n;
+// Tile order: bands of `group_m` row tiles, column tile fastest-varying across the band's rows, so that the clusters
+// running at one time share a few A row-panels and W column-panels in L2. Eight rows per band balance the two operands
+// (74 tiles at a time make about a square); the host side picks taller bands when the band's rows of A can stay in L2
+// and W is too large to (up-projection M = 4352: one band, 109.7 against 113.3 us; 6144 x 5120 x 15360: 297 against 311).
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn, int group_m = 8) {
+    const int per_group = group_m * tiles_n;
     const int group = t / per_group;
-    const int first_m = group * GROUP_M;
-    const int gsize = min(GROUP_M, tiles_m - first_m);
+    const int first_m = group * group_m;
+    const int gsize = min(group_m, tiles_m - first_m);
     const int r = t - group * per_group;
     tm = first_m + r % gsize;
     tn = r / gsize;
@@ -527,7 +530,7 @@ __device__ __forceinline__ void epilogue_rot(const GemmParams& p, const CUtensor
     float nx_ws[4], nx_b[4], nx_xs = 1.f;
     auto fetch = [&](int w) {
         int tm, tn;
-        tile_coords(w, p.tiles_m, p.tiles_n, tm, tn);
+        tile_coords(w, p.tiles_m, p.tiles_n, tm, tn, p.group_m ? p.group_m : 8);
         const int row = tm * (2 * BM) + rank * BM + quad * 32 + lane;
         nx_xs = p.xs ? __ldg(p.xs + (row < p.M ? row : p.M - 1)) : 1.f;
 #pragma unroll
@@ -541,7 +544,7 @@ __device__ __forceinline__ void epilogue_rot(const GemmParams& p, const CUtensor
 
     for (int w = cluster_id; w < p.num_items; w += nclusters) {
         int tm, tn;
-        tile_coords(w, p.tiles_m, p.tiles_n, tm, tn);
+        tile_coords(w, p.tiles_m, p.tiles_n, tm, tn, p.group_m ? p.group_m : 8);
         const int n0 = tn * 256;
         const int row0 = tm * (2 * BM) + rank * BM + quad * 32;
         const int row = row0 + lane;
@@ -768,7 +771,7 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             for (int w = cluster_id; w < p.num_items && ok; w += nclusters) {
                 const WorkItem wi = decode_item(p, w);
                 int tm, tn;
-                tile_coords(wi.tile, p.tiles_m, p.tiles_n, tm, tn);
+                tile_coords(wi.tile, p.tiles_m, p.tiles_n, tm, tn, p.group_m ? p.group_m : 8);
                 const int row_a = tm * (2 * BM) + (int)rank * BM;
                 const int row_w = tn * BN + (int)rank * (BN / 2);
                 for (int kb = wi.k0; kb < wi.k0 + wi.kn; ++kb) {
@@ -856,7 +859,7 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         for (int w = cluster_id; w < p.num_items; w += nclusters) {
             const WorkItem wi = decode_item(p, w);
             int tm, tn;
-            tile_coords(wi.tile, p.tiles_m, p.tiles_n, tm, tn);
+            tile_coords(wi.tile, p.tiles_m, p.tiles_n, tm, tn, p.group_m ? p.group_m : 8);
             const int n0 = tn * BN;
             const int row0 = tm * (2 * BM) + (int)rank * BM + quad * 32;
             const int row = row0 + lane;
@@ -1485,6 +1488,13 @@ int run_gemm(int epi, const int8_t* A, const int8_t* W, const float* xs, const f
     p.tiles_m = (int)((M + 2 * BM - 1) / (2 * BM));
     p.tiles_n = (int)((N + bn - 1) / bn);
     p.num_tiles = p.tiles_m * p.tiles_n;
+    {   // Bands whose rows of A (M x K bytes) stay in L2 while W and D stream past, as few of them as that allows: W is
+        // then read from DRAM once per band. A small W stays in L2 by itself, and bands of eight rows (about a square of
+        // tiles per wave) serve both operands best (16896 x 3072 x 3072: 110 against 113 us with tall bands).
+        const int64_t bands = (M * K + kResidentOperandBytes - 1) / kResidentOperandBytes;
+        const int gm = (int)((p.tiles_m + bands - 1) / bands);
+        p.group_m = (N * K > kResidentOperandBytes / 2 && gm > 12) ? gm : 8;      // a little taller than eight makes no difference
+    }
     CUtensorMap ta, tw, td;
     if (!make_operand_tmap(&ta, A, M, K, BM) || !make_operand_tmap(&tw, W, N, K, bn / 2)) return -203;
     if (rot) {
